@@ -1,0 +1,195 @@
+/*
+ * monet_b200.h — C ABI of libmonet_b200.so, the sm_100a replacement for the
+ * native extensions underneath MONeT's low-memory operator library
+ * (monet/lm_ops/*.cpp, *.cu in utsaslab/MONeT).
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless the parameter name ends in
+ *     `_host`.  All activations are fp32.  Nothing here allocates device
+ *     memory: outputs and workspaces are supplied by the caller (the Python
+ *     operators obtain them from PyTorch's caching allocator so that MONeT's
+ *     memory profiler, monet/meminfo.py:231-243, keeps measuring the truth).
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default
+ *     stream).  Every kernel is enqueued on it; no call synchronises.
+ *   - Return value: MB_OK or an MB_ERR_* code; mb_last_error() gives the
+ *     message of the calling thread's last failure.
+ *   - `layout` selects the physical order of a logical N x C x H x W
+ *     activation: MB_NCHW (the reference's only layout) or MB_NHWC
+ *     (torch.channels_last; the layout the tensor-core convolutions use).
+ *   - Packed intermediates (1-bit ReLU masks, 4-bit max-pool indices) are
+ *     indexed by the PHYSICAL element offset, so for MB_NCHW they are
+ *     byte-identical with the reference's pack.cu output.
+ */
+#ifndef MONET_B200_H
+#define MONET_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  MB_OK = 0,
+  MB_ERR_INVALID_ARGUMENT = 1,   /* bad pointer / size / alignment            */
+  MB_ERR_UNSUPPORTED = 2,        /* variant or shape this build cannot run    */
+  MB_ERR_WORKSPACE = 3,          /* workspace missing or too small            */
+  MB_ERR_LAUNCH = 4,             /* CUDA reported an error at launch          */
+  MB_ERR_DEVICE = 5              /* kernel-side status word reported a fault  */
+};
+
+enum { MB_NCHW = 0, MB_NHWC = 1 };
+
+/* ---- library ---------------------------------------------------------- */
+
+/* Message of the calling thread's most recent failing call ("" if none).    */
+const char* mb_last_error(void);
+/* ABI version, bumped when a signature changes.                             */
+int mb_abi_version(void);
+/* Number of kernels this library has launched in this process (all threads).
+ * bench.py reads it to report `gpu_launches`.                               */
+unsigned long long mb_launch_count(void);
+
+/* ---- ReLU (replaces lrrelu.cpp:11-20, lrrelu.cu:4-15; relu.py:9-118) ---- */
+
+/* y = max(x, 0) (NaN propagates).  y may alias x (in-place, relu.py:17-18). */
+int mb_relu_fwd(const float* x, float* y, size_t n, void* stream);
+/* y = max(x, 0) and mask = packbits(x > 0), MSB first, ceil(n/8) bytes, tail
+ * bits zero: BinaryActReLU.forward (relu.py:100-104) + pack_kernel
+ * (pack.cu:22-31) in one pass.  y may alias x.                              */
+int mb_relu_fwd_mask(const float* x, float* y, uint8_t* mask, size_t n, void* stream);
+/* dx = bit ? dy : 0: BinaryActReLU.backward (relu.py:109-118) without the
+ * n-byte bool temporary of unpack_kernel (pack.cu:32-40).  dx may alias dy. */
+int mb_relu_bwd_mask(const float* dy, const uint8_t* mask, float* dx, size_t n, void* stream);
+/* dx = act > threshold ? dy : 0, `act` being the saved input or output:
+ * threshold_kernel (lrrelu.cu:4-9).  dx may alias dy (the reference always
+ * works in place on dy, lrrelu.cpp:14-15).                                  */
+int mb_relu_bwd_act(const float* dy, const float* act, float threshold, float* dx, size_t n,
+                    void* stream);
+
+/* ---- bit / nibble packing (replaces pack.cpp:38-131, pack.cu:3-50) ------ */
+
+/* out[j] bit (7-k) = (in[8j+k] != 0); ceil(n/8) bytes.                      */
+int mb_pack_bits(const uint8_t* in, uint8_t* out, size_t n, void* stream);
+/* out[i] = bit i of the packed stream, as 0/1 bytes.                        */
+int mb_unpack_bits(const uint8_t* in, uint8_t* out, size_t n, void* stream);
+/* out[i] = bit i ? v[i] : 0 (unpack_multiply_kernel, pack.cu:41-50).        */
+int mb_unpack_multiply(const uint8_t* in, const float* v, float* out, size_t n, void* stream);
+/* out[j] = in[2j] << 4 | in[2j+1]; ceil(n/2) bytes, odd tail low nibble 0.  */
+int mb_pack_nibbles(const uint8_t* in, uint8_t* out, size_t n, void* stream);
+int mb_unpack_nibbles(const uint8_t* in, uint8_t* out, size_t n, void* stream);
+
+/* ---- hardtanh / ReLU6 (replaces lrhardtanh.cpp:9-16; hardtanh.py:9-93) -- */
+
+int mb_hardtanh_fwd(const float* x, float* y, float lo, float hi, size_t n, void* stream);
+/* dx = (lo < act < hi) ? dy : 0, act = saved input or output.               */
+int mb_hardtanh_bwd(const float* dy, const float* act, float lo, float hi, float* dx, size_t n,
+                    void* stream);
+
+/* ---- residual add (replaces the ATen calls of funcs.py:23-59) ----------- */
+
+/* y = a + alpha * b.  y may alias a (AddIP with op.inplace).                */
+int mb_add_fwd(const float* a, const float* b, float alpha, float* y, size_t n, void* stream);
+/* y = alpha * x  (the `grad_output * s` of Add.backward when s != 1).       */
+int mb_scale(const float* x, float alpha, float* y, size_t n, void* stream);
+
+/* ---- max-pool with 4-bit window-local indices --------------------------- */
+/* (replaces maxpool.cpp:369-435, maxpool.cu:26-131 and the nibble kernels
+ *  pack.cu:3-21; pool.py:38-69)                                             */
+
+typedef struct {
+  int N, C, H, W;        /* input extent                                     */
+  int P, Q;              /* output extent                                    */
+  int kh, kw, sh, sw, ph, pw, dh, dw;
+  int layout;            /* MB_NCHW or MB_NHWC, same for input and output    */
+} mb_pool_desc;
+
+/* Output extent for one spatial dim (PyTorch's pooling_output_shape).       */
+int mb_pool_out_size(int in, int k, int s, int p, int d, int ceil_mode);
+/* y = maxpool(x); nibbles = packed window-local argmax, kh*kw <= 16.  Local
+ * index of tap (i,j) is i*kw+j counted from the UNCLIPPED window origin
+ * (maxpool.cu:42-61); first maximum wins, NaN wins.  Element e (physical
+ * offset in y) goes to byte e/2, even e in the high nibble (pack.cu:3-12).
+ * `nibbles` may be NULL (values only: SimpleMaxPool2D, pool.py:8-24).       */
+int mb_maxpool2d_fwd(const float* x, float* y, uint8_t* nibbles, const mb_pool_desc* d,
+                     void* stream);
+/* dx[n,c,h,w] = sum of dy over the windows whose stored index points at
+ * (h,w); every element of dx is written (no memset needed, unlike
+ * pool.py:64).                                                              */
+int mb_maxpool2d_bwd(const float* dy, const uint8_t* nibbles, float* dx, const mb_pool_desc* d,
+                     void* stream);
+
+/* ---- batch norm (replaces lrbn.cpp:21-172, lrbn.cu:138-235; bn.py) ------ */
+
+typedef struct {
+  int N, C, HW;          /* logical extent, HW = H*W                         */
+  int layout;
+  float eps;
+  float momentum;
+} mb_bn_desc;
+
+/* Bytes of scratch the statistics kernels need for this shape.              */
+size_t mb_bn_workspace_bytes(const mb_bn_desc* d);
+/* Training forward (lrbn.cpp:21-41): batch statistics over (N,H,W), then
+ * y = gamma*(x-mean)*invstd + beta.  Writes save_mean[C], save_invstd[C]
+ * (= 1/sqrt(biased var + eps), cuDNN semantics) and, when non-NULL, updates
+ * running_mean / running_var (unbiased) with `momentum`.  y may alias x.    */
+int mb_bn_fwd_train(const float* x, const float* gamma, const float* beta, float* running_mean,
+                    float* running_var, float* y, float* save_mean, float* save_invstd,
+                    const mb_bn_desc* d, void* workspace, size_t workspace_bytes, void* stream);
+/* y = gamma*(x-mean)*invstd + beta with given statistics: the recompute
+ * forward of bn.py:33-34 (with the exact saved invstd, i.e. without that
+ * path's second +eps).  y may alias x.                                      */
+int mb_bn_fwd_apply(const float* x, const float* gamma, const float* beta, const float* mean,
+                    const float* invstd, float* y, const mb_bn_desc* d, void* stream);
+/* Backward from the stored OUTPUT y (output_activated_bn_backward,
+ * lrbn.cpp:154-172, lrbn.cu:138-209): xhat = (y-beta)/gamma.  gamma == 0 is
+ * undefined, as in the reference.  dx may alias dy.                          */
+int mb_bn_bwd_from_output(const float* dy, const float* y, const float* gamma, const float* beta,
+                          const float* save_invstd, float* dx, float* dgamma, float* dbeta,
+                          const mb_bn_desc* d, void* workspace, size_t workspace_bytes,
+                          void* stream);
+/* Backward from the stored INPUT x (cudnn_backward, lrbn.cpp:43-70).         */
+int mb_bn_bwd_from_input(const float* dy, const float* x, const float* gamma,
+                         const float* save_mean, const float* save_invstd, float* dx,
+                         float* dgamma, float* dbeta, const mb_bn_desc* d, void* workspace,
+                         size_t workspace_bytes, void* stream);
+
+/* ---- softmax / cross-entropy (replaces softmax.cpp:11-33, softmax.cu) --- */
+
+/* Softmax over `classes` for a [outer, classes, inner] contiguous tensor.   */
+int mb_softmax_fwd(const float* x, float* y, size_t outer, int classes, size_t inner,
+                   int log_softmax, void* stream);
+/* dx = y*(dy - sum(dy*y)) (softmax) or dy - exp(y)*sum(dy) (log-softmax),
+ * one kernel instead of the reference's product + reduce pair
+ * (softmax.cpp:31).                                                          */
+int mb_softmax_bwd(const float* dy, const float* y, float* dx, size_t outer, int classes,
+                   size_t inner, int log_softmax, void* stream);
+/* Fused log-softmax + NLL forward AND backward in one pass over the logits
+ * ([outer, classes, inner], int64 labels [outer, inner]):
+ *   loss_rows[r] = logsumexp(x_r) - x_r[label_r]
+ *   dlogits      = (softmax(x_r) - onehot(label_r)) * grad_scale
+ * The reference has no such operator (its loss sits outside the graph,
+ * examples/imagenet.py:327); it stands for nn.CrossEntropyLoss fwd+bwd.     */
+int mb_softmax_ce_fwd_bwd(const float* logits, const int64_t* labels, float* loss_rows,
+                          float* dlogits, size_t outer, int classes, size_t inner,
+                          float grad_scale, void* stream);
+
+/* ---- layout / pooling glue --------------------------------------------- */
+
+/* Physical NCHW -> NHWC (and back) of an N x C x H x W fp32 tensor.         */
+int mb_nchw_to_nhwc(const float* x, float* y, int N, int C, int H, int W, void* stream);
+int mb_nhwc_to_nchw(const float* x, float* y, int N, int C, int H, int W, void* stream);
+/* Global average pool (adaptive_avg_pool2d to 1x1; funcs.py:7-21):
+ * y[N,C] = mean over H*W; backward dx = dy / HW broadcast, written fully
+ * (no zeros tensor as in funcs.py:20).                                       */
+int mb_global_avgpool_fwd(const float* x, float* y, int N, int C, int HW, int layout,
+                          void* stream);
+int mb_global_avgpool_bwd(const float* dy, float* dx, int N, int C, int HW, int layout,
+                          void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MONET_B200_H */

@@ -1,0 +1,101 @@
+"""ctypes binding of ``libmonet_b200.so`` (the C ABI declared in ``include/monet_b200.h``).
+
+There is no fallback: if the shared library is missing, ``lib()`` raises, and every
+operator that needs a kernel raises with it.  A non-zero status from an entry point
+becomes a ``RuntimeError`` carrying ``mb_last_error()``, which is what the reference's
+``try/except`` retry in conv.py:279-283 and the profiler's failure handling in
+meminfo.py:52-55 expect from a native op.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libmonet_b200.so"
+
+MB_NCHW, MB_NHWC = 0, 1
+
+c_f = C.c_void_p      # device pointers travel as integers
+c_sz = C.c_size_t
+
+
+class PoolDesc(C.Structure):
+    _fields_ = [(n, C.c_int) for n in
+                ("N", "C", "H", "W", "P", "Q", "kh", "kw", "sh", "sw", "ph", "pw", "dh", "dw",
+                 "layout")]
+
+
+class BnDesc(C.Structure):
+    _fields_ = [("N", C.c_int), ("C", C.c_int), ("HW", C.c_int), ("layout", C.c_int),
+                ("eps", C.c_float), ("momentum", C.c_float)]
+
+
+class ConvDesc(C.Structure):
+    _fields_ = [(n, C.c_int) for n in
+                ("N", "C", "H", "W", "K", "R", "S", "P", "Q", "stride_h", "stride_w", "pad_h",
+                 "pad_w", "dil_h", "dil_w", "groups")]
+
+
+# name -> (restype, argtypes); every symbol of include/monet_b200.h
+PROTOTYPES = {
+    "mb_last_error": (C.c_char_p, []),
+    "mb_abi_version": (C.c_int, []),
+    "mb_launch_count": (C.c_ulonglong, []),
+    "mb_relu_fwd": (C.c_int, [c_f, c_f, c_sz, c_f]),
+    "mb_relu_fwd_mask": (C.c_int, [c_f, c_f, c_f, c_sz, c_f]),
+    "mb_relu_bwd_mask": (C.c_int, [c_f, c_f, c_f, c_sz, c_f]),
+    "mb_relu_bwd_act": (C.c_int, [c_f, c_f, C.c_float, c_f, c_sz, c_f]),
+    "mb_pack_bits": (C.c_int, [c_f, c_f, c_sz, c_f]),
+    "mb_unpack_bits": (C.c_int, [c_f, c_f, c_sz, c_f]),
+    "mb_unpack_multiply": (C.c_int, [c_f, c_f, c_f, c_sz, c_f]),
+    "mb_pack_nibbles": (C.c_int, [c_f, c_f, c_sz, c_f]),
+    "mb_unpack_nibbles": (C.c_int, [c_f, c_f, c_sz, c_f]),
+    "mb_hardtanh_fwd": (C.c_int, [c_f, c_f, C.c_float, C.c_float, c_sz, c_f]),
+    "mb_hardtanh_bwd": (C.c_int, [c_f, c_f, C.c_float, C.c_float, c_f, c_sz, c_f]),
+    "mb_add_fwd": (C.c_int, [c_f, c_f, C.c_float, c_f, c_sz, c_f]),
+    "mb_scale": (C.c_int, [c_f, C.c_float, c_f, c_sz, c_f]),
+    "mb_pool_out_size": (C.c_int, [C.c_int] * 6),
+    "mb_maxpool2d_fwd": (C.c_int, [c_f, c_f, c_f, C.POINTER(PoolDesc), c_f]),
+    "mb_maxpool2d_bwd": (C.c_int, [c_f, c_f, c_f, C.POINTER(PoolDesc), c_f]),
+    "mb_bn_workspace_bytes": (c_sz, [C.POINTER(BnDesc)]),
+    "mb_bn_fwd_train": (C.c_int, [c_f] * 8 + [C.POINTER(BnDesc), c_f, c_sz, c_f]),
+    "mb_bn_fwd_apply": (C.c_int, [c_f] * 6 + [C.POINTER(BnDesc), c_f]),
+    "mb_bn_bwd_from_output": (C.c_int, [c_f] * 8 + [C.POINTER(BnDesc), c_f, c_sz, c_f]),
+    "mb_bn_bwd_from_input": (C.c_int, [c_f] * 8 + [C.POINTER(BnDesc), c_f, c_sz, c_f]),
+    "mb_softmax_fwd": (C.c_int, [c_f, c_f, c_sz, C.c_int, c_sz, C.c_int, c_f]),
+    "mb_softmax_bwd": (C.c_int, [c_f, c_f, c_f, c_sz, C.c_int, c_sz, C.c_int, c_f]),
+    "mb_softmax_ce_fwd_bwd": (C.c_int, [c_f, c_f, c_f, c_f, c_sz, C.c_int, c_sz, C.c_float, c_f]),
+    "mb_nchw_to_nhwc": (C.c_int, [c_f, c_f, C.c_int, C.c_int, C.c_int, C.c_int, c_f]),
+    "mb_nhwc_to_nchw": (C.c_int, [c_f, c_f, C.c_int, C.c_int, C.c_int, C.c_int, c_f]),
+    "mb_global_avgpool_fwd": (C.c_int, [c_f, c_f, C.c_int, C.c_int, C.c_int, C.c_int, c_f]),
+    "mb_global_avgpool_bwd": (C.c_int, [c_f, c_f, C.c_int, C.c_int, C.c_int, C.c_int, c_f]),
+}
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """The loaded library with typed entry points; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m monet_b200.build` "
+                "(there is no fallback path)")
+        handle = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in PROTOTYPES.items():
+            fn = getattr(handle, name)     # AttributeError if the symbol is not exported
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def last_error() -> str:
+    return lib().mb_last_error().decode("utf-8", "replace")
+
+
+def check(status: int, what: str = "") -> None:
+    """Raise RuntimeError for a non-zero status of a C-ABI call."""
+    if status != 0:
+        raise RuntimeError(f"libmonet_b200 {what} failed (status {status}): {last_error()}")

@@ -1,0 +1,553 @@
+// Batch normalisation for training: statistics + normalise forward (optionally
+// in place), cached-statistics forward, and a backward that works either from
+// the stored INPUT x or from the stored OUTPUT y (so x never has to be kept).
+//
+// Every pass is "reduce per channel, then a pure element-wise sweep":
+//
+//   reduce   grid = (row chunks S) x (channel slabs); each CTA reduces its rows
+//            with 128-bit loads, a shared-memory stage over the row lanes, and
+//            writes one partial per channel to the workspace  ws[2][S][C].
+//            Many CTAs per channel: a 64-channel layer still fills 148 SMs
+//            (the reference runs one CTA per channel, lrbn.cu:228-232).
+//   finalize one warp-column per channel sums the S partials in fp64 and writes
+//            the per-channel constants the sweep needs.
+//   sweep    element-wise, 128-bit, grid-stride.
+//
+// Forward statistics are accumulated around a per-channel shift K = the first
+// element of the channel, so var = E[(x-K)^2] - E[x-K]^2 does not cancel
+// catastrophically when |mean| >> std.
+//
+// Both backward flavours reduce S1 = sum(dy) and S2 = sum(dy * xhat):
+//   from input : xhat = (x - mean) * invstd
+//   from output: xhat = (y - beta) / gamma          (lrbn.cu:153-175)
+// and then   dx = (dy - xhat*S2/M - S1/M) * invstd * gamma,  dgamma = S2,
+// dbeta = S1  (lrbn.cu:176-208 written in terms of xhat).
+#include "common.cuh"
+
+namespace mb {
+namespace {
+
+constexpr int kBlock = 256;
+
+struct Geometry {
+  int C, HW, N;
+  size_t M;      // N*HW, elements per channel
+  int tx, ty;    // NHWC block shape: tx channel groups x ty rows
+  int slabs;     // NHWC: channel slabs of tx*4 channels
+  int S;         // chunks per channel
+  int vec;       // NHWC: 4 if C % 4 == 0 else 1
+};
+
+int pow2ceil(int v) {
+  int p = 1;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+Geometry make_geometry(const mb_bn_desc* d) {
+  Geometry g;
+  g.C = d->C;
+  g.HW = d->HW;
+  g.N = d->N;
+  g.M = static_cast<size_t>(d->N) * d->HW;
+  if (d->layout == MB_NHWC) {
+    g.vec = (d->C % 4 == 0) ? 4 : 1;
+    int groups = d->C / g.vec;
+    g.tx = pow2ceil(groups < kBlock ? groups : kBlock);
+    g.ty = kBlock / g.tx;
+    g.slabs = (groups + g.tx - 1) / g.tx;
+    size_t rows_per_cta_min = static_cast<size_t>(g.ty) * 8;
+    size_t want = (g.M + rows_per_cta_min - 1) / rows_per_cta_min;
+    size_t cap = static_cast<size_t>(kNumSMs) * 6 / g.slabs;
+    if (cap < 1) cap = 1;
+    g.S = static_cast<int>(want < cap ? want : cap);
+  } else {
+    g.vec = 1;
+    g.tx = g.ty = 0;
+    g.slabs = 1;
+    size_t want = (g.M + 4095) / 4096;
+    size_t cap = static_cast<size_t>(kNumSMs) * 8 / (d->C > 0 ? d->C : 1);
+    if (cap < 1) cap = 1;
+    g.S = static_cast<int>(want < cap ? want : cap);
+  }
+  if (g.S < 1) g.S = 1;
+  return g;
+}
+
+// workspace: partials [2][S][C] floats, then constants [2][C] floats
+size_t ws_floats(const Geometry& g) { return (2 * static_cast<size_t>(g.S) + 2) * g.C; }
+
+enum { kFwd = 0, kBwd = 1 };
+
+// ------------------------------------------------------------- NHWC reduce
+// MODE kFwd: a = x;          accumulates (x-K), (x-K)^2
+// MODE kBwd: a = dy, b = v;  accumulates dy, dy*(v-p0)*p1
+template <int MODE, int VEC>
+__global__ void __launch_bounds__(kBlock) bn_reduce_nhwc(const float* __restrict__ a,
+                                                         const float* __restrict__ b,
+                                                         const float* __restrict__ p0v,
+                                                         const float* __restrict__ p1v,
+                                                         int p1_is_gamma, float* __restrict__ ws,
+                                                         int C, size_t M, int S, int tx_n,
+                                                         int ty_n) {
+  extern __shared__ float sm[];  // [ty_n][tx_n][2*VEC]
+  const int tx = threadIdx.x % tx_n, ty = threadIdx.x / tx_n;
+  const int c0 = (blockIdx.y * tx_n + tx) * VEC;
+  const bool live = c0 < C;
+  float s1[VEC], s2[VEC], p0[VEC], p1[VEC];
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) {
+    s1[k] = s2[k] = 0.f;
+    p0[k] = 0.f;
+    p1[k] = 1.f;
+  }
+  if (live) {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+      if (MODE == kFwd) {
+        p0[k] = __ldg(a + c0 + k);  // shift K = first row of the channel
+      } else {
+        p0[k] = __ldg(p0v + c0 + k);
+        float t = __ldg(p1v + c0 + k);
+        p1[k] = p1_is_gamma ? 1.f / t : t;
+      }
+    }
+    const size_t rows_per = (M + S - 1) / S;
+    const size_t r0 = static_cast<size_t>(blockIdx.x) * rows_per;
+    size_t r1 = r0 + rows_per;
+    if (r1 > M) r1 = M;
+    size_t r = r0 + ty;
+    if (VEC == 4) {
+      // four rows in flight per thread
+      for (; r + 3 * static_cast<size_t>(ty_n) < r1; r += 4 * static_cast<size_t>(ty_n)) {
+        float4 u[4], w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const size_t off = (r + i * static_cast<size_t>(ty_n)) * C + c0;
+          u[i] = __ldcs(reinterpret_cast<const float4*>(a + off));
+          if (MODE == kBwd) w[i] = __ldcs(reinterpret_cast<const float4*>(b + off));
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float uu[4] = {u[i].x, u[i].y, u[i].z, u[i].w};
+          const float ww[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            if (MODE == kFwd) {
+              const float dlt = uu[k] - p0[k];
+              s1[k] += dlt;
+              s2[k] = fmaf(dlt, dlt, s2[k]);
+            } else {
+              s1[k] += uu[k];
+              s2[k] = fmaf(uu[k], (ww[k] - p0[k]) * p1[k], s2[k]);
+            }
+          }
+        }
+      }
+    }
+    for (; r < r1; r += ty_n) {
+      const size_t off = r * C + c0;
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        const float uu = __ldg(a + off + k);
+        if (MODE == kFwd) {
+          const float dlt = uu - p0[k];
+          s1[k] += dlt;
+          s2[k] = fmaf(dlt, dlt, s2[k]);
+        } else {
+          const float ww = __ldg(b + off + k);
+          s1[k] += uu;
+          s2[k] = fmaf(uu, (ww - p0[k]) * p1[k], s2[k]);
+        }
+      }
+    }
+  }
+  float* mine = sm + (static_cast<size_t>(ty) * tx_n + tx) * 2 * VEC;
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) {
+    mine[k] = s1[k];
+    mine[VEC + k] = s2[k];
+  }
+  __syncthreads();
+  if (ty == 0 && live) {
+    for (int j = 1; j < ty_n; ++j) {
+      const float* o = sm + (static_cast<size_t>(j) * tx_n + tx) * 2 * VEC;
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        s1[k] += o[k];
+        s2[k] += o[VEC + k];
+      }
+    }
+    float* w1 = ws + static_cast<size_t>(blockIdx.x) * C + c0;
+    float* w2 = ws + (static_cast<size_t>(S) + blockIdx.x) * C + c0;
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+      w1[k] = s1[k];
+      w2[k] = s2[k];
+    }
+  }
+}
+
+// ------------------------------------------------------------- NCHW reduce
+// grid (C, S); a chunk is a range of the channel's N*HW elements.
+template <int MODE>
+__global__ void __launch_bounds__(kBlock) bn_reduce_nchw(const float* __restrict__ a,
+                                                         const float* __restrict__ b,
+                                                         const float* __restrict__ p0v,
+                                                         const float* __restrict__ p1v,
+                                                         int p1_is_gamma, float* __restrict__ ws,
+                                                         int C, int HW, size_t M, int S) {
+  __shared__ float red[2][kBlock / 32];
+  const int c = blockIdx.x;
+  float p0, p1 = 1.f;
+  if (MODE == kFwd) {
+    p0 = __ldg(a + static_cast<size_t>(c) * HW);
+  } else {
+    p0 = __ldg(p0v + c);
+    float t = __ldg(p1v + c);
+    p1 = p1_is_gamma ? 1.f / t : t;
+  }
+  const size_t per = (M + S - 1) / S;
+  const size_t j0 = static_cast<size_t>(blockIdx.y) * per;
+  size_t j1 = j0 + per;
+  if (j1 > M) j1 = M;
+  float s1 = 0.f, s2 = 0.f;
+  for (size_t j = j0 + threadIdx.x; j < j1; j += kBlock) {
+    const size_t n = j / HW;
+    const size_t off = (n * C + c) * HW + (j - n * HW);
+    const float u = __ldg(a + off);
+    if (MODE == kFwd) {
+      const float dlt = u - p0;
+      s1 += dlt;
+      s2 = fmaf(dlt, dlt, s2);
+    } else {
+      const float w = __ldg(b + off);
+      s1 += u;
+      s2 = fmaf(u, (w - p0) * p1, s2);
+    }
+  }
+  s1 = warp_sum(s1);
+  s2 = warp_sum(s2);
+  if ((threadIdx.x & 31) == 0) {
+    red[0][threadIdx.x >> 5] = s1;
+    red[1][threadIdx.x >> 5] = s2;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < kBlock / 32; ++i) {
+      s1 += red[0][i];
+      s2 += red[1][i];
+    }
+    ws[static_cast<size_t>(blockIdx.y) * C + c] = s1;
+    ws[(static_cast<size_t>(S) + blockIdx.y) * C + c] = s2;
+  }
+}
+
+// ---------------------------------------------------------------- finalize
+// block (32 channels, 8 chunk stripes); fp64 accumulation of the partials.
+template <int MODE>
+__global__ void __launch_bounds__(256) bn_finalize(const float* __restrict__ ws_part,
+                                                   float* __restrict__ ws_const,
+                                                   const float* __restrict__ first_elems,
+                                                   size_t first_stride, int C, size_t M, int S,
+                                                   float eps, float momentum,
+                                                   float* __restrict__ running_mean,
+                                                   float* __restrict__ running_var,
+                                                   float* __restrict__ out0,
+                                                   float* __restrict__ out1) {
+  __shared__ double red[2][8][32];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + tx;
+  double s1 = 0.0, s2 = 0.0;
+  if (c < C) {
+    for (int s = ty; s < S; s += 8) {
+      s1 += static_cast<double>(ws_part[static_cast<size_t>(s) * C + c]);
+      s2 += static_cast<double>(ws_part[(static_cast<size_t>(S) + s) * C + c]);
+    }
+  }
+  red[0][ty][tx] = s1;
+  red[1][ty][tx] = s2;
+  __syncthreads();
+  if (ty == 0 && c < C) {
+    for (int j = 1; j < 8; ++j) {
+      s1 += red[0][j][tx];
+      s2 += red[1][j][tx];
+    }
+    const double m = static_cast<double>(M);
+    if (MODE == kFwd) {
+      const double K = static_cast<double>(first_elems[static_cast<size_t>(c) * first_stride]);
+      const double e1 = s1 / m;
+      double var = s2 / m - e1 * e1;
+      if (var < 0.0) var = 0.0;
+      const double mean = K + e1;
+      out0[c] = static_cast<float>(mean);                                   // save_mean
+      out1[c] = static_cast<float>(1.0 / sqrt(var + static_cast<double>(eps)));  // save_invstd
+      if (running_mean) running_mean[c] = (1.f - momentum) * running_mean[c] + momentum * static_cast<float>(mean);
+      if (running_var) {
+        const double unbiased = M > 1 ? var * m / (m - 1.0) : var;
+        running_var[c] = (1.f - momentum) * running_var[c] + momentum * static_cast<float>(unbiased);
+      }
+    } else {
+      out0[c] = static_cast<float>(s2);  // dgamma
+      out1[c] = static_cast<float>(s1);  // dbeta
+      ws_const[c] = static_cast<float>(s1 / m);
+      ws_const[C + c] = static_cast<float>(s2 / m);
+    }
+  }
+}
+
+// ------------------------------------------------------------------- sweeps
+// MODE kFwd: out = (a - mean)*(invstd*gamma) + beta
+// MODE kBwd: out = (a - xhat*k2 - k1)*(invstd*gamma),  a = dy, xhat = (b-p0)*p1
+struct SweepConst {
+  const float* gamma;
+  const float* beta;    // fwd
+  const float* mean;    // fwd
+  const float* invstd;
+  const float* p0v;     // bwd
+  const float* p1v;     // bwd
+  int p1_is_gamma;
+  const float* k12;     // bwd: [2][C]
+};
+
+template <int MODE>
+__device__ __forceinline__ void load_const(const SweepConst& k, int c, int C, float& q0, float& q1,
+                                           float& q2, float& q3, float& q4) {
+  if (MODE == kFwd) {
+    q0 = __ldg(k.mean + c);
+    q1 = __ldg(k.invstd + c) * __ldg(k.gamma + c);
+    q2 = __ldg(k.beta + c);
+    q3 = q4 = 0.f;
+  } else {
+    q0 = __ldg(k.p0v + c);
+    float t = __ldg(k.p1v + c);
+    q1 = k.p1_is_gamma ? 1.f / t : t;
+    q2 = __ldg(k.k12 + c);      // S1/M
+    q3 = __ldg(k.k12 + C + c);  // S2/M
+    q4 = __ldg(k.invstd + c) * __ldg(k.gamma + c);
+  }
+}
+
+template <int MODE>
+__device__ __forceinline__ float sweep1(float a, float b, float q0, float q1, float q2, float q3,
+                                        float q4) {
+  if (MODE == kFwd) return fmaf(a - q0, q1, q2);
+  const float xhat = (b - q0) * q1;
+  return (a - xhat * q3 - q2) * q4;
+}
+
+template <int MODE, int VEC>
+__global__ void __launch_bounds__(kBlock) bn_sweep_nhwc(const float* a, const float* b, float* out,
+                                                        SweepConst k, int C, size_t M, int tx_n,
+                                                        int ty_n) {
+  const int tx = threadIdx.x % tx_n, ty = threadIdx.x / tx_n;
+  const int c0 = (blockIdx.y * tx_n + tx) * VEC;
+  if (c0 >= C) return;
+  float q0[VEC], q1[VEC], q2[VEC], q3[VEC], q4[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) load_const<MODE>(k, c0 + i, C, q0[i], q1[i], q2[i], q3[i], q4[i]);
+  const size_t step = static_cast<size_t>(gridDim.x) * ty_n;
+  size_t r = static_cast<size_t>(blockIdx.x) * ty_n + ty;
+  if (VEC == 4) {
+    for (; r + 3 * step < M; r += 4 * step) {
+      float4 u[4], w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const size_t off = (r + i * step) * C + c0;
+        u[i] = *reinterpret_cast<const float4*>(a + off);
+        if (MODE == kBwd) w[i] = *reinterpret_cast<const float4*>(b + off);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float4 o;
+        o.x = sweep1<MODE>(u[i].x, w[i].x, q0[0], q1[0], q2[0], q3[0], q4[0]);
+        o.y = sweep1<MODE>(u[i].y, w[i].y, q0[1], q1[1], q2[1], q3[1], q4[1]);
+        o.z = sweep1<MODE>(u[i].z, w[i].z, q0[2], q1[2], q2[2], q3[2], q4[2]);
+        o.w = sweep1<MODE>(u[i].w, w[i].w, q0[3], q1[3], q2[3], q3[3], q4[3]);
+        *reinterpret_cast<float4*>(out + (r + i * step) * C + c0) = o;
+      }
+    }
+  }
+  for (; r < M; r += step) {
+    const size_t off = r * C + c0;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const float u = a[off + i];
+      const float w = MODE == kBwd ? b[off + i] : 0.f;
+      out[off + i] = sweep1<MODE>(u, w, q0[i], q1[i], q2[i], q3[i], q4[i]);
+    }
+  }
+}
+
+// grid (planes = N*C, chunks of HW)
+template <int MODE>
+__global__ void __launch_bounds__(kBlock) bn_sweep_nchw(const float* a, const float* b, float* out,
+                                                        SweepConst k, int C, int HW) {
+  const int c = blockIdx.x % C;
+  float q0, q1, q2, q3, q4;
+  load_const<MODE>(k, c, C, q0, q1, q2, q3, q4);
+  const size_t base = static_cast<size_t>(blockIdx.x) * HW;
+  for (int i = blockIdx.y * kBlock + threadIdx.x; i < HW; i += gridDim.y * kBlock) {
+    const float u = a[base + i];
+    const float w = MODE == kBwd ? b[base + i] : 0.f;
+    out[base + i] = sweep1<MODE>(u, w, q0, q1, q2, q3, q4);
+  }
+}
+
+int check(const char* who, const mb_bn_desc* d) {
+  if (!d) return fail(MB_ERR_INVALID_ARGUMENT, "%s: null descriptor", who);
+  if (d->N <= 0 || d->C <= 0 || d->HW <= 0)
+    return fail(MB_ERR_INVALID_ARGUMENT, "%s: bad extent N=%d C=%d HW=%d", who, d->N, d->C, d->HW);
+  if (d->layout != MB_NCHW && d->layout != MB_NHWC)
+    return fail(MB_ERR_INVALID_ARGUMENT, "%s: bad layout %d", who, d->layout);
+  return MB_OK;
+}
+
+template <int MODE>
+int run_reduce(const char* who, const mb_bn_desc* d, const Geometry& g, const float* a,
+               const float* b, const float* p0v, const float* p1v, int p1_is_gamma, float* ws,
+               cudaStream_t st) {
+  if (d->layout == MB_NHWC) {
+    dim3 grid(g.S, g.slabs);
+    const size_t smem = static_cast<size_t>(kBlock) * 2 * g.vec * sizeof(float);
+    if (g.vec == 4)
+      bn_reduce_nhwc<MODE, 4><<<grid, kBlock, smem, st>>>(a, b, p0v, p1v, p1_is_gamma, ws, g.C, g.M, g.S, g.tx, g.ty);
+    else
+      bn_reduce_nhwc<MODE, 1><<<grid, kBlock, smem, st>>>(a, b, p0v, p1v, p1_is_gamma, ws, g.C, g.M, g.S, g.tx, g.ty);
+  } else {
+    dim3 grid(g.C, g.S);
+    bn_reduce_nchw<MODE><<<grid, kBlock, 0, st>>>(a, b, p0v, p1v, p1_is_gamma, ws, g.C, g.HW, g.M, g.S);
+  }
+  return after_launch(who);
+}
+
+template <int MODE>
+int run_sweep(const char* who, const mb_bn_desc* d, const Geometry& g, const float* a,
+              const float* b, float* out, const SweepConst& k, cudaStream_t st) {
+  if (d->layout == MB_NHWC) {
+    size_t want = (g.M + static_cast<size_t>(g.ty) * 4 - 1) / (static_cast<size_t>(g.ty) * 4);
+    size_t cap = static_cast<size_t>(kNumSMs) * 8 / g.slabs;
+    if (cap < 1) cap = 1;
+    dim3 grid(static_cast<unsigned>(want < cap ? want : cap), g.slabs);
+    if (grid.x < 1) grid.x = 1;
+    if (g.vec == 4)
+      bn_sweep_nhwc<MODE, 4><<<grid, kBlock, 0, st>>>(a, b, out, k, g.C, g.M, g.tx, g.ty);
+    else
+      bn_sweep_nhwc<MODE, 1><<<grid, kBlock, 0, st>>>(a, b, out, k, g.C, g.M, g.tx, g.ty);
+  } else {
+    const size_t planes = static_cast<size_t>(g.N) * g.C;
+    if (planes > 0x7fffffffULL) return fail(MB_ERR_UNSUPPORTED, "%s: N*C too large", who);
+    int ychunks = (g.HW + kBlock * 4 - 1) / (kBlock * 4);
+    if (ychunks > 65535) ychunks = 65535;
+    dim3 grid(static_cast<unsigned>(planes), ychunks);
+    bn_sweep_nchw<MODE><<<grid, kBlock, 0, st>>>(a, b, out, k, g.C, g.HW);
+  }
+  return after_launch(who);
+}
+
+int check_alignment(const char* who, const mb_bn_desc* d, const void* p0, const void* p1,
+                    const void* p2) {
+  if (d->layout == MB_NHWC && d->C % 4 == 0 &&
+      !(aligned(p0, 16) && aligned(p1, 16) && aligned(p2, 16)))
+    return fail(MB_ERR_INVALID_ARGUMENT, "%s: activation pointers must be 16-byte aligned", who);
+  return MB_OK;
+}
+
+int bwd_common(const char* who, const float* dy, const float* v, const float* gamma,
+               const float* p0v, const float* p1v, int p1_is_gamma, const float* invstd, float* dx,
+               float* dgamma, float* dbeta, const mb_bn_desc* d, void* workspace,
+               size_t workspace_bytes, void* stream) {
+  int rc = check(who, d);
+  if (rc) return rc;
+  if (!dy || !v || !gamma || !p0v || !p1v || !invstd || !dx || !dgamma || !dbeta)
+    return fail(MB_ERR_INVALID_ARGUMENT, "%s: null pointer", who);
+  rc = check_alignment(who, d, dy, v, dx);
+  if (rc) return rc;
+  Geometry g = make_geometry(d);
+  if (!workspace || workspace_bytes < ws_floats(g) * sizeof(float))
+    return fail(MB_ERR_WORKSPACE, "%s: workspace of %zu bytes needed, %zu given", who,
+                ws_floats(g) * sizeof(float), workspace ? workspace_bytes : size_t(0));
+  float* ws = static_cast<float*>(workspace);
+  float* ws_const = ws + 2 * static_cast<size_t>(g.S) * g.C;
+  cudaStream_t st = as_stream(stream);
+  rc = run_reduce<kBwd>("bn_bwd_reduce", d, g, dy, v, p0v, p1v, p1_is_gamma, ws, st);
+  if (rc) return rc;
+  bn_finalize<kBwd><<<(g.C + 31) / 32, 256, 0, st>>>(ws, ws_const, nullptr, 0, g.C, g.M, g.S, 0.f,
+                                                    0.f, nullptr, nullptr, dgamma, dbeta);
+  rc = after_launch("bn_bwd_finalize");
+  if (rc) return rc;
+  SweepConst k{gamma, nullptr, nullptr, invstd, p0v, p1v, p1_is_gamma, ws_const};
+  return run_sweep<kBwd>("bn_bwd_sweep", d, g, dy, v, dx, k, st);
+}
+
+}  // namespace
+}  // namespace mb
+
+using namespace mb;
+
+extern "C" {
+
+size_t mb_bn_workspace_bytes(const mb_bn_desc* d) {
+  if (!d || d->N <= 0 || d->C <= 0 || d->HW <= 0) return 0;
+  return ws_floats(make_geometry(d)) * sizeof(float);
+}
+
+int mb_bn_fwd_train(const float* x, const float* gamma, const float* beta, float* running_mean,
+                    float* running_var, float* y, float* save_mean, float* save_invstd,
+                    const mb_bn_desc* d, void* workspace, size_t workspace_bytes, void* stream) {
+  const char* who = "mb_bn_fwd_train";
+  int rc = check(who, d);
+  if (rc) return rc;
+  if (!x || !gamma || !beta || !y || !save_mean || !save_invstd)
+    return fail(MB_ERR_INVALID_ARGUMENT, "%s: null pointer", who);
+  rc = check_alignment(who, d, x, y, y);
+  if (rc) return rc;
+  Geometry g = make_geometry(d);
+  if (!workspace || workspace_bytes < ws_floats(g) * sizeof(float))
+    return fail(MB_ERR_WORKSPACE, "%s: workspace of %zu bytes needed, %zu given", who,
+                ws_floats(g) * sizeof(float), workspace ? workspace_bytes : size_t(0));
+  float* ws = static_cast<float*>(workspace);
+  cudaStream_t st = as_stream(stream);
+  rc = run_reduce<kFwd>("bn_fwd_reduce", d, g, x, nullptr, nullptr, nullptr, 0, ws, st);
+  if (rc) return rc;
+  const size_t first_stride = d->layout == MB_NHWC ? 1 : static_cast<size_t>(d->HW);
+  bn_finalize<kFwd><<<(g.C + 31) / 32, 256, 0, st>>>(ws, nullptr, x, first_stride, g.C, g.M, g.S,
+                                                    d->eps, d->momentum, running_mean,
+                                                    running_var, save_mean, save_invstd);
+  rc = after_launch("bn_fwd_finalize");
+  if (rc) return rc;
+  SweepConst k{gamma, beta, save_mean, save_invstd, nullptr, nullptr, 0, nullptr};
+  return run_sweep<kFwd>("bn_fwd_sweep", d, g, x, nullptr, y, k, st);
+}
+
+int mb_bn_fwd_apply(const float* x, const float* gamma, const float* beta, const float* mean,
+                    const float* invstd, float* y, const mb_bn_desc* d, void* stream) {
+  const char* who = "mb_bn_fwd_apply";
+  int rc = check(who, d);
+  if (rc) return rc;
+  if (!x || !gamma || !beta || !mean || !invstd || !y)
+    return fail(MB_ERR_INVALID_ARGUMENT, "%s: null pointer", who);
+  rc = check_alignment(who, d, x, y, y);
+  if (rc) return rc;
+  Geometry g = make_geometry(d);
+  SweepConst k{gamma, beta, mean, invstd, nullptr, nullptr, 0, nullptr};
+  return run_sweep<kFwd>("bn_fwd_sweep", d, g, x, nullptr, y, k, as_stream(stream));
+}
+
+int mb_bn_bwd_from_output(const float* dy, const float* y, const float* gamma, const float* beta,
+                          const float* save_invstd, float* dx, float* dgamma, float* dbeta,
+                          const mb_bn_desc* d, void* workspace, size_t workspace_bytes,
+                          void* stream) {
+  return bwd_common("mb_bn_bwd_from_output", dy, y, gamma, beta, gamma, 1, save_invstd, dx, dgamma,
+                    dbeta, d, workspace, workspace_bytes, stream);
+}
+
+int mb_bn_bwd_from_input(const float* dy, const float* x, const float* gamma,
+                         const float* save_mean, const float* save_invstd, float* dx,
+                         float* dgamma, float* dbeta, const mb_bn_desc* d, void* workspace,
+                         size_t workspace_bytes, void* stream) {
+  return bwd_common("mb_bn_bwd_from_input", dy, x, gamma, save_mean, save_invstd, 0, save_invstd,
+                    dx, dgamma, dbeta, d, workspace, workspace_bytes, stream);
+}
+
+}  // extern "C"

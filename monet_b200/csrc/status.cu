@@ -1,0 +1,36 @@
+// Error reporting and launch accounting shared by every entry point.
+#include "common.cuh"
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+
+namespace {
+thread_local char g_error[512] = "";
+std::atomic<unsigned long long> g_launches{0};
+}  // namespace
+
+namespace mb {
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int after_launch(const char* kernel_name) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess)
+    return fail(MB_ERR_LAUNCH, "%s: launch failed: %s", kernel_name, cudaGetErrorString(e));
+  return MB_OK;
+}
+
+}  // namespace mb
+
+extern "C" {
+const char* mb_last_error(void) { return g_error; }
+int mb_abi_version(void) { return 1; }
+unsigned long long mb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+}

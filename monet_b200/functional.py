@@ -1,0 +1,437 @@
+"""Tensor-level wrappers over the C ABI: allocation (through PyTorch's caching
+allocator, so the reference's memory profiler sees every byte), layout detection,
+stream selection and argument checking.  CUDA tensors only: a CPU tensor raises.
+
+Layouts.  A logical N x C x H x W activation may be dense NCHW (``is_contiguous()``)
+or dense NHWC (``torch.channels_last``).  Element-wise kernels work on the physical
+buffer and keep the input's strides; layout-aware kernels (batch norm, pooling) get
+the layout flag.  Anything else is first made contiguous.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import MB_NCHW, MB_NHWC, BnDesc, PoolDesc, check, lib
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("monet_b200 operators run on CUDA tensors only (no CPU fallback)")
+        if t is not None and t.dtype not in (torch.float32, torch.uint8, torch.int64, torch.bool):
+            raise RuntimeError(f"monet_b200: unsupported dtype {t.dtype}")
+
+
+def is_nhwc(t: torch.Tensor) -> bool:
+    return (t.dim() == 4 and not t.is_contiguous()
+            and t.is_contiguous(memory_format=torch.channels_last))
+
+
+def dense(t: torch.Tensor) -> torch.Tensor:
+    """`t` itself if it is dense NCHW / NHWC, else a contiguous copy."""
+    if t.is_contiguous() or is_nhwc(t):
+        return t
+    return t.contiguous()
+
+
+def layout_of(t: torch.Tensor) -> int:
+    return MB_NHWC if is_nhwc(t) else MB_NCHW
+
+
+def like(t: torch.Tensor, other: torch.Tensor) -> torch.Tensor:
+    """`other` re-laid out, if needed, to share `t`'s physical element order."""
+    other = dense(other)
+    if other.dim() == 4 and t.dim() == 4 and layout_of(other) != layout_of(t):
+        fmt = torch.channels_last if is_nhwc(t) else torch.contiguous_format
+        other = other.contiguous(memory_format=fmt)
+    return other
+
+
+def _f32(t: torch.Tensor, name: str) -> None:
+    if t.dtype != torch.float32:
+        raise RuntimeError(f"monet_b200: {name} must be float32, got {t.dtype}")
+
+
+# --------------------------------------------------------------------------- ReLU
+
+def relu(x: torch.Tensor, inplace: bool = False) -> torch.Tensor:
+    _need_cuda(x); _f32(x, "x")
+    xd = dense(x)
+    y = xd if (inplace and xd is x) else torch.empty_like(xd)
+    check(lib().mb_relu_fwd(xd.data_ptr(), y.data_ptr(), xd.numel(), _stream()), "relu_fwd")
+    return y
+
+
+def relu_mask(x: torch.Tensor, inplace: bool = False):
+    """(relu(x), 1-bit mask of x > 0 in physical element order, MSB first)."""
+    _need_cuda(x); _f32(x, "x")
+    xd = dense(x)
+    y = xd if (inplace and xd is x) else torch.empty_like(xd)
+    n = xd.numel()
+    mask = torch.empty((n + 7) // 8, dtype=torch.uint8, device=x.device)
+    check(lib().mb_relu_fwd_mask(xd.data_ptr(), y.data_ptr(), mask.data_ptr(), n, _stream()),
+          "relu_fwd_mask")
+    return y, mask
+
+
+def relu_bwd_mask(dy: torch.Tensor, mask: torch.Tensor, inplace: bool = True) -> torch.Tensor:
+    _need_cuda(dy, mask); _f32(dy, "dy")
+    d = dense(dy)
+    n = d.numel()
+    if mask.dtype != torch.uint8 or mask.numel() != (n + 7) // 8:
+        raise RuntimeError("monet_b200: mask size does not match the gradient")
+    dx = d if inplace else torch.empty_like(d)
+    check(lib().mb_relu_bwd_mask(d.data_ptr(), mask.data_ptr(), dx.data_ptr(), n, _stream()),
+          "relu_bwd_mask")
+    return dx
+
+
+def relu_bwd_act(dy: torch.Tensor, act: torch.Tensor, threshold: float = 0.0,
+                 inplace: bool = True) -> torch.Tensor:
+    _need_cuda(dy, act); _f32(dy, "dy"); _f32(act, "act")
+    a = dense(act)
+    d = like(a, dy)
+    if d.shape != a.shape:
+        raise RuntimeError("monet_b200: gradient and activation shapes differ")
+    dx = d if inplace else torch.empty_like(d)
+    check(lib().mb_relu_bwd_act(d.data_ptr(), a.data_ptr(), float(threshold), dx.data_ptr(),
+                                d.numel(), _stream()), "relu_bwd_act")
+    return dx
+
+
+# ------------------------------------------------------------------------ packing
+
+def pack_bits(flags: torch.Tensor) -> torch.Tensor:
+    _need_cuda(flags)
+    src = flags.contiguous().view(-1)
+    src = src.view(torch.uint8) if src.dtype == torch.bool else src
+    n = src.numel()
+    out = torch.empty((n + 7) // 8, dtype=torch.uint8, device=flags.device)
+    check(lib().mb_pack_bits(src.data_ptr(), out.data_ptr(), n, _stream()), "pack_bits")
+    return out
+
+
+def unpack_bits(packed: torch.Tensor, n: int) -> torch.Tensor:
+    _need_cuda(packed)
+    out = torch.empty(n, dtype=torch.uint8, device=packed.device)
+    check(lib().mb_unpack_bits(packed.data_ptr(), out.data_ptr(), n, _stream()), "unpack_bits")
+    return out.view(torch.bool)
+
+
+def unpack_multiply(packed: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    return relu_bwd_mask(v, packed, inplace=False)
+
+
+def pack_nibbles(idx: torch.Tensor) -> torch.Tensor:
+    _need_cuda(idx)
+    src = idx.contiguous().view(-1)
+    n = src.numel()
+    out = torch.empty((n + 1) // 2, dtype=torch.uint8, device=idx.device)
+    check(lib().mb_pack_nibbles(src.data_ptr(), out.data_ptr(), n, _stream()), "pack_nibbles")
+    return out
+
+
+def unpack_nibbles(packed: torch.Tensor, n: int) -> torch.Tensor:
+    _need_cuda(packed)
+    out = torch.empty(n, dtype=torch.uint8, device=packed.device)
+    check(lib().mb_unpack_nibbles(packed.data_ptr(), out.data_ptr(), n, _stream()),
+          "unpack_nibbles")
+    return out
+
+
+# ----------------------------------------------------------------------- hardtanh
+
+def hardtanh(x: torch.Tensor, lo: float, hi: float, inplace: bool = False) -> torch.Tensor:
+    _need_cuda(x); _f32(x, "x")
+    xd = dense(x)
+    y = xd if (inplace and xd is x) else torch.empty_like(xd)
+    check(lib().mb_hardtanh_fwd(xd.data_ptr(), y.data_ptr(), float(lo), float(hi), xd.numel(),
+                                _stream()), "hardtanh_fwd")
+    return y
+
+
+def hardtanh_bwd(dy: torch.Tensor, act: torch.Tensor, lo: float, hi: float,
+                 inplace: bool = False) -> torch.Tensor:
+    _need_cuda(dy, act); _f32(dy, "dy"); _f32(act, "act")
+    a = dense(act)
+    d = like(a, dy)
+    dx = d if inplace else torch.empty_like(d)
+    check(lib().mb_hardtanh_bwd(d.data_ptr(), a.data_ptr(), float(lo), float(hi), dx.data_ptr(),
+                                d.numel(), _stream()), "hardtanh_bwd")
+    return dx
+
+
+# ---------------------------------------------------------------------------- add
+
+def add(a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0, inplace: bool = False):
+    _need_cuda(a, b); _f32(a, "a"); _f32(b, "b")
+    if a.shape != b.shape:
+        raise RuntimeError("monet_b200.add: broadcasting is not supported")
+    ad = dense(a)
+    bd = like(ad, b)
+    y = ad if (inplace and ad is a) else torch.empty_like(ad)
+    check(lib().mb_add_fwd(ad.data_ptr(), bd.data_ptr(), float(alpha), y.data_ptr(), ad.numel(),
+                           _stream()), "add_fwd")
+    return y
+
+
+def scale(x: torch.Tensor, alpha: float) -> torch.Tensor:
+    _need_cuda(x); _f32(x, "x")
+    xd = dense(x)
+    y = torch.empty_like(xd)
+    check(lib().mb_scale(xd.data_ptr(), float(alpha), y.data_ptr(), xd.numel(), _stream()),
+          "scale")
+    return y
+
+
+# ----------------------------------------------------------------------- max pool
+
+def _pair(v):
+    if isinstance(v, (list, tuple)):
+        return (int(v[0]), int(v[0])) if len(v) == 1 else (int(v[0]), int(v[1]))
+    return int(v), int(v)
+
+
+def pool_desc(shape, layout, kernel_size, stride, padding, dilation, ceil_mode) -> PoolDesc:
+    kh, kw = _pair(kernel_size)
+    sh, sw = _pair(stride) if stride not in (None, [], ()) else (kh, kw)
+    ph, pw = _pair(padding)
+    dh, dw = _pair(dilation)
+    N, Cc, H, W = (int(s) for s in shape)
+    L = lib()
+    P = L.mb_pool_out_size(H, kh, sh, ph, dh, int(bool(ceil_mode)))
+    Q = L.mb_pool_out_size(W, kw, sw, pw, dw, int(bool(ceil_mode)))
+    return PoolDesc(N, Cc, H, W, P, Q, kh, kw, sh, sw, ph, pw, dh, dw, layout)
+
+
+def _out_4d(x: torch.Tensor, N, Cc, P, Q, layout) -> torch.Tensor:
+    fmt = torch.channels_last if layout == MB_NHWC else torch.contiguous_format
+    return torch.empty((N, Cc, P, Q), dtype=x.dtype, device=x.device, memory_format=fmt)
+
+
+def maxpool2d(x: torch.Tensor, kernel_size, stride, padding, dilation, ceil_mode,
+              with_indices: bool = True):
+    """(y, packed 4-bit window-local argmax or None, descriptor)."""
+    _need_cuda(x); _f32(x, "x")
+    if x.dim() != 4:
+        raise RuntimeError("monet_b200.maxpool2d expects a 4-D tensor")
+    xd = dense(x)
+    d = pool_desc(xd.shape, layout_of(xd), kernel_size, stride, padding, dilation, ceil_mode)
+    if d.P <= 0 or d.Q <= 0:
+        raise RuntimeError("monet_b200.maxpool2d: empty output")
+    y = _out_4d(xd, d.N, d.C, d.P, d.Q, d.layout)
+    nib = None
+    if with_indices:
+        nib = torch.empty((y.numel() + 1) // 2, dtype=torch.uint8, device=x.device)
+    check(lib().mb_maxpool2d_fwd(xd.data_ptr(), y.data_ptr(), nib.data_ptr() if nib is not None else None,
+                                 C.byref(d), _stream()), "maxpool2d_fwd")
+    return y, nib, d
+
+
+def maxpool2d_bwd(dy: torch.Tensor, nibbles: torch.Tensor, d: PoolDesc) -> torch.Tensor:
+    _need_cuda(dy, nibbles); _f32(dy, "dy")
+    fmt = torch.channels_last if d.layout == MB_NHWC else torch.contiguous_format
+    dyd = dy.contiguous(memory_format=fmt)
+    if tuple(dyd.shape) != (d.N, d.C, d.P, d.Q):
+        raise RuntimeError("monet_b200.maxpool2d_bwd: gradient shape does not match the forward")
+    dx = _out_4d(dyd, d.N, d.C, d.H, d.W, d.layout)
+    check(lib().mb_maxpool2d_bwd(dyd.data_ptr(), nibbles.data_ptr(), dx.data_ptr(), C.byref(d),
+                                 _stream()), "maxpool2d_bwd")
+    return dx
+
+
+# --------------------------------------------------------------------- batch norm
+
+def bn_desc(x: torch.Tensor, eps: float, momentum: float) -> BnDesc:
+    if x.dim() < 2:
+        raise RuntimeError("monet_b200 batch norm expects at least 2 dimensions")
+    N, Cc = int(x.shape[0]), int(x.shape[1])
+    HW = 1
+    for s in x.shape[2:]:
+        HW *= int(s)
+    layout = MB_NHWC if (x.dim() == 4 and is_nhwc(x)) else MB_NCHW
+    return BnDesc(N, Cc, HW, layout, float(eps), float(momentum if momentum is not None else 0.1))
+
+
+def _bn_dense(x: torch.Tensor) -> torch.Tensor:
+    if x.dim() == 4:
+        return dense(x)
+    return x.contiguous()
+
+
+def _bn_workspace(d: BnDesc, device) -> torch.Tensor:
+    nbytes = lib().mb_bn_workspace_bytes(C.byref(d))
+    return torch.empty(nbytes, dtype=torch.uint8, device=device)
+
+
+def bn_fwd_train(x, gamma, beta, running_mean, running_var, momentum, eps, inplace=False):
+    """(y, save_mean, save_invstd); updates the running statistics in place."""
+    _need_cuda(x, gamma, beta, running_mean, running_var); _f32(x, "x")
+    xd = _bn_dense(x)
+    d = bn_desc(xd, eps, momentum)
+    y = xd if (inplace and xd is x) else torch.empty_like(xd)
+    save_mean = torch.empty(d.C, dtype=torch.float32, device=x.device)
+    save_invstd = torch.empty(d.C, dtype=torch.float32, device=x.device)
+    ws = _bn_workspace(d, x.device)
+    check(lib().mb_bn_fwd_train(
+        xd.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
+        running_mean.data_ptr() if running_mean is not None else None,
+        running_var.data_ptr() if running_var is not None else None,
+        y.data_ptr(), save_mean.data_ptr(), save_invstd.data_ptr(), C.byref(d),
+        ws.data_ptr(), ws.numel(), _stream()), "bn_fwd_train")
+    return y, save_mean, save_invstd
+
+
+def bn_fwd_apply(x, gamma, beta, mean, invstd, eps=1e-5, inplace=False):
+    _need_cuda(x, gamma, beta, mean, invstd); _f32(x, "x")
+    xd = _bn_dense(x)
+    d = bn_desc(xd, eps, 0.0)
+    y = xd if (inplace and xd is x) else torch.empty_like(xd)
+    check(lib().mb_bn_fwd_apply(xd.data_ptr(), gamma.data_ptr(), beta.data_ptr(), mean.data_ptr(),
+                                invstd.data_ptr(), y.data_ptr(), C.byref(d), _stream()),
+          "bn_fwd_apply")
+    return y
+
+
+def _bn_bwd(entry, dy, saved, gamma, p, save_invstd, inplace):
+    _need_cuda(dy, saved, gamma, p, save_invstd); _f32(dy, "dy"); _f32(saved, "saved activation")
+    sd = _bn_dense(saved)
+    dyd = like(sd, dy) if sd.dim() == 4 else dy.contiguous()
+    if dyd.shape != sd.shape:
+        raise RuntimeError("monet_b200 batch norm backward: gradient shape mismatch")
+    d = bn_desc(sd, 0.0, 0.0)
+    dx = dyd if (inplace and dyd is dy) else torch.empty_like(sd)
+    dgamma = torch.empty(d.C, dtype=torch.float32, device=dy.device)
+    dbeta = torch.empty(d.C, dtype=torch.float32, device=dy.device)
+    ws = _bn_workspace(d, dy.device)
+    fn = getattr(lib(), entry)
+    check(fn(dyd.data_ptr(), sd.data_ptr(), gamma.data_ptr(), p.data_ptr(),
+             save_invstd.data_ptr(), dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(),
+             C.byref(d), ws.data_ptr(), ws.numel(), _stream()), entry)
+    return dx, dgamma, dbeta
+
+
+def bn_bwd_from_output(dy, y, gamma, beta, save_invstd, inplace=False):
+    """(dx, dgamma, dbeta) from the stored output y; x is never needed."""
+    return _bn_bwd("mb_bn_bwd_from_output", dy, y, gamma, beta, save_invstd, inplace)
+
+
+def bn_bwd_from_input(dy, x, gamma, save_mean, save_invstd, inplace=False):
+    return _bn_bwd("mb_bn_bwd_from_input", dy, x, gamma, save_mean, save_invstd, inplace)
+
+
+# ------------------------------------------------------------------------ softmax
+
+def _split_dim(x: torch.Tensor, dim: int):
+    dim = dim % x.dim()
+    outer = 1
+    for s in x.shape[:dim]:
+        outer *= int(s)
+    inner = 1
+    for s in x.shape[dim + 1:]:
+        inner *= int(s)
+    return outer, int(x.shape[dim]), inner
+
+
+def softmax(x: torch.Tensor, dim: int, log: bool = False) -> torch.Tensor:
+    _need_cuda(x); _f32(x, "x")
+    xc = x.contiguous()
+    outer, classes, inner = _split_dim(xc, dim)
+    y = torch.empty_like(xc)
+    check(lib().mb_softmax_fwd(xc.data_ptr(), y.data_ptr(), outer, classes, inner, int(log),
+                               _stream()), "softmax_fwd")
+    return y
+
+
+def softmax_bwd(dy: torch.Tensor, y: torch.Tensor, dim: int, log: bool = False) -> torch.Tensor:
+    _need_cuda(dy, y); _f32(dy, "dy"); _f32(y, "y")
+    yc, dyc = y.contiguous(), dy.contiguous()
+    outer, classes, inner = _split_dim(yc, dim)
+    dx = torch.empty_like(yc)
+    check(lib().mb_softmax_bwd(dyc.data_ptr(), yc.data_ptr(), dx.data_ptr(), outer, classes,
+                               inner, int(log), _stream()), "softmax_bwd")
+    return dx
+
+
+def cross_entropy_fwd_bwd(logits: torch.Tensor, labels: torch.Tensor, grad_scale: float):
+    """Per-position losses and d(logits) = (softmax - onehot) * grad_scale in one pass.
+
+    `logits` is [N, classes] or [N, classes, d1, ...]; `labels` int64 of the matching shape.
+    For a mean-reduced loss pass grad_scale = 1 / labels.numel().
+    """
+    _need_cuda(logits, labels); _f32(logits, "logits")
+    if labels.dtype != torch.int64:
+        raise RuntimeError("monet_b200.cross_entropy: labels must be int64")
+    lc, lab = logits.contiguous(), labels.contiguous()
+    outer, classes, inner = _split_dim(lc, 1)
+    if lab.numel() != outer * inner:
+        raise RuntimeError("monet_b200.cross_entropy: label shape does not match the logits")
+    loss_rows = torch.empty(lab.shape, dtype=torch.float32, device=logits.device)
+    dlogits = torch.empty_like(lc)
+    check(lib().mb_softmax_ce_fwd_bwd(lc.data_ptr(), lab.data_ptr(), loss_rows.data_ptr(),
+                                      dlogits.data_ptr(), outer, classes, inner,
+                                      float(grad_scale), _stream()), "softmax_ce_fwd_bwd")
+    return loss_rows, dlogits
+
+
+# ----------------------------------------------------------------- layout / pooling
+
+def to_nhwc(x: torch.Tensor) -> torch.Tensor:
+    """A channels_last tensor with x's values (x itself if it already is one)."""
+    _need_cuda(x); _f32(x, "x")
+    if x.dim() != 4:
+        raise RuntimeError("monet_b200.to_nhwc expects a 4-D tensor")
+    if x.is_contiguous(memory_format=torch.channels_last):
+        return x
+    xc = x.contiguous()
+    N, Cc, H, W = (int(s) for s in xc.shape)
+    y = torch.empty((N, Cc, H, W), dtype=x.dtype, device=x.device,
+                    memory_format=torch.channels_last)
+    check(lib().mb_nchw_to_nhwc(xc.data_ptr(), y.data_ptr(), N, Cc, H, W, _stream()),
+          "nchw_to_nhwc")
+    return y
+
+
+def to_nchw(x: torch.Tensor) -> torch.Tensor:
+    _need_cuda(x); _f32(x, "x")
+    if x.dim() != 4:
+        raise RuntimeError("monet_b200.to_nchw expects a 4-D tensor")
+    if x.is_contiguous():
+        return x
+    xd = dense(x)
+    if not is_nhwc(xd):
+        return xd
+    N, Cc, H, W = (int(s) for s in xd.shape)
+    y = torch.empty((N, Cc, H, W), dtype=x.dtype, device=x.device)
+    check(lib().mb_nhwc_to_nchw(xd.data_ptr(), y.data_ptr(), N, Cc, H, W, _stream()),
+          "nhwc_to_nchw")
+    return y
+
+
+def global_avgpool(x: torch.Tensor) -> torch.Tensor:
+    _need_cuda(x); _f32(x, "x")
+    xd = dense(x)
+    N, Cc, H, W = (int(s) for s in xd.shape)
+    y = torch.empty((N, Cc, 1, 1), dtype=x.dtype, device=x.device)
+    check(lib().mb_global_avgpool_fwd(xd.data_ptr(), y.data_ptr(), N, Cc, H * W, layout_of(xd),
+                                      _stream()), "global_avgpool_fwd")
+    return y
+
+
+def global_avgpool_bwd(dy: torch.Tensor, shape, nhwc: bool) -> torch.Tensor:
+    _need_cuda(dy); _f32(dy, "dy")
+    N, Cc, H, W = (int(s) for s in shape)
+    dyc = dy.contiguous()
+    fmt = torch.channels_last if nhwc else torch.contiguous_format
+    dx = torch.empty((N, Cc, H, W), dtype=dy.dtype, device=dy.device, memory_format=fmt)
+    check(lib().mb_global_avgpool_bwd(dyc.data_ptr(), dx.data_ptr(), N, Cc, H * W,
+                                      MB_NHWC if nhwc else MB_NCHW, _stream()),
+          "global_avgpool_bwd")
+    return dx
