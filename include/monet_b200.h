@@ -181,6 +181,10 @@ int mb_softmax_ce_fwd_bwd(const float* logits, const int64_t* labels, float* los
 /* Physical NCHW -> NHWC (and back) of an N x C x H x W fp32 tensor.         */
 int mb_nchw_to_nhwc(const float* x, float* y, int N, int C, int H, int W, void* stream);
 int mb_nhwc_to_nchw(const float* x, float* y, int N, int C, int H, int W, void* stream);
+/* NCHW -> NHWC with the channels zero-padded to Cp (multiple of 4): prepares a
+ * few-channel network input (C = 3) for the tensor-core convolution.         */
+int mb_nchw_to_nhwc_pad(const float* x, float* y, int N, int C, int H, int W, int Cp,
+                        void* stream);
 /* Global average pool (adaptive_avg_pool2d to 1x1; funcs.py:7-21):
  * y[N,C] = mean over H*W; backward dx = dy / HW broadcast, written fully
  * (no zeros tensor as in funcs.py:20).                                       */
@@ -188,6 +192,56 @@ int mb_global_avgpool_fwd(const float* x, float* y, int N, int C, int HW, int la
                           void* stream);
 int mb_global_avgpool_bwd(const float* dy, float* dx, int N, int C, int HW, int layout,
                           void* stream);
+
+/* ---- convolution on the tensor cores ------------------------------------ */
+/* (replaces conv.cpp:299-731: cudnn_convolution, cudnn_convolution_backward_input,
+ *  cudnn_convolution_backward_weight and the n_*_algos counters; conv.py:260-341)
+ *
+ * Layout: activations NHWC fp32 (torch.channels_last), filters [K][R][S][C]
+ * fp32 (a channels_last weight tensor), gradients alike.  Arithmetic: TF32
+ * operands, fp32 accumulation (tcgen05.mma kind::tf32).  C and K must be
+ * multiples of 4, groups == 1, stride <= 2.
+ *
+ * "Variants" take the place of the reference's cuDNN algorithm index: each
+ * pass has mb_conv_num_variants(pass) of them, numbered from 0, that trade
+ * workspace for speed or determinism; mb_conv_workspace_bytes() says how much
+ * scratch a variant needs so the MONeT solver can budget for it.  A variant
+ * that cannot run a shape returns MB_ERR_UNSUPPORTED (the profiler records it
+ * as infeasible, meminfo.py:52-55).                                          */
+
+typedef struct {
+  int N, C, H, W;        /* input  N x C x H x W                             */
+  int K, R, S;           /* filter K x C x R x S                             */
+  int P, Q;              /* output N x K x P x Q                             */
+  int stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
+  int groups;
+} mb_conv_desc;
+
+enum { MB_CONV_FPROP = 0, MB_CONV_DGRAD = 1, MB_CONV_WGRAD = 2 };
+
+/* conv.cpp:729-731 (n_fwd_algos / n_bwd_ip_algos / n_bwd_wt_algos).         */
+int mb_conv_num_variants(int pass);
+size_t mb_conv_workspace_bytes(int pass, int variant, const mb_conv_desc* d);
+/* y = conv(x, w) (+ bias[K] when non-NULL, fused; conv.py:284-285 adds it in
+ * a second kernel).  Variant 0: implicit GEMM, no workspace.                 */
+int mb_conv2d_fprop(const float* x, const float* w, const float* bias, float* y,
+                    const mb_conv_desc* d, int variant, void* workspace, size_t workspace_bytes,
+                    void* stream);
+/* dx = backward-data.  Variant 0: implicit GEMM over dy with the filter
+ * transposed to [C][R][S][K] in the workspace (K*R*S*C*4 bytes).             */
+int mb_conv2d_dgrad(const float* dy, const float* w, float* dx, const mb_conv_desc* d, int variant,
+                    void* workspace, size_t workspace_bytes, void* stream);
+/* dw = backward-filter, dbias[K] = sum of dy when non-NULL (conv.py:313-314).
+ * Variant 0: split reduction combined with red.global.add (no workspace,
+ * summation order not fixed).  Variant 1: per-split partials in the
+ * workspace and a deterministic reduction.                                   */
+int mb_conv2d_wgrad(const float* x, const float* dy, float* dw, float* dbias,
+                    const mb_conv_desc* d, int variant, void* workspace, size_t workspace_bytes,
+                    void* stream);
+/* Status word of the tensor-core kernels: 0 = healthy, otherwise the code of
+ * the first pipeline wait that timed out (the kernel then gave up cleanly).
+ * Synchronises the device.  reset != 0 clears it.                            */
+int mb_conv_device_status(int reset);
 
 #ifdef __cplusplus
 }

@@ -36,6 +36,9 @@ class ConvDesc(C.Structure):
                  "pad_w", "dil_h", "dil_w", "groups")]
 
 
+MB_CONV_FPROP, MB_CONV_DGRAD, MB_CONV_WGRAD = 0, 1, 2
+
+
 # name -> (restype, argtypes); every symbol of include/monet_b200.h
 PROTOTYPES = {
     "mb_last_error": (C.c_char_p, []),
@@ -67,6 +70,13 @@ PROTOTYPES = {
     "mb_softmax_ce_fwd_bwd": (C.c_int, [c_f, c_f, c_f, c_f, c_sz, C.c_int, c_sz, C.c_float, c_f]),
     "mb_nchw_to_nhwc": (C.c_int, [c_f, c_f, C.c_int, C.c_int, C.c_int, C.c_int, c_f]),
     "mb_nhwc_to_nchw": (C.c_int, [c_f, c_f, C.c_int, C.c_int, C.c_int, C.c_int, c_f]),
+    "mb_nchw_to_nhwc_pad": (C.c_int, [c_f, c_f, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, c_f]),
+    "mb_conv_num_variants": (C.c_int, [C.c_int]),
+    "mb_conv_workspace_bytes": (c_sz, [C.c_int, C.c_int, C.POINTER(ConvDesc)]),
+    "mb_conv2d_fprop": (C.c_int, [c_f, c_f, c_f, c_f, C.POINTER(ConvDesc), C.c_int, c_f, c_sz, c_f]),
+    "mb_conv2d_dgrad": (C.c_int, [c_f, c_f, c_f, C.POINTER(ConvDesc), C.c_int, c_f, c_sz, c_f]),
+    "mb_conv2d_wgrad": (C.c_int, [c_f, c_f, c_f, c_f, C.POINTER(ConvDesc), C.c_int, c_f, c_sz, c_f]),
+    "mb_conv_device_status": (C.c_int, [C.c_int]),
     "mb_global_avgpool_fwd": (C.c_int, [c_f, c_f, C.c_int, C.c_int, C.c_int, C.c_int, c_f]),
     "mb_global_avgpool_bwd": (C.c_int, [c_f, c_f, C.c_int, C.c_int, C.c_int, C.c_int, c_f]),
 }

@@ -1,0 +1,526 @@
+// Host side of the tensor-core convolutions: validation, tiling, tap tables,
+// tensor maps, workspace accounting and the three C-ABI passes.
+//
+// Data layout.  Activations are NHWC fp32 (torch.channels_last), filters are
+// [K][R][S][C] fp32 (a channels_last weight), gradients alike.  C and K must be
+// multiples of 4 (16-byte TMA strides).
+//
+// Passes
+//   fprop  y = conv(x, w) + bias        implicit GEMM, A = x, B = w
+//   dgrad  dx = conv^T(dy, w)           implicit GEMM per stride phase, A = dy,
+//                                       B = filter transposed to [C][R][S][K]
+//                                       in the workspace
+//   wgrad  dw = x (*) dy, db = sum dy   see conv_wgrad.cuh
+#include "conv_gemm.cuh"
+#include "conv_wgrad.cuh"
+
+#include <cstring>
+#include <mutex>
+
+namespace mb {
+
+
+namespace {
+
+// ------------------------------------------------------- driver entry point
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// fp32 tensor map, 128-byte swizzle, zero fill.  dims/strides innermost first;
+// strides[i] is the byte stride of dims[i+1].
+int encode_map(const char* who, CUtensorMap* m, const void* base, int rank, const cuuint64_t* dims,
+               const cuuint64_t* strides, const cuuint32_t* box, CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(MB_ERR_LAUNCH, "%s: cuTensorMapEncodeTiled is not available", who);
+  cuuint32_t ones[5] = {1, 1, 1, 1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, rank, const_cast<void*>(base), dims, strides,
+                  box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(MB_ERR_INVALID_ARGUMENT,
+                "%s: tensor map rejected (CUresult %d; rank %d dims %llu %llu %llu %llu box %u %u %u %u)",
+                who, static_cast<int>(r), rank, (unsigned long long)dims[0],
+                (unsigned long long)dims[1], (unsigned long long)(rank > 2 ? dims[2] : 0),
+                (unsigned long long)(rank > 3 ? dims[3] : 0), box[0], box[1], rank > 2 ? box[2] : 0,
+                rank > 3 ? box[3] : 0);
+  return MB_OK;
+}
+
+// NHWC activation view {C, Wv, Hv, Nv} with byte strides of w / h / n.
+int encode_act(const char* who, CUtensorMap* m, const float* base, int C, long long Wv, long long Hv,
+               long long Nv, long long sw_b, long long sh_b, long long sn_b, int bw, int bh, int bn,
+               CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+  cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)Wv, (cuuint64_t)Hv, (cuuint64_t)Nv};
+  cuuint64_t strides[3] = {(cuuint64_t)sw_b, (cuuint64_t)sh_b, (cuuint64_t)sn_b};
+  cuuint32_t box[4] = {(cuuint32_t)kChunkK, (cuuint32_t)bw, (cuuint32_t)bh, (cuuint32_t)bn};
+  return encode_map(who, m, base, 4, dims, strides, box, swizzle);
+}
+
+// Filter view {Cin, taps, Kout} of a [Kout][taps][Cin] array; box {32, 1, rows}.
+int encode_filter(const char* who, CUtensorMap* m, const float* base, int Cin, int taps, int Kout,
+                  int rows) {
+  cuuint64_t dims[3] = {(cuuint64_t)Cin, (cuuint64_t)taps, (cuuint64_t)Kout};
+  cuuint64_t strides[2] = {(cuuint64_t)Cin * 4, (cuuint64_t)Cin * taps * 4};
+  cuuint32_t box[3] = {(cuuint32_t)kChunkK, 1, (cuuint32_t)rows};
+  return encode_map(who, m, base, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+// ------------------------------------------------------------------- tiling
+struct TileShape { int bw, bh, bn; };
+
+// Pixels per tile along w/h/n with bw*bh*bn <= 128, maximising the fraction
+// of MMA rows that land on real output pixels.
+TileShape pick_tile(int N, int P, int Q) {
+  TileShape best{1, 1, 1};
+  double best_u = -1.0;
+  const int wsplit = (Q + kTileM - 1) / kTileM;
+  const int bw = (Q + wsplit - 1) / wsplit;
+  for (int bh = 1; bh <= P && bw * bh <= kTileM; ++bh) {
+    int bn = 1;
+    if (bh == P) {
+      bn = kTileM / (bw * bh);
+      if (bn > N) bn = N;
+      if (bn < 1) bn = 1;
+    }
+    const double tiles = static_cast<double>((Q + bw - 1) / bw) * ((P + bh - 1) / bh) * ((N + bn - 1) / bn);
+    const double u = static_cast<double>(N) * P * Q / (tiles * kTileM);
+    if (u > best_u + 1e-9) {
+      best_u = u;
+      best = TileShape{bw, bh, bn};
+    }
+  }
+  return best;
+}
+
+int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+// Tile width along N and pipeline depth for `kout` output channels.
+void pick_bn_stages(int kout, long long m_tiles, int* BN, int* stages, size_t* smem) {
+  int bn = round_up(kout < 256 ? kout : 256, 16);
+  // prefer more, narrower tiles when the wide ones would leave SMs idle in the last wave
+  auto eff = [&](int b) {
+    const double tiles = static_cast<double>(m_tiles) * ((kout + b - 1) / b);
+    const double waves = (tiles + kNumSMs - 1) / kNumSMs;
+    return tiles / (static_cast<double>(static_cast<long long>(waves)) * kNumSMs);
+  };
+  while (bn > 64 && bn % 32 == 0 && eff(bn / 2) > eff(bn) * 1.15) bn /= 2;
+  const size_t stage = kAStageBytes + static_cast<size_t>(bn) * 128;
+  int st = static_cast<int>((220 * 1024 - 2048) / stage);
+  if (st > 8) st = 8;
+  if (st < 2) st = 2;
+  *BN = bn;
+  *stages = st;
+  *smem = 512 + 1024 + stage * st;
+}
+
+struct GemmLaunch {
+  CUtensorMap a[4];
+  CUtensorMap b;
+  GemmParams p;
+  size_t smem;
+  int grid;
+};
+
+int launch_gemm(const char* who, GemmLaunch& L, cudaStream_t st) {
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(conv_gemm_kmajor, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  });
+  if (attr_err != cudaSuccess)
+    return fail(MB_ERR_LAUNCH, "%s: cannot raise the shared-memory limit: %s", who, cudaGetErrorString(attr_err));
+  conv_gemm_kmajor<<<L.grid, 192, L.smem, st>>>(L.a[0], L.a[1], L.a[2], L.a[3], L.b, L.p);
+  return after_launch(who);
+}
+
+int floordiv(int a, int b) { return (a >= 0) ? a / b : -((-a + b - 1) / b); }
+int posmod(int a, int b) { return a - floordiv(a, b) * b; }
+
+int validate(const char* who, const mb_conv_desc* d) {
+  if (!d) return fail(MB_ERR_INVALID_ARGUMENT, "%s: null descriptor", who);
+  if (d->N <= 0 || d->C <= 0 || d->H <= 0 || d->W <= 0 || d->K <= 0 || d->R <= 0 || d->S <= 0)
+    return fail(MB_ERR_INVALID_ARGUMENT, "%s: bad extent", who);
+  if (d->stride_h <= 0 || d->stride_w <= 0 || d->dil_h <= 0 || d->dil_w <= 0 || d->pad_h < 0 || d->pad_w < 0)
+    return fail(MB_ERR_INVALID_ARGUMENT, "%s: bad stride / dilation / padding", who);
+  const int P = (d->H + 2 * d->pad_h - d->dil_h * (d->R - 1) - 1) / d->stride_h + 1;
+  const int Q = (d->W + 2 * d->pad_w - d->dil_w * (d->S - 1) - 1) / d->stride_w + 1;
+  if (P <= 0 || Q <= 0 || P != d->P || Q != d->Q)
+    return fail(MB_ERR_INVALID_ARGUMENT, "%s: output extent %dx%d does not match the geometry (%dx%d)",
+                who, d->P, d->Q, P, Q);
+  if (d->groups != 1)
+    return fail(MB_ERR_UNSUPPORTED, "%s: groups=%d (grouped convolution runs the depthwise kernels)", who, d->groups);
+  if (d->C % 4 || d->K % 4)
+    return fail(MB_ERR_UNSUPPORTED, "%s: C=%d and K=%d must be multiples of 4", who, d->C, d->K);
+  if (d->R * d->S > kMaxTaps)
+    return fail(MB_ERR_UNSUPPORTED, "%s: %dx%d filter has more than %d taps", who, d->R, d->S, kMaxTaps);
+  if (d->stride_h > 2 || d->stride_w > 2)
+    return fail(MB_ERR_UNSUPPORTED, "%s: stride above 2", who);
+  return MB_OK;
+}
+
+bool is_pointwise(const mb_conv_desc* d) {
+  return d->R == 1 && d->S == 1 && d->stride_h == 1 && d->stride_w == 1 && d->pad_h == 0 && d->pad_w == 0;
+}
+
+__global__ void __launch_bounds__(256) transpose_filter(const float* __restrict__ w,
+                                                        float* __restrict__ wt, int K, int T, int C) {
+  // wt[c][t][k] = w[k][t][c]
+  const size_t total = static_cast<size_t>(K) * T * C;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const int k = static_cast<int>(i % K);
+    const size_t r = i / K;
+    const int t = static_cast<int>(r % T);
+    const int c = static_cast<int>(r / T);
+    wt[i] = __ldg(w + (static_cast<size_t>(k) * T + t) * C + c);
+  }
+}
+
+}  // namespace
+}  // namespace mb
+
+namespace mb {
+
+int wgrad_run(const char* who, const float* x, const float* dy, float* dw, float* dbias,
+              const mb_conv_desc* d, int variant, void* workspace, size_t workspace_bytes,
+              cudaStream_t st) {
+  const CUtensorMapSwizzle kWg = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;   // MN-major TF32 operands
+  wg::Plan pl;
+  if (!wg::make_plan(d, variant, &pl))
+    return fail(MB_ERR_UNSUPPORTED, "%s: geometry not supported by the tensor-core kernel", who);
+  WgradParams& p = pl.p;
+  const size_t dw_elems = static_cast<size_t>(d->K) * d->R * d->S * d->C;
+  int rc;
+  if (variant == 0) {
+    if (cudaMemsetAsync(dw, 0, dw_elems * sizeof(float), st) != cudaSuccess)
+      return fail(MB_ERR_LAUNCH, "%s: memset failed", who);
+    p.out = dw;
+    p.split_stride = 0;
+  } else {
+    const size_t need = static_cast<size_t>(p.splits) * dw_elems * sizeof(float);
+    if (!workspace || workspace_bytes < need || !aligned(workspace, 16))
+      return fail(MB_ERR_WORKSPACE, "%s: workspace of %zu bytes needed, %zu given", who, need,
+                  workspace ? workspace_bytes : size_t(0));
+    if (p.ntaps < p.T && cudaMemsetAsync(workspace, 0, need, st) != cudaSuccess)
+      return fail(MB_ERR_LAUNCH, "%s: memset failed", who);
+    p.out = static_cast<float*>(workspace);
+    p.split_stride = static_cast<long long>(dw_elems);
+  }
+  CUtensorMap mdy, mx[4];
+  const long long K4 = static_cast<long long>(d->K) * 4, C4 = static_cast<long long>(d->C) * 4;
+  if (pl.flat) {
+    const long long pixels = static_cast<long long>(d->N) * d->P * d->Q;
+    rc = encode_act(who, &mdy, dy, d->K, pixels, 1, 1, K4, K4 * pixels, K4 * pixels, p.bw, 1, 1, kWg);
+    if (rc) return rc;
+    rc = encode_act(who, &mx[0], x, d->C, pixels, 1, 1, C4, C4 * pixels, C4 * pixels, p.bw, 1, 1, kWg);
+    if (rc) return rc;
+    mx[1] = mx[2] = mx[3] = mx[0];
+  } else {
+    rc = encode_act(who, &mdy, dy, d->K, d->Q, d->P, d->N, K4, K4 * d->Q, K4 * d->Q * d->P, p.bw,
+                    p.bh, p.bn, kWg);
+    if (rc) return rc;
+    int first = -1;
+    for (int mi = 0; mi < d->stride_h * d->stride_w; ++mi) {
+      if (!pl.map_used[mi]) continue;
+      const int a = mi / d->stride_w, b = mi % d->stride_w;
+      const long long Wv = (d->W - b + d->stride_w - 1) / d->stride_w;
+      const long long Hv = (d->H - a + d->stride_h - 1) / d->stride_h;
+      rc = encode_act(who, &mx[mi], x + (static_cast<long long>(a) * d->W + b) * d->C, d->C, Wv, Hv,
+                      d->N, C4 * d->stride_w, C4 * d->W * d->stride_h, C4 * d->W * d->H, p.bw, p.bh,
+                      p.bn, kWg);
+      if (rc) return rc;
+      if (first < 0) first = mi;
+    }
+    for (int mi = 0; mi < 4; ++mi)
+      if (mi >= d->stride_h * d->stride_w || !pl.map_used[mi]) mx[mi] = mx[first];
+  }
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(conv_wgrad_tcgen05, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  });
+  if (attr_err != cudaSuccess)
+    return fail(MB_ERR_LAUNCH, "%s: cannot raise the shared-memory limit: %s", who, cudaGetErrorString(attr_err));
+  conv_wgrad_tcgen05<<<pl.grid, 192, pl.smem, st>>>(mdy, mx[0], mx[1], mx[2], mx[3], p);
+  rc = after_launch("conv_wgrad_tcgen05");
+  if (rc) return rc;
+  if (variant == 1) {
+    wgrad_reduce_splits<<<grid_for(dw_elems, 256, 8), 256, 0, st>>>(static_cast<const float*>(workspace), dw, dw_elems, p.splits);
+    rc = after_launch("conv_wgrad_reduce");
+    if (rc) return rc;
+  }
+  if (dbias) {
+    if (cudaMemsetAsync(dbias, 0, static_cast<size_t>(d->K) * sizeof(float), st) != cudaSuccess)
+      return fail(MB_ERR_LAUNCH, "%s: memset failed", who);
+    const size_t pixels = static_cast<size_t>(d->N) * d->P * d->Q;
+    int chunks = static_cast<int>((pixels + 2047) / 2048);
+    const int cap = 4 * kNumSMs / ((d->K + 31) / 32) + 1;
+    if (chunks > cap) chunks = cap;
+    dim3 grid((d->K + 31) / 32, chunks);
+    bias_grad_kernel<<<grid, 256, 0, st>>>(dy, dbias, pixels, d->K);
+    rc = after_launch("conv_bias_grad");
+    if (rc) return rc;
+  }
+  return MB_OK;
+}
+
+}  // namespace mb
+
+using namespace mb;
+
+extern "C" {
+
+int mb_conv_num_variants(int pass) {
+  switch (pass) {
+    case MB_CONV_FPROP: return 1;
+    case MB_CONV_DGRAD: return 1;
+    case MB_CONV_WGRAD: return 2;
+    default: return 0;
+  }
+}
+
+size_t mb_conv_workspace_bytes(int pass, int variant, const mb_conv_desc* d) {
+  if (!d || variant < 0 || variant >= mb_conv_num_variants(pass)) return 0;
+  if (pass == MB_CONV_DGRAD) return static_cast<size_t>(d->K) * d->R * d->S * d->C * sizeof(float);
+  if (pass == MB_CONV_WGRAD) return wgrad_workspace_bytes(d, variant);
+  return 0;
+}
+
+int mb_conv_device_status(int reset) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_conv_status, sizeof(int)) != cudaSuccess) return -1;
+  if (reset && v != 0) {
+    int z = 0;
+    cudaMemcpyToSymbol(g_conv_status, &z, sizeof(int));
+  }
+  return v;
+}
+
+int mb_conv2d_fprop(const float* x, const float* w, const float* bias, float* y,
+                    const mb_conv_desc* d, int variant, void* workspace, size_t workspace_bytes,
+                    void* stream) {
+  const char* who = "mb_conv2d_fprop";
+  int rc = validate(who, d);
+  if (rc) return rc;
+  if (variant < 0 || variant >= mb_conv_num_variants(MB_CONV_FPROP))
+    return fail(MB_ERR_UNSUPPORTED, "%s: no variant %d", who, variant);
+  if (!x || !w || !y) return fail(MB_ERR_INVALID_ARGUMENT, "%s: null pointer", who);
+  if (!aligned(x, 16) || !aligned(w, 16) || !aligned(y, 16) || !aligned(bias, 16))
+    return fail(MB_ERR_INVALID_ARGUMENT, "%s: pointers must be 16-byte aligned", who);
+  (void)workspace; (void)workspace_bytes;
+
+  GemmLaunch L;
+  std::memset(&L.p, 0, sizeof(L.p));
+  GemmParams& p = L.p;
+  p.out = y;
+  p.bias = bias;
+  p.Kout = d->K;
+  p.kchunks = (d->C + kChunkK - 1) / kChunkK;
+  const long long C4 = static_cast<long long>(d->C) * 4;
+  TileShape ts;
+  if (is_pointwise(d)) {
+    const long long pixels = static_cast<long long>(d->N) * d->H * d->W;
+    if (pixels > 0x7fffffffLL) return fail(MB_ERR_UNSUPPORTED, "%s: more than 2^31 pixels", who);
+    ts = TileShape{kTileM, 1, 1};
+    p.Nimg = 1; p.P = 1; p.Q = static_cast<int>(pixels);
+    p.out_sn = 0; p.out_sh = 0; p.out_sw = d->K;
+    rc = encode_act(who, &L.a[0], x, d->C, pixels, 1, 1, C4, C4 * pixels, C4 * pixels, ts.bw, 1, 1);
+    if (rc) return rc;
+    L.a[1] = L.a[2] = L.a[3] = L.a[0];
+    p.num_taps = 1;
+    p.taps.dh[0] = p.taps.dw[0] = 0;
+    p.taps.map[0] = 0;
+    p.taps.btap[0] = 0;
+  } else {
+    ts = pick_tile(d->N, d->P, d->Q);
+    p.Nimg = d->N; p.P = d->P; p.Q = d->Q;
+    p.out_sw = d->K;
+    p.out_sh = static_cast<long long>(d->Q) * d->K;
+    p.out_sn = p.out_sh * d->P;
+    bool have[4] = {false, false, false, false};
+    int nt = 0;
+    for (int r = 0; r < d->R; ++r) {
+      const int oh = r * d->dil_h - d->pad_h;
+      const int a = posmod(oh, d->stride_h), dh = (oh - a) / d->stride_h;
+      for (int s = 0; s < d->S; ++s) {
+        const int ow = s * d->dil_w - d->pad_w;
+        const int b = posmod(ow, d->stride_w), dw = (ow - b) / d->stride_w;
+        if (a >= d->H || b >= d->W) continue;   // this phase of the input is empty
+        const int mi = a * d->stride_w + b;
+        have[mi] = true;
+        p.taps.dh[nt] = static_cast<short>(dh);
+        p.taps.dw[nt] = static_cast<short>(dw);
+        p.taps.map[nt] = static_cast<unsigned char>(mi);
+        p.taps.btap[nt] = static_cast<unsigned char>(r * d->S + s);
+        ++nt;
+      }
+    }
+    p.num_taps = nt;
+    int first = -1;
+    for (int mi = 0; mi < d->stride_h * d->stride_w; ++mi) {
+      if (!have[mi]) continue;
+      const int a = mi / d->stride_w, b = mi % d->stride_w;
+      const long long Wv = (d->W - b + d->stride_w - 1) / d->stride_w;
+      const long long Hv = (d->H - a + d->stride_h - 1) / d->stride_h;
+      rc = encode_act(who, &L.a[mi], x + (static_cast<long long>(a) * d->W + b) * d->C, d->C, Wv, Hv,
+                      d->N, C4 * d->stride_w, C4 * d->W * d->stride_h, C4 * d->W * d->H, ts.bw, ts.bh,
+                      ts.bn);
+      if (rc) return rc;
+      if (first < 0) first = mi;
+    }
+    if (first < 0) return fail(MB_ERR_INVALID_ARGUMENT, "%s: no filter tap touches the input", who);
+    for (int mi = 0; mi < 4; ++mi)
+      if (mi >= d->stride_h * d->stride_w || !have[mi]) L.a[mi] = L.a[first];
+  }
+  p.bw = ts.bw; p.bh = ts.bh; p.bn = ts.bn;
+  p.tiles_w = (p.Q + ts.bw - 1) / ts.bw;
+  p.tiles_h = (p.P + ts.bh - 1) / ts.bh;
+  const long long tiles_n = (p.Nimg + ts.bn - 1) / ts.bn;
+  const long long m_tiles = static_cast<long long>(p.tiles_w) * p.tiles_h * tiles_n;
+  pick_bn_stages(d->K, m_tiles, &p.BN, &p.stages, &L.smem);
+  p.tiles_c = (d->K + p.BN - 1) / p.BN;
+  const long long tiles = m_tiles * p.tiles_c;
+  if (tiles > 0x7fffffffLL) return fail(MB_ERR_UNSUPPORTED, "%s: too many tiles", who);
+  p.num_tiles = static_cast<int>(tiles);
+  rc = encode_filter(who, &L.b, w, d->C, d->R * d->S, d->K, p.BN);
+  if (rc) return rc;
+  L.grid = p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs;
+  return launch_gemm("conv_fprop_tcgen05", L, as_stream(stream));
+}
+
+int mb_conv2d_dgrad(const float* dy, const float* w, float* dx, const mb_conv_desc* d, int variant,
+                    void* workspace, size_t workspace_bytes, void* stream) {
+  const char* who = "mb_conv2d_dgrad";
+  int rc = validate(who, d);
+  if (rc) return rc;
+  if (variant < 0 || variant >= mb_conv_num_variants(MB_CONV_DGRAD))
+    return fail(MB_ERR_UNSUPPORTED, "%s: no variant %d", who, variant);
+  if (!dy || !w || !dx) return fail(MB_ERR_INVALID_ARGUMENT, "%s: null pointer", who);
+  if (!aligned(dy, 16) || !aligned(w, 16) || !aligned(dx, 16))
+    return fail(MB_ERR_INVALID_ARGUMENT, "%s: pointers must be 16-byte aligned", who);
+  const size_t need = mb_conv_workspace_bytes(MB_CONV_DGRAD, variant, d);
+  if (!workspace || workspace_bytes < need || !aligned(workspace, 16))
+    return fail(MB_ERR_WORKSPACE, "%s: workspace of %zu bytes needed, %zu given", who, need,
+                workspace ? workspace_bytes : size_t(0));
+  cudaStream_t st = as_stream(stream);
+  const int T = d->R * d->S;
+  float* wt = static_cast<float*>(workspace);   // [C][R*S][K]
+  {
+    const size_t total = static_cast<size_t>(d->K) * T * d->C;
+    transpose_filter<<<grid_for(total, 256, 8), 256, 0, st>>>(w, wt, d->K, T, d->C);
+    rc = after_launch("conv_transpose_filter");
+    if (rc) return rc;
+  }
+  const long long K4 = static_cast<long long>(d->K) * 4;
+  const int sh = d->stride_h, sw = d->stride_w;
+  // a phase of dx that no filter tap reaches is zero: clear dx first if there is one
+  bool any_empty = false;
+  for (int a = 0; a < sh && a < d->H; ++a)
+    for (int b = 0; b < sw && b < d->W; ++b) {
+      int cnt = 0;
+      for (int r = 0; r < d->R; ++r)
+        for (int s = 0; s < d->S; ++s)
+          if (!posmod(a + d->pad_h - r * d->dil_h, sh) && !posmod(b + d->pad_w - s * d->dil_w, sw)) ++cnt;
+      if (!cnt) any_empty = true;
+    }
+  if (any_empty &&
+      cudaMemsetAsync(dx, 0, static_cast<size_t>(d->N) * d->H * d->W * d->C * sizeof(float), st) != cudaSuccess)
+    return fail(MB_ERR_LAUNCH, "%s: memset failed", who);
+  for (int a = 0; a < sh; ++a) {
+    for (int b = 0; b < sw; ++b) {
+      if (a >= d->H || b >= d->W) continue;
+      GemmLaunch L;
+      std::memset(&L.p, 0, sizeof(L.p));
+      GemmParams& p = L.p;
+      int nt = 0;
+      // dx[h = i*sh + a] takes dy[(h + pad - r*dil) / sh] for the taps where that is exact
+      for (int r = 0; r < d->R; ++r) {
+        const int oh = a + d->pad_h - r * d->dil_h;
+        if (posmod(oh, sh)) continue;
+        for (int s = 0; s < d->S; ++s) {
+          const int ow = b + d->pad_w - s * d->dil_w;
+          if (posmod(ow, sw)) continue;
+          p.taps.dh[nt] = static_cast<short>(floordiv(oh, sh));
+          p.taps.dw[nt] = static_cast<short>(floordiv(ow, sw));
+          p.taps.map[nt] = 0;
+          p.taps.btap[nt] = static_cast<unsigned char>(r * d->S + s);
+          ++nt;
+        }
+      }
+      const int Hv = (d->H - a + sh - 1) / sh, Wv = (d->W - b + sw - 1) / sw;
+      if (nt == 0) continue;
+      p.num_taps = nt;
+      p.out = dx + (static_cast<long long>(a) * d->W + b) * d->C;
+      p.bias = nullptr;
+      p.Kout = d->C;
+      p.kchunks = (d->K + kChunkK - 1) / kChunkK;
+      TileShape ts;
+      const bool flat = is_pointwise(d);
+      if (flat) {
+        const long long pixels = static_cast<long long>(d->N) * d->H * d->W;
+        if (pixels > 0x7fffffffLL) return fail(MB_ERR_UNSUPPORTED, "%s: more than 2^31 pixels", who);
+        ts = TileShape{kTileM, 1, 1};
+        p.Nimg = 1; p.P = 1; p.Q = static_cast<int>(pixels);
+        p.out_sw = d->C;
+        rc = encode_act(who, &L.a[0], dy, d->K, pixels, 1, 1, K4, K4 * pixels, K4 * pixels, ts.bw, 1, 1);
+      } else {
+        ts = pick_tile(d->N, Hv, Wv);
+        p.Nimg = d->N; p.P = Hv; p.Q = Wv;
+        p.out_sw = static_cast<long long>(sw) * d->C;
+        p.out_sh = static_cast<long long>(sh) * d->W * d->C;
+        p.out_sn = static_cast<long long>(d->H) * d->W * d->C;
+        rc = encode_act(who, &L.a[0], dy, d->K, d->Q, d->P, d->N, K4, K4 * d->Q, K4 * d->Q * d->P,
+                        ts.bw, ts.bh, ts.bn);
+      }
+      if (rc) return rc;
+      L.a[1] = L.a[2] = L.a[3] = L.a[0];
+      p.bw = ts.bw; p.bh = ts.bh; p.bn = ts.bn;
+      p.tiles_w = (p.Q + ts.bw - 1) / ts.bw;
+      p.tiles_h = (p.P + ts.bh - 1) / ts.bh;
+      const long long tiles_n = (p.Nimg + ts.bn - 1) / ts.bn;
+      const long long m_tiles = static_cast<long long>(p.tiles_w) * p.tiles_h * tiles_n;
+      pick_bn_stages(d->C, m_tiles, &p.BN, &p.stages, &L.smem);
+      p.tiles_c = (d->C + p.BN - 1) / p.BN;
+      const long long tiles = m_tiles * p.tiles_c;
+      if (tiles > 0x7fffffffLL) return fail(MB_ERR_UNSUPPORTED, "%s: too many tiles", who);
+      p.num_tiles = static_cast<int>(tiles);
+      rc = encode_filter(who, &L.b, wt, d->K, T, d->C, p.BN);
+      if (rc) return rc;
+      L.grid = p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs;
+      rc = launch_gemm("conv_dgrad_tcgen05", L, st);
+      if (rc) return rc;
+    }
+  }
+  return MB_OK;
+}
+
+int mb_conv2d_wgrad(const float* x, const float* dy, float* dw, float* dbias,
+                    const mb_conv_desc* d, int variant, void* workspace, size_t workspace_bytes,
+                    void* stream) {
+  const char* who = "mb_conv2d_wgrad";
+  int rc = validate(who, d);
+  if (rc) return rc;
+  if (variant < 0 || variant >= mb_conv_num_variants(MB_CONV_WGRAD))
+    return fail(MB_ERR_UNSUPPORTED, "%s: no variant %d", who, variant);
+  if (!x || !dy || !dw) return fail(MB_ERR_INVALID_ARGUMENT, "%s: null pointer", who);
+  if (!aligned(x, 16) || !aligned(dy, 16) || !aligned(dw, 16))
+    return fail(MB_ERR_INVALID_ARGUMENT, "%s: pointers must be 16-byte aligned", who);
+  return wgrad_run(who, x, dy, dw, dbias, d, variant, workspace, workspace_bytes, as_stream(stream));
+}
+
+}  // extern "C"

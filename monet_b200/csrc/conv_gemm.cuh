@@ -1,0 +1,276 @@
+// Implicit-GEMM convolution on the 5th-generation tensor cores (tcgen05, TF32
+// inputs, fp32 accumulation in tensor memory), operands fetched by TMA.
+//
+//   D[pixel, out_channel] = sum over taps t, channel chunks kc of
+//                           A_t[pixel, 32 ch] * B_t[out_channel, 32 ch]^T
+//
+// A is an NHWC activation seen through up to four 4-D tensor maps (one per
+// stride phase); a tap is (map, dh, dw, filter tap) and its A tile is the TMA
+// box {32 channels, bw, bh, bn pixels} at {kc*32, q0+dw, p0+dh, n0}: halo and
+// padding come from TMA's out-of-bounds zero fill, so there is no im2col
+// buffer and no per-element index arithmetic.  B is a [out_channel][tap][ch]
+// filter.  Forward convolution and backward-data are both instances of this
+// kernel (backward-data uses the gradient as A and the transposed filter).
+//
+// Persistent CTAs (one per SM), 192 threads, three roles:
+//   warp 4   TMA producer: fills a ring of `stages` {A,B} slots
+//   warp 5   MMA issuer  : one thread issues tcgen05.mma (M=128, N=BN, K=8),
+//                          commits free the slots and publish the accumulator
+//   warps 0-3 epilogue   : tcgen05.ld of a double-buffered accumulator, bias,
+//                          128-byte-per-thread stores, overlapped with the
+//                          next tile's main loop
+// Every mbarrier wait is bounded; on a time-out the CTA records a status code
+// in g_conv_status, frees its tensor memory and exits.
+#pragma once
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace mb {
+
+constexpr int kMaxTaps = 64;
+constexpr int kTileM = 128;
+constexpr int kChunkK = 32;                     // fp32 per 128-byte swizzle row
+constexpr int kAStageBytes = kTileM * 128;      // 16 KiB
+
+struct Taps {
+  short dh[kMaxTaps];
+  short dw[kMaxTaps];
+  unsigned char map[kMaxTaps];
+  unsigned char btap[kMaxTaps];
+};
+
+struct GemmParams {
+  float* out;
+  const float* bias;            // may be null
+  long long out_sn, out_sh, out_sw;   // element strides of the output pixel grid
+  int Nimg, P, Q;               // output pixel grid
+  int bn, bh, bw;               // pixels per tile along n / h / w
+  int tiles_h, tiles_w, tiles_c;
+  int num_tiles;
+  int Kout;                     // GEMM N extent (output channels)
+  int BN;                       // tile width along N (multiple of 16, <= 256)
+  int kchunks;                  // ceil(input channels / 32)
+  int num_taps;
+  int stages;
+  Taps taps;
+};
+
+// Status word written by kernels that gave up waiting (0 = healthy).
+static __device__ int g_conv_status = 0;
+
+namespace detail {
+
+struct Ring {
+  int stage;
+  uint32_t phase;
+  int stages;
+  __device__ __forceinline__ void advance() {
+    if (++stage == stages) {
+      stage = 0;
+      phase ^= 1u;
+    }
+  }
+};
+
+}  // namespace detail
+
+__global__ void __launch_bounds__(192, 1)
+conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUtensorMap mapA1,
+                 const __grid_constant__ CUtensorMap mapA2, const __grid_constant__ CUtensorMap mapA3,
+                 const __grid_constant__ CUtensorMap mapB, const __grid_constant__ GemmParams p) {
+  using namespace sm100;
+  extern __shared__ uint8_t smem_raw[];
+  // control block first, then 1024-byte aligned operand slots
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw);          // [stages]
+  uint64_t* empty = full + 16;                                      // [stages]
+  uint64_t* acc_full = empty + 16;                                  // [2]
+  uint64_t* acc_empty = acc_full + 2;                               // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t slots0 = (smem_u32(smem_raw) + 512u + 1023u) & ~1023u;
+  const uint32_t b_stage_bytes = static_cast<uint32_t>(p.BN) * 128u;
+  const uint32_t stage_bytes = kAStageBytes + b_stage_bytes;
+  uint8_t* slots_ptr = smem_raw + (slots0 - smem_u32(smem_raw));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // two accumulators of BN columns; the epilogue reads whole 32-column groups, so the
+  // allocation must also cover the round-up of the second accumulator's last group
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < static_cast<uint32_t>(p.BN + (p.BN + 31) / 32 * 32)) tmem_cols <<= 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 128);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int box_rows = p.bn * p.bh * p.bw;
+  const uint32_t tx_bytes = static_cast<uint32_t>(box_rows) * 128u + b_stage_bytes;
+  const int kblocks = p.num_taps * p.kchunks;
+
+  auto decode = [&](int tile, int& c0, int& q0, int& p0, int& n0) {
+    const int ct = tile % p.tiles_c;
+    int r = tile / p.tiles_c;
+    const int wt = r % p.tiles_w;
+    r /= p.tiles_w;
+    const int ht = r % p.tiles_h;
+    const int nt = r / p.tiles_h;
+    c0 = ct * p.BN;
+    q0 = wt * p.bw;
+    p0 = ht * p.bh;
+    n0 = nt * p.bn;
+  };
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      prefetch_tensormap(&mapA0);
+      prefetch_tensormap(&mapB);
+      detail::Ring ring{0, 0u, p.stages};
+      uint32_t armed[16];   // per slot: 0 = never armed, else 1 + parity of the last arming
+      for (int s = 0; s < 16; ++s) armed[s] = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+        int c0, q0, p0, n0;
+        decode(tile, c0, q0, p0, n0);
+        for (int t = 0; ok && t < p.num_taps; ++t) {
+          const int mi = p.taps.map[t];
+          const CUtensorMap* ma = mi == 0 ? &mapA0 : mi == 1 ? &mapA1 : mi == 2 ? &mapA2 : &mapA3;
+          const int cw = q0 + p.taps.dw[t], ch = p0 + p.taps.dh[t], bt = p.taps.btap[t];
+          for (int kc = 0; kc < p.kchunks; ++kc) {
+            if (!mbar_wait(&empty[ring.stage], ring.phase ^ 1u, abort_flag)) {
+              ok = false;
+              break;
+            }
+            uint8_t* slot = slots_ptr + static_cast<size_t>(ring.stage) * stage_bytes;
+            mbar_arrive_expect_tx(&full[ring.stage], tx_bytes);
+            armed[ring.stage] = 1u + ring.phase;
+            tma_load_4d(ma, slot, &full[ring.stage], kc * kChunkK, cw, ch, n0);
+            tma_load_3d(&mapB, slot + kAStageBytes, &full[ring.stage], kc * kChunkK, bt, c0);
+            ring.advance();
+          }
+        }
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        atomicCAS(&g_conv_status, 0, 1);
+        // copies already issued still write this CTA's shared memory: give each armed
+        // slot a bounded time to complete before the CTA is allowed to exit
+        for (int s = 0; s < p.stages; ++s) {
+          if (!armed[s]) continue;
+          const long long t0 = clock64();
+          while (!mbar_try_wait(&full[s], armed[s] - 1u) && clock64() - t0 < 20000000LL) {
+          }
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = idesc_tf32(kTileM, p.BN, 0, 0);
+      detail::Ring ring{0, 0u, p.stages};
+      bool ok = true;
+      int it = 0;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1u;
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * p.BN);
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&full[ring.stage], ring.phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = slots0 + static_cast<uint32_t>(ring.stage) * stage_bytes;
+          const uint64_t da = smem_desc_sw128(a_addr, 16, 1024);
+          const uint64_t db = smem_desc_sw128(a_addr + kAStageBytes, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)   // 4 x K=8 per 32-channel chunk, 32 bytes apart
+            mma_tf32(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          mma_commit(&empty[ring.stage]);
+          ring.advance();
+        }
+        if (ok) mma_commit(&acc_full[acc]);
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        atomicCAS(&g_conv_status, 0, 2);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    bool ok = true;
+    int it = 0;
+    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1u;
+      int c0, q0, p0, n0;
+      decode(tile, c0, q0, p0, n0);
+      const int m = warp * 32 + lane;
+      const int wi = m % p.bw, hi = (m / p.bw) % p.bh, ni = m / (p.bw * p.bh);
+      const bool valid = m < box_rows && (n0 + ni) < p.Nimg && (p0 + hi) < p.P && (q0 + wi) < p.Q;
+      float* orow = p.out + (n0 + ni) * p.out_sn + (p0 + hi) * p.out_sh + (q0 + wi) * p.out_sw + c0;
+      // the whole warp must agree before the warp-collective tensor-memory loads
+      const bool got = mbar_wait(&acc_full[acc], acc_phase, abort_flag);
+      if (!__all_sync(0xffffffffu, got)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) +
+                             static_cast<uint32_t>(acc * p.BN);
+      for (int col = 0; col < p.BN && c0 + col < p.Kout; col += 32) {
+        float v[32];
+        tmem_ld32(t_row + col, v);
+        tmem_ld_wait();
+        if (valid) {
+          // columns of this tile that exist: bounded by the tile width and by Kout
+          const int left = min(p.Kout - (c0 + col), p.BN - col);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (j * 4 < left) {
+              float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              if (p.bias) {
+                const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + col + 4 * j));
+                o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
+              }
+              *reinterpret_cast<float4*>(orow + col + 4 * j) = o;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[acc]);
+    }
+    if (!ok && lane == 0) {
+      *abort_flag = 1;
+      atomicCAS(&g_conv_status, 0, 3);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem_base, tmem_cols);
+}
+
+}  // namespace mb

@@ -1,0 +1,379 @@
+// Backward-weight convolution on tcgen05: dw[k][tap][c] = sum over output
+// pixels of dy[pixel][k] * x[pixel shifted by the tap][c].
+//
+// The reduction runs over PIXELS, so both operands are "MN-major" for the MMA:
+// a TMA box {32 channels, pixels...} lands in shared memory as rows of one
+// pixel x 32 channels (128 bytes).  For 32-bit MN-major operands the MMA only
+// accepts the 128-byte swizzle with a 32-byte base, so the wgrad tensor maps
+// use SWIZZLE_128B_ATOM_32B; four pixel rows form a 512-byte atom and one
+// K = 8 step consumes two of them.
+//
+//   A  = dy tile : up to four boxes of 32 output channels (M = 128)
+//   B_u          : one box of 32 input channels of x, shifted by the filter
+//                  tap of "unit" u = (tap, 32-channel chunk); N = 32
+//   D_u          : 128 x 32 fp32 accumulator in tensor-memory columns 32u..
+//
+// One CTA owns a work item (tile of 128 output channels, group of up to U
+// units, range of pixel tiles) and keeps all U accumulators in tensor memory,
+// so the dy tile is loaded once and reused by every unit of the group.  The
+// pixel range is a split of the reduction; partial results are combined either
+// with red.global.add (variant 0, dw zeroed first) or through a workspace of
+// per-split partials and a deterministic reduction kernel (variant 1).
+//
+// Pixel boxes always hold a multiple of 8 rows, and rows outside the image are
+// zero-filled by TMA in dy, so padding rows contribute nothing.
+#pragma once
+#include "conv_gemm.cuh"
+
+namespace mb {
+
+constexpr int kWgMaxUnits = 12;     // accumulators (32 columns each) per CTA
+
+struct WgradParams {
+  float* out;               // dw, or the partial-sum workspace
+  long long split_stride;   // elements between the partials of two splits (0: atomics into dw)
+  int K, C, T;              // output channels, input channels, filter taps R*S
+  int ntaps;                // taps that touch the input at all
+  int cchunks;              // ceil(C / 32)
+  int units, units_per_group, groups;
+  int k_tiles, splits;
+  int bw, bh, bn, rows;     // pixel box, rows = bw*bh*bn (multiple of 8)
+  int tiles_w, tiles_h;
+  int pix_tiles;            // total pixel tiles
+  int stages;
+  int use_atomics;
+  Taps taps;
+};
+
+__global__ void __launch_bounds__(192, 1)
+conv_wgrad_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_constant__ CUtensorMap mapX0,
+                   const __grid_constant__ CUtensorMap mapX1, const __grid_constant__ CUtensorMap mapX2,
+                   const __grid_constant__ CUtensorMap mapX3, const __grid_constant__ WgradParams p) {
+  using namespace sm100;
+  extern __shared__ uint8_t smem_raw[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw);
+  uint64_t* empty = full + 16;
+  uint64_t* acc_full = empty + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t slots0 = (smem_u32(smem_raw) + 512u + 1023u) & ~1023u;
+  uint8_t* slots_ptr = smem_raw + (slots0 - smem_u32(smem_raw));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // work item
+  int wi = blockIdx.x;
+  const int split = wi % p.splits;
+  wi /= p.splits;
+  const int group = wi % p.groups;
+  const int kt = wi / p.groups;
+  const int k0 = kt * kTileM;
+  const int u0 = group * p.units_per_group;
+  const int nu = (p.units - u0) < p.units_per_group ? (p.units - u0) : p.units_per_group;
+  int ka = (p.K - k0 + 31) / 32;          // boxes of 32 output channels that exist
+  if (ka > 4) ka = 4;
+  const int per = (p.pix_tiles + p.splits - 1) / p.splits;
+  const int t_begin = split * per;
+  const int t_end = (t_begin + per) < p.pix_tiles ? (t_begin + per) : p.pix_tiles;
+  const int n_iter = t_end > t_begin ? t_end - t_begin : 0;
+
+  const uint32_t box_bytes = static_cast<uint32_t>(p.rows) * 128u;
+  const uint32_t a_bytes = 4u * box_bytes;                 // slot layout is fixed: 4 A boxes
+  const uint32_t stage_bytes = a_bytes + static_cast<uint32_t>(p.units_per_group) * box_bytes;
+  const uint32_t tx_bytes = static_cast<uint32_t>(ka + nu) * box_bytes;
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < 32u * p.units_per_group) tmem_cols <<= 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(&acc_full[0], 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    if (lane == 0 && n_iter > 0) {
+      prefetch_tensormap(&mapDy);
+      prefetch_tensormap(&mapX0);
+      detail::Ring ring{0, 0u, p.stages};
+      uint32_t armed[16];
+      for (int s = 0; s < 16; ++s) armed[s] = 0;
+      bool ok = true;
+      for (int t = t_begin; ok && t < t_end; ++t) {
+        const int wt = t % p.tiles_w;
+        int r = t / p.tiles_w;
+        const int ht = r % p.tiles_h;
+        const int nt = r / p.tiles_h;
+        const int q0 = wt * p.bw, p0 = ht * p.bh, n0 = nt * p.bn;
+        if (!mbar_wait(&empty[ring.stage], ring.phase ^ 1u, abort_flag)) {
+          ok = false;
+          break;
+        }
+        uint8_t* slot = slots_ptr + static_cast<size_t>(ring.stage) * stage_bytes;
+        mbar_arrive_expect_tx(&full[ring.stage], tx_bytes);
+        armed[ring.stage] = 1u + ring.phase;
+        for (int j = 0; j < ka; ++j)
+          tma_load_4d(&mapDy, slot + j * box_bytes, &full[ring.stage], k0 + 32 * j, q0, p0, n0);
+        for (int u = 0; u < nu; ++u) {
+          const int unit = u0 + u;
+          const int cc = unit / p.ntaps, ti = unit - cc * p.ntaps;
+          const int mi = p.taps.map[ti];
+          const CUtensorMap* mx = mi == 0 ? &mapX0 : mi == 1 ? &mapX1 : mi == 2 ? &mapX2 : &mapX3;
+          tma_load_4d(mx, slot + a_bytes + u * box_bytes, &full[ring.stage], cc * 32,
+                      q0 + p.taps.dw[ti], p0 + p.taps.dh[ti], n0);
+        }
+        ring.advance();
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        atomicCAS(&g_conv_status, 0, 11);
+        for (int s = 0; s < p.stages; ++s) {
+          if (!armed[s]) continue;
+          const long long t0 = clock64();
+          while (!mbar_try_wait(&full[s], armed[s] - 1u) && clock64() - t0 < 20000000LL) {
+          }
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0 && n_iter > 0) {
+      const uint32_t idesc = idesc_tf32(kTileM, 32, 1, 1);
+      detail::Ring ring{0, 0u, p.stages};
+      bool ok = true;
+      const int ksteps = p.rows / 8;
+      for (int it = 0; it < n_iter; ++it) {
+        if (!mbar_wait(&full[ring.stage], ring.phase, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t a_addr = slots0 + static_cast<uint32_t>(ring.stage) * stage_bytes;
+        // A: 32-channel groups are box_bytes apart (LBO), 4-pixel atoms 512 bytes apart (SBO)
+        const uint64_t da = smem_desc(a_addr, box_bytes, 512, kSwizzle128BBase32B);
+        for (int u = 0; u < nu; ++u) {
+          const uint64_t db = smem_desc(a_addr + a_bytes + u * box_bytes, box_bytes, 512, kSwizzle128BBase32B);
+          const uint32_t d_tmem = tmem_base + 32u * u;
+          for (int k = 0; k < ksteps; ++k)   // 8 pixels = 1024 bytes (two atoms) per step
+            mma_tf32(d_tmem, da + 64u * k, db + 64u * k, idesc, (it | k) != 0 ? 1u : 0u);
+        }
+        mma_commit(&empty[ring.stage]);
+        ring.advance();
+      }
+      if (ok) {
+        mma_commit(&acc_full[0]);
+      } else {
+        *abort_flag = 1;
+        atomicCAS(&g_conv_status, 0, 12);
+      }
+    }
+  } else if (n_iter > 0 || !p.use_atomics) {
+    // epilogue: thread = output channel row, 32 input channels per unit
+    bool got = n_iter > 0 ? mbar_wait(&acc_full[0], 0, abort_flag) : true;
+    got = __all_sync(0xffffffffu, got);
+    if (got) {
+      tc_fence_after();
+      const int k = k0 + warp * 32 + lane;
+      float* base = p.out + static_cast<long long>(split) * p.split_stride;
+      for (int u = 0; u < nu; ++u) {
+        const int unit = u0 + u;
+        const int cc = unit / p.ntaps, ti = unit - cc * p.ntaps;
+        float v[32];
+        if (n_iter > 0) {
+          tmem_ld32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + 32u * u, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        }
+        if (k < p.K) {
+          float* dst = base + (static_cast<long long>(k) * p.T + p.taps.btap[ti]) * p.C + cc * 32;
+          const int left = p.C - cc * 32;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (4 * j < left) {
+              if (p.use_atomics) {
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * j),
+                             "f"(v[4 * j]), "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
+                             : "memory");
+              } else {
+                *reinterpret_cast<float4*>(dst + 4 * j) =
+                    make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              }
+            }
+          }
+        }
+      }
+    } else if (lane == 0) {
+      *abort_flag = 1;
+      atomicCAS(&g_conv_status, 0, 13);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem_base, tmem_cols);
+}
+
+// out[i] = sum over splits of part[s][i]; also used for the bias gradient.
+__global__ void __launch_bounds__(256) wgrad_reduce_splits(const float* __restrict__ part,
+                                                           float* __restrict__ out, size_t n,
+                                                           int splits) {
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    float s = 0.f;
+    for (int j = 0; j < splits; ++j) s += __ldg(part + static_cast<size_t>(j) * n + i);
+    out[i] = s;
+  }
+}
+
+// db[k] = sum over pixels of dy[pixel][k]; dy is [pixels][K].  grid = (K/32 column
+// groups, row chunks); partial sums are combined with atomics into a zeroed db.
+__global__ void __launch_bounds__(256) bias_grad_kernel(const float* __restrict__ dy,
+                                                        float* __restrict__ db, size_t pixels,
+                                                        int K) {
+  __shared__ float red[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int k = blockIdx.x * 32 + tx;
+  const size_t per = (pixels + gridDim.y - 1) / gridDim.y;
+  const size_t r0 = blockIdx.y * per;
+  const size_t r1 = (r0 + per) < pixels ? (r0 + per) : pixels;
+  float s = 0.f;
+  if (k < K)
+    for (size_t r = r0 + ty; r < r1; r += 8) s += __ldg(dy + r * K + k);
+  red[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && k < K) {
+    for (int j = 1; j < 8; ++j) s += red[j][tx];
+    atomicAdd(db + k, s);
+  }
+}
+
+namespace wg {
+
+struct Plan {
+  WgradParams p;
+  size_t smem;
+  int grid;
+  int map_used[4];
+  bool flat;
+};
+
+inline int posmod_(int a, int b) { int m = a % b; return m < 0 ? m + b : m; }
+
+// Fills tap table, pixel box, unit grouping and split count.  Returns false if
+// the geometry is not supported.
+inline bool make_plan(const mb_conv_desc* d, int variant, Plan* pl) {
+  WgradParams& p = pl->p;
+  memset(&p, 0, sizeof(p));
+  for (int i = 0; i < 4; ++i) pl->map_used[i] = 0;
+  p.K = d->K; p.C = d->C; p.T = d->R * d->S;
+  p.cchunks = (d->C + 31) / 32;
+  const bool flat = d->R == 1 && d->S == 1 && d->stride_h == 1 && d->stride_w == 1 &&
+                    d->pad_h == 0 && d->pad_w == 0;
+  pl->flat = flat;
+  int nt = 0;
+  for (int r = 0; r < d->R; ++r) {
+    const int oh = r * d->dil_h - d->pad_h;
+    const int a = posmod_(oh, d->stride_h), dh = (oh - a) / d->stride_h;
+    for (int s = 0; s < d->S; ++s) {
+      const int ow = s * d->dil_w - d->pad_w;
+      const int b = posmod_(ow, d->stride_w), dw = (ow - b) / d->stride_w;
+      if (a >= d->H || b >= d->W) continue;
+      const int mi = a * d->stride_w + b;
+      pl->map_used[mi] = 1;
+      p.taps.dh[nt] = static_cast<short>(dh);
+      p.taps.dw[nt] = static_cast<short>(dw);
+      p.taps.map[nt] = static_cast<unsigned char>(mi);
+      p.taps.btap[nt] = static_cast<unsigned char>(r * d->S + s);
+      ++nt;
+    }
+  }
+  if (nt == 0) return false;
+  p.ntaps = nt;
+  p.units = nt * p.cchunks;
+  // units per CTA: all taps of a channel chunk together when they fit
+  int U = nt <= kWgMaxUnits ? nt : kWgMaxUnits;
+  if (nt < kWgMaxUnits) {           // several chunks per group while they fit
+    U = (kWgMaxUnits / nt) * nt;
+    if (U > p.units) U = p.units;
+  }
+  p.units_per_group = U;
+  p.groups = (p.units + U - 1) / U;
+  p.k_tiles = (d->K + kTileM - 1) / kTileM;
+  // pixel box: rows multiple of 8, stage = (4 + U) * rows * 128 bytes, >= 2 stages
+  const int max_rows_smem = static_cast<int>((200 * 1024 / 2) / ((4 + U) * 128)) / 8 * 8;
+  int max_rows = max_rows_smem < 128 ? max_rows_smem : 128;
+  if (max_rows < 8) return false;
+  if (flat) {
+    const long long pixels = static_cast<long long>(d->N) * d->P * d->Q;
+    if (pixels > 0x7fffffffLL) return false;
+    p.bw = max_rows > 64 ? 64 : max_rows; p.bh = 1; p.bn = 1;
+    p.tiles_w = static_cast<int>((pixels + p.bw - 1) / p.bw);
+    p.tiles_h = 1;
+    p.pix_tiles = p.tiles_w;
+  } else {
+    // widest run along w (<= 64), then rows of h until bw*bh is a multiple of 8
+    int bw = d->Q < 64 ? d->Q : 64;
+    if (d->Q > 64) bw = 56;
+    int bh = 1;
+    while ((bw * bh) % 8) ++bh;
+    if (bw * bh > max_rows) {       // fall back to a run of 8k pixels along w
+      bw = max_rows < 64 ? max_rows : 64;
+      bw = bw / 8 * 8;
+      bh = 1;
+    } else {
+      while (bw * bh * 2 <= max_rows && bw * bh * 2 <= 64 && bh * 2 <= d->P) bh *= 2;
+    }
+    p.bw = bw; p.bh = bh; p.bn = 1;
+    p.tiles_w = (d->Q + bw - 1) / bw;
+    p.tiles_h = (d->P + bh - 1) / bh;
+    const long long tiles = static_cast<long long>(p.tiles_w) * p.tiles_h * d->N;
+    if (tiles > 0x7fffffffLL) return false;
+    p.pix_tiles = static_cast<int>(tiles);
+  }
+  p.rows = p.bw * p.bh * p.bn;
+  const size_t stage = static_cast<size_t>(4 + U) * p.rows * 128;
+  int st = static_cast<int>((216 * 1024) / stage);
+  if (st > 8) st = 8;
+  if (st < 2) return false;
+  p.stages = st;
+  pl->smem = 512 + 1024 + stage * st;
+  // splits: fill the machine about twice over, at least 4 pixel tiles per split
+  const int items = p.k_tiles * p.groups;
+  int splits = (2 * kNumSMs + items - 1) / items;
+  const int max_splits = (p.pix_tiles + 3) / 4;
+  if (splits > max_splits) splits = max_splits;
+  if (splits < 1) splits = 1;
+  if (variant == 1 && splits > 64) splits = 64;
+  p.splits = splits;
+  p.use_atomics = variant == 0;
+  pl->grid = items * splits;
+  return true;
+}
+
+}  // namespace wg
+
+inline size_t wgrad_workspace_bytes(const mb_conv_desc* d, int variant) {
+  if (variant != 1) return 0;
+  wg::Plan pl;
+  if (d->groups != 1 || !wg::make_plan(d, variant, &pl)) return 0;
+  return static_cast<size_t>(pl.p.splits) * d->K * d->R * d->S * d->C * sizeof(float);
+}
+
+// Defined in conv.cu (needs the tensor-map helpers).
+int wgrad_run(const char* who, const float* x, const float* dy, float* dw, float* dbias,
+              const mb_conv_desc* d, int variant, void* workspace, size_t workspace_bytes,
+              cudaStream_t st);
+
+}  // namespace mb

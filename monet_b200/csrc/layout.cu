@@ -37,6 +37,28 @@ int transpose(const char* who, const float* x, float* y, int N, int rows, int co
   return after_launch(who);
 }
 
+// NCHW -> NHWC with the channel count padded to Cp (zeros): one thread per pixel reads the
+// C planes (coalesced across the warp) and writes Cp contiguous floats.  For the few-channel
+// network input (C = 3 -> 4), which the tensor-core convolution needs 16-byte aligned.
+__global__ void __launch_bounds__(256) nchw_to_nhwc_pad(const float* __restrict__ x,
+                                                        float* __restrict__ y, int C, int Cp,
+                                                        size_t HW, size_t total_pixels) {
+  for (size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total_pixels;
+       t += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t n = t / HW, i = t - n * HW;
+    const float* src = x + n * C * HW + i;
+    float* dst = y + t * Cp;
+    for (int c0 = 0; c0 < Cp; c0 += 4) {
+      float4 v;
+      v.x = (c0 + 0 < C) ? __ldg(src + (c0 + 0) * HW) : 0.f;
+      v.y = (c0 + 1 < C) ? __ldg(src + (c0 + 1) * HW) : 0.f;
+      v.z = (c0 + 2 < C) ? __ldg(src + (c0 + 2) * HW) : 0.f;
+      v.w = (c0 + 3 < C) ? __ldg(src + (c0 + 3) * HW) : 0.f;
+      *reinterpret_cast<float4*>(dst + c0) = v;
+    }
+  }
+}
+
 // NHWC global average pool: thread = (n, 4 channels), loop over HW rows.
 __global__ void __launch_bounds__(256) gap_fwd_nhwc(const float* __restrict__ x,
                                                     float* __restrict__ y, int N, int C, int HW) {
@@ -100,6 +122,17 @@ int mb_nchw_to_nhwc(const float* x, float* y, int N, int C, int H, int W, void* 
 int mb_nhwc_to_nchw(const float* x, float* y, int N, int C, int H, int W, void* stream) {
   if (H <= 0 || W <= 0) return fail(MB_ERR_INVALID_ARGUMENT, "mb_nhwc_to_nchw: bad extent");
   return transpose("mb_nhwc_to_nchw", x, y, N, H * W, C, stream);
+}
+
+int mb_nchw_to_nhwc_pad(const float* x, float* y, int N, int C, int H, int W, int Cp,
+                        void* stream) {
+  if (N < 0 || C <= 0 || H <= 0 || W <= 0 || Cp < C || Cp % 4)
+    return fail(MB_ERR_INVALID_ARGUMENT, "mb_nchw_to_nhwc_pad: bad extent (Cp must be a multiple of 4, >= C)");
+  if (N == 0) return MB_OK;
+  if (!x || !y || !aligned(y, 16)) return fail(MB_ERR_INVALID_ARGUMENT, "mb_nchw_to_nhwc_pad: bad pointer");
+  const size_t HW = static_cast<size_t>(H) * W, total = HW * N;
+  nchw_to_nhwc_pad<<<grid_for(total, 256, 8), 256, 0, as_stream(stream)>>>(x, y, C, Cp, HW, total);
+  return after_launch("nchw_to_nhwc_pad");
 }
 
 int mb_global_avgpool_fwd(const float* x, float* y, int N, int C, int HW, int layout,

@@ -435,3 +435,131 @@ def global_avgpool_bwd(dy: torch.Tensor, shape, nhwc: bool) -> torch.Tensor:
                                       MB_NHWC if nhwc else MB_NCHW, _stream()),
           "global_avgpool_bwd")
     return dx
+
+
+# -------------------------------------------------------------------- convolution
+# Tensor-core passes work on NHWC activations and [K][R][S][C] filters, which is what
+# torch.channels_last tensors are physically; other layouts are converted on entry.
+# Channel counts that are not multiples of 4 (the 3-channel network input, a 1- or
+# 2-class head) are zero-padded to the next multiple of 4 and sliced back.
+
+from ._lib import MB_CONV_DGRAD, MB_CONV_FPROP, MB_CONV_WGRAD, ConvDesc  # noqa: E402
+
+
+def _pad4(n: int) -> int:
+    return (n + 3) // 4 * 4
+
+
+def conv_desc(x_shape, w_shape, stride, padding, dilation, groups) -> ConvDesc:
+    N, Cc, H, W = (int(v) for v in x_shape)
+    K, Cg, R, S = (int(v) for v in w_shape)
+    sh, sw = _pair(stride); ph, pw = _pair(padding); dh, dw = _pair(dilation)
+    P = (H + 2 * ph - dh * (R - 1) - 1) // sh + 1
+    Q = (W + 2 * pw - dw * (S - 1) - 1) // sw + 1
+    return ConvDesc(N, Cc, H, W, K, R, S, P, Q, sh, sw, ph, pw, dh, dw, int(groups))
+
+
+def conv_num_variants(conv_pass: int) -> int:
+    return lib().mb_conv_num_variants(conv_pass)
+
+
+def conv_workspace_bytes(conv_pass: int, variant: int, d: ConvDesc) -> int:
+    return lib().mb_conv_workspace_bytes(conv_pass, variant, C.byref(d))
+
+
+def _act_nhwc(x: torch.Tensor) -> torch.Tensor:
+    """NHWC activation with a channel count that is a multiple of 4."""
+    N, Cc, H, W = (int(v) for v in x.shape)
+    Cp = _pad4(Cc)
+    if Cp == Cc:
+        return to_nhwc(x)
+    xc = x.contiguous()
+    y = torch.empty((N, Cp, H, W), dtype=x.dtype, device=x.device, memory_format=torch.channels_last)
+    check(lib().mb_nchw_to_nhwc_pad(xc.data_ptr(), y.data_ptr(), N, Cc, H, W, Cp, _stream()),
+          "nchw_to_nhwc_pad")
+    return y
+
+
+def _filter_krsc(w: torch.Tensor) -> torch.Tensor:
+    """[K][R][S][C] filter with K and C padded to multiples of 4 (tiny; torch copies)."""
+    K, Cc, R, S = (int(v) for v in w.shape)
+    Kp, Cp = _pad4(K), _pad4(Cc)
+    if Kp == K and Cp == Cc:
+        return w.detach().contiguous(memory_format=torch.channels_last)
+    wp = torch.empty((Kp, Cp, R, S), dtype=w.dtype, device=w.device,
+                     memory_format=torch.channels_last).zero_()
+    wp[:K, :Cc] = w.detach()
+    return wp
+
+
+def _padded_desc(d: ConvDesc) -> ConvDesc:
+    return ConvDesc(d.N, _pad4(d.C), d.H, d.W, _pad4(d.K), d.R, d.S, d.P, d.Q, d.stride_h,
+                    d.stride_w, d.pad_h, d.pad_w, d.dil_h, d.dil_w, d.groups)
+
+
+def _workspace(conv_pass: int, variant: int, d: ConvDesc, device) -> torch.Tensor:
+    n = conv_workspace_bytes(conv_pass, variant, d)
+    return torch.empty(max(n, 16), dtype=torch.uint8, device=device)
+
+
+def conv2d_fprop(x, w, bias, stride, padding, dilation, groups=1, variant: int = 0):
+    """y = conv2d(x, w) + bias; y is a channels_last tensor of logical shape N x K x P x Q."""
+    _need_cuda(x, w, bias); _f32(x, "x"); _f32(w, "w")
+    d0 = conv_desc(x.shape, w.shape, stride, padding, dilation, groups)
+    d = _padded_desc(d0)
+    xa, wk = _act_nhwc(x), _filter_krsc(w)
+    b = None
+    if bias is not None:
+        b = bias.detach().contiguous()
+        if d.K != d0.K:
+            b = torch.nn.functional.pad(b, (0, d.K - d0.K))
+    y = torch.empty((d.N, d.K, d.P, d.Q), dtype=x.dtype, device=x.device,
+                    memory_format=torch.channels_last)
+    ws = _workspace(MB_CONV_FPROP, variant, d, x.device)
+    check(lib().mb_conv2d_fprop(xa.data_ptr(), wk.data_ptr(), b.data_ptr() if b is not None else None,
+                                y.data_ptr(), C.byref(d), int(variant), ws.data_ptr(), ws.numel(),
+                                _stream()), "conv2d_fprop")
+    return y if d.K == d0.K else y[:, :d0.K]
+
+
+def conv2d_dgrad(dy, w, x_shape, stride, padding, dilation, groups=1, variant: int = 0):
+    """dx (channels_last, logical shape x_shape) from dy and the filter."""
+    _need_cuda(dy, w); _f32(dy, "dy"); _f32(w, "w")
+    d0 = conv_desc(x_shape, w.shape, stride, padding, dilation, groups)
+    d = _padded_desc(d0)
+    if tuple(dy.shape) != (d0.N, d0.K, d0.P, d0.Q):
+        raise RuntimeError("monet_b200.conv2d_dgrad: gradient shape does not match the geometry")
+    ga, wk = _act_nhwc(dy), _filter_krsc(w)
+    dx = torch.empty((d.N, d.C, d.H, d.W), dtype=dy.dtype, device=dy.device,
+                     memory_format=torch.channels_last)
+    ws = _workspace(MB_CONV_DGRAD, variant, d, dy.device)
+    check(lib().mb_conv2d_dgrad(ga.data_ptr(), wk.data_ptr(), dx.data_ptr(), C.byref(d), int(variant),
+                                ws.data_ptr(), ws.numel(), _stream()), "conv2d_dgrad")
+    return dx if d.C == d0.C else dx[:, :d0.C]
+
+
+def conv2d_wgrad(x, dy, w_shape, stride, padding, dilation, groups=1, variant: int = 0,
+                 need_bias: bool = False):
+    """(dw, db): dw is a channels_last tensor of logical shape w_shape; db = dy.sum((0,2,3))."""
+    _need_cuda(x, dy); _f32(x, "x"); _f32(dy, "dy")
+    d0 = conv_desc(x.shape, w_shape, stride, padding, dilation, groups)
+    d = _padded_desc(d0)
+    if tuple(dy.shape) != (d0.N, d0.K, d0.P, d0.Q):
+        raise RuntimeError("monet_b200.conv2d_wgrad: gradient shape does not match the geometry")
+    xa, ga = _act_nhwc(x), _act_nhwc(dy)
+    dw = torch.empty((d.K, d.C, d.R, d.S), dtype=x.dtype, device=x.device,
+                     memory_format=torch.channels_last)
+    db = torch.empty(d.K, dtype=x.dtype, device=x.device) if need_bias else None
+    ws = _workspace(MB_CONV_WGRAD, variant, d, x.device)
+    check(lib().mb_conv2d_wgrad(xa.data_ptr(), ga.data_ptr(), dw.data_ptr(),
+                                db.data_ptr() if db is not None else None, C.byref(d), int(variant),
+                                ws.data_ptr(), ws.numel(), _stream()), "conv2d_wgrad")
+    if d.K != d0.K or d.C != d0.C:
+        dw = dw[:d0.K, :d0.C]
+        db = db[:d0.K] if db is not None else None
+    return dw, db
+
+
+def conv_device_status(reset: bool = True) -> int:
+    """0 when no tensor-core kernel has reported a pipeline time-out (synchronises)."""
+    return lib().mb_conv_device_status(int(reset))

@@ -6,5 +6,5 @@ Importing this package fills ``registry`` in the reference's module order
 """
 from .base import (COMMON_MODES, OP, InputStorage, IntermediateStorage, OutputStorage,
                    StorageInfo, all_modes, implements, install_into, list_ops, registry)
-from . import relu, elementary, pool, linear, bn, cat, hardtanh, funcs  # noqa: E402,F401
+from . import conv, relu, elementary, pool, linear, bn, cat, hardtanh, funcs  # noqa: E402,F401
 from .elementary import NativeOP  # noqa: F401

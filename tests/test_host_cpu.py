@@ -1,0 +1,132 @@
+"""CPU-only checks: the oracle against committed golden vectors and its own two forms, the
+registry's slot order, graph extraction, and that the C-ABI library loads and exports every
+symbol the header declares."""
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import lm_ops_oracle as oracle
+
+ROOT = Path(__file__).resolve().parent.parent
+GOLDEN = ROOT / "tests" / "golden" / "lm_ops_golden.npz"
+
+
+def test_library_exports_every_declared_symbol(built_lib):
+    from monet_b200 import _lib
+    header = (ROOT / "include" / "monet_b200.h").read_text()
+    declared = set(re.findall(r"\b(mb_[a-z0-9_]+)\s*\(", header))
+    declared -= {"mb_pool_desc", "mb_bn_desc", "mb_conv_desc"}
+    assert declared, "no declarations found"
+    assert declared == set(_lib.PROTOTYPES), declared ^ set(_lib.PROTOTYPES)
+    handle = _lib.lib()
+    for name in declared:
+        assert hasattr(handle, name), name
+    assert handle.mb_abi_version() >= 1
+    assert handle.mb_conv_num_variants(0) >= 1 and handle.mb_conv_num_variants(2) >= 2
+    assert handle.mb_pool_out_size(112, 3, 2, 1, 1, 0) == 56
+    assert handle.mb_pool_out_size(10, 3, 2, 0, 1, 1) == 5
+
+
+def test_ops_refuse_cpu_tensors(built_lib):
+    from monet_b200 import functional as F
+    with pytest.raises(RuntimeError, match="CUDA"):
+        F.relu(torch.randn(8))
+
+
+def test_registry_slot_order():
+    import monet_b200.lm_ops as L
+    names = lambda mode, op: [c.__name__ for c in L.list_ops(mode, op)]   # noqa: E731
+    m = "conv_multiway_newnode"
+    assert names(m, "aten::relu") == ["InputActReLU", "OutputActReLU", "BinaryActReLU"]
+    assert names(m, "aten::relu_") == ["InputActReLU", "OutputActReLU", "BinaryActReLU"]
+    assert names(m, "aten::batch_norm") == ["InputActBatchNorm", "OutputActBatchNorm"]
+    assert names(m, "aten::max_pool2d") == ["SimpleMaxPool2D", "IndicesActMaxPool2D"]
+    assert names(m, "aten::_convolution") == ["SpecificAlgoConvolution"]
+    assert names("normal", "aten::_convolution") == ["GreedyAlgoConvolution"]
+    assert names("none", "aten::_convolution") == ["PytorchConvolution"]
+    assert names("normal", "aten::relu") == ["InputActReLU"]
+    assert names("conv_normal", "aten::relu") == ["OutputActReLU"]
+    assert names(m, "aten::hardtanh") == ["InputActHardTanh", "OutputActHardTanh"]
+    for mode, table in L.registry.items():
+        for op, impls in table.items():
+            assert len(impls) <= 3, (mode, op)          # the solver has three slots per op
+    assert L.relu.BinaryActReLU.backward_storage.size((4, 64, 112, 112)) == 401408
+    assert L.pool.IndicesActMaxPool2D.backward_storage.size((4, 64, 56, 56)) == 401408
+
+
+def test_install_into_a_foreign_registry():
+    import types
+    import monet_b200.lm_ops as L
+    fake = types.SimpleNamespace(registry={"normal": {"aten::relu": ["stale"]}})
+    L.install_into(fake)
+    assert fake.registry["normal"]["aten::relu"] == L.list_ops("normal", "aten::relu")
+
+
+def test_graph_extraction_and_policies():
+    import torchvision
+    from monet_b200 import runner
+    model = torchvision.models.resnet50()
+    nodes, out = runner.extract_graph(model)
+    ops = [n.op for n in nodes]
+    assert ops.count("aten::_convolution") == 53 and ops.count("aten::batch_norm") == 53
+    assert ops.count("aten::add") == 16 and nodes[out].op == "aten::addmm"
+    r = runner.Runner(model, runner.low_memory)
+    bn = [n for n in nodes if n.op == "aten::batch_norm"]
+    assert all(r.choices[n.id].impl == 1 for n in bn)
+    with pytest.raises(ValueError):
+        runner.Runner(model, lambda ns, n: runner.Choice(inplace=(n.op == "aten::_convolution")))
+
+
+def test_oracle_maxpool_forms_agree():
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(2, 3, 9, 10, generator=g)
+    x[0, 0, 1, 1] = float("nan")
+    for k, s, p, d, c in [(3, 2, 1, 1, False), (2, 2, 0, 1, False), (3, 2, 0, 1, True), (3, 1, 1, 2, False)]:
+        _, a = oracle.maxpool_local_index(x, k, s, p, d, c)
+        _, b = oracle.maxpool_forward(x, k, s, p, d, c)
+        assert np.array_equal(a, b)
+
+
+def test_oracle_bn_from_output_matches_autograd():
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(4, 6, 5, 5, generator=g)
+    gamma = torch.rand(6, generator=g) + 0.5
+    beta = torch.randn(6, generator=g)
+    dy = torch.randn(4, 6, 5, 5, generator=g)
+    y, mean, invstd, _, _ = oracle.bn_forward_train(x, gamma, beta, torch.zeros(6), torch.ones(6))
+    dx, dg, db = oracle.bn_backward_from_output(dy, y, gamma, beta, invstd)
+    rx, rg, rb = oracle.bn_backward_from_input(dy, x, gamma)
+    assert torch.allclose(dx, rx, atol=1e-5) and torch.allclose(dg, rg, atol=1e-4) and torch.allclose(db, rb, atol=1e-4)
+
+
+def test_oracle_against_golden_vectors():
+    """Fixtures generated once from PyTorch CPU by tests/golden/make_golden.py."""
+    z = np.load(GOLDEN)
+    x = torch.from_numpy(z["relu_x"])
+    assert np.array_equal(oracle.relu_mask_bytes(x), z["relu_mask"])
+    assert np.array_equal(oracle.pack_nibbles(z["nib_in"]), z["nib_out"])
+    assert np.array_equal(oracle.unpack_nibbles(z["nib_out"], z["nib_in"].size), z["nib_in"])
+    px = torch.from_numpy(z["pool_x"])
+    y, local = oracle.maxpool_forward(px, 3, 2, 1)
+    assert np.array_equal(y.numpy(), z["pool_y"]) and np.array_equal(local, z["pool_local"])
+    assert np.array_equal(oracle.maxpool_nibbles(local), z["pool_nibbles"])
+    dx = oracle.maxpool_backward_from_index(torch.from_numpy(z["pool_dy"]), local, px.shape, 3, 2, 1)
+    assert np.allclose(dx.numpy(), z["pool_dx"], atol=1e-6)
+    bx = torch.from_numpy(z["bn_x"])
+    y, mean, invstd, rm, rv = oracle.bn_forward_train(
+        bx, torch.from_numpy(z["bn_gamma"]), torch.from_numpy(z["bn_beta"]),
+        torch.zeros(bx.shape[1]), torch.ones(bx.shape[1]))
+    assert np.allclose(y.numpy(), z["bn_y"], atol=1e-5)
+    assert np.allclose(mean.numpy(), z["bn_mean"], atol=1e-6) and np.allclose(invstd.numpy(), z["bn_invstd"], rtol=1e-5)
+    dx, dg, db = oracle.bn_backward_from_output(torch.from_numpy(z["bn_dy"]), y, torch.from_numpy(z["bn_gamma"]),
+                                               torch.from_numpy(z["bn_beta"]), invstd)
+    assert np.allclose(dx.numpy(), z["bn_dx"], atol=1e-5) and np.allclose(dg.numpy(), z["bn_dgamma"], atol=1e-4)
+    loss, dlog = oracle.cross_entropy(torch.from_numpy(z["ce_logits"]), torch.from_numpy(z["ce_labels"]), 0.25)
+    assert np.allclose(loss.numpy(), z["ce_loss"], atol=1e-6) and np.allclose(dlog.numpy(), z["ce_dlogits"], atol=1e-7)
+    s = oracle.stem_reference(N=1, H=32, W=32)
+    assert np.allclose(s["y"].numpy(), z["stem_y"], atol=1e-5)
+    assert np.array_equal(s["mask"], z["stem_mask"]) and np.array_equal(s["nibbles"], z["stem_nibbles"])
+    assert np.allclose(s["dw"].numpy(), z["stem_dw"], atol=1e-4)

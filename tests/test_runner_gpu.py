@@ -1,0 +1,132 @@
+"""Whole-network parity: a ResNet run through the low-memory operators (both policies)
+against stock PyTorch autograd in fp32 on the CPU.  Convolutions run in TF32, so outputs and
+gradients are compared at the convolution tolerance (rtol 2e-2 of the tensor's scale)."""
+import copy
+
+import pytest
+import torch
+import torchvision
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, ref):
+    return float((a - ref).norm() / ref.norm().clamp_min(1e-12))
+
+
+def _reference_step(model, x, labels):
+    model = copy.deepcopy(model).cpu().train()
+    out = model(x)
+    loss = torch.nn.functional.cross_entropy(out, labels)
+    loss.backward()
+    return out.detach(), loss.detach(), {k: p.grad.clone() for k, p in model.named_parameters()}, \
+        {k: b.clone() for k, b in model.named_buffers()}
+
+
+class _TinyResNet(torch.nn.Module):
+    """Stem + one bottleneck with a strided downsample + classifier: every operator of the
+    ResNet graph, but shallow enough that TF32 rounding is not amplified by depth."""
+
+    def __init__(self):
+        super().__init__()
+        nn = torch.nn
+        self.conv1 = nn.Conv2d(3, 32, 7, 2, 3, bias=False)
+        self.bn1 = nn.BatchNorm2d(32)
+        self.relu = nn.ReLU(inplace=True)
+        self.maxpool = nn.MaxPool2d(3, 2, 1)
+        self.c1 = nn.Conv2d(32, 16, 1, bias=False); self.b1 = nn.BatchNorm2d(16)
+        self.c2 = nn.Conv2d(16, 16, 3, 2, 1, bias=False); self.b2 = nn.BatchNorm2d(16)
+        self.c3 = nn.Conv2d(16, 64, 1, bias=True); self.b3 = nn.BatchNorm2d(64)
+        self.ds = nn.Conv2d(32, 64, 1, 2, bias=False); self.bds = nn.BatchNorm2d(64)
+        self.avgpool = nn.AdaptiveAvgPool2d((1, 1))
+        self.fc = nn.Linear(64, 10)
+
+    def forward(self, x):
+        x = self.maxpool(self.relu(self.bn1(self.conv1(x))))
+        idt = self.bds(self.ds(x))
+        out = self.relu(self.b1(self.c1(x)))
+        out = self.relu(self.b2(self.c2(out)))
+        out = self.b3(self.c3(out))
+        out = out + idt
+        out = self.relu(out)
+        return self.fc(torch.flatten(self.avgpool(out), 1))
+
+
+def _run_ours(model, x, labels, policy, cuda):
+    from monet_b200 import runner
+    from monet_b200.lm_ops.softmax import SoftmaxCrossEntropy
+    gm = copy.deepcopy(model).to(cuda).train()
+    r = runner.Runner(gm, getattr(runner, policy))
+    out = r.forward(x.to(cuda))
+    ce = SoftmaxCrossEntropy()
+    loss = ce.forward(out, labels.to(cuda))
+    r.backward(ce.backward())
+    torch.cuda.synchronize()
+    return gm, out, loss
+
+
+@pytest.mark.parametrize("policy", ["store_all", "low_memory"])
+def test_tiny_resnet_step_matches_autograd(cuda, policy):
+    torch.manual_seed(0)
+    model = _TinyResNet().train()
+    x = torch.randn(16, 3, 64, 64)
+    labels = torch.randint(0, 10, (16,))
+    ref_out, ref_loss, ref_grads, ref_bufs = _reference_step(model, x, labels)
+    gm, out, loss = _run_ours(model, x, labels, policy, cuda)
+    assert _rel(out.cpu(), ref_out) < 2e-2
+    assert abs(float(loss) - float(ref_loss)) < 1e-2
+    for k, p in gm.named_parameters():
+        assert p.grad is not None, k
+        assert _rel(p.grad.cpu(), ref_grads[k]) < 2e-2, (k, _rel(p.grad.cpu(), ref_grads[k]))
+    for k, b in gm.named_buffers():
+        if "num_batches" not in k:
+            assert _rel(b.cpu(), ref_bufs[k]) < 1e-2, k
+
+
+@pytest.mark.parametrize("arch", ["resnet18", "resnet50"])
+def test_deep_resnet_tracks_tf32_autograd(cuda, arch):
+    """Deep randomly initialised nets amplify TF32 rounding (stock PyTorch with TF32 cuDNN
+    convolutions is itself ~10 % off the fp32 CPU gradients here), so the bar is relative:
+    no worse than 1.6x the error stock PyTorch's TF32 path shows, plus 2 %."""
+    torch.manual_seed(0)
+    model = getattr(torchvision.models, arch)(num_classes=10).train()
+    x = torch.randn(8, 3, 64, 64)
+    labels = torch.randint(0, 10, (8,))
+    ref_out, ref_loss, ref_grads, _ = _reference_step(model, x, labels)
+    torch.backends.cudnn.allow_tf32 = True
+    try:
+        tm = copy.deepcopy(model).to(cuda).train()
+        torch.nn.functional.cross_entropy(tm(x.to(cuda)), labels.to(cuda)).backward()
+    finally:
+        torch.backends.cudnn.allow_tf32 = False
+    results = {}
+    for policy in ("store_all", "low_memory"):
+        gm, out, loss = _run_ours(model, x, labels, policy, cuda)
+        assert _rel(out.cpu(), ref_out) < 5e-2
+        for (k, p), (_, tp) in zip(gm.named_parameters(), tm.named_parameters()):
+            ours, theirs = _rel(p.grad.cpu(), ref_grads[k]), _rel(tp.grad.cpu(), ref_grads[k])
+            assert ours < 1.6 * theirs + 2e-2, (k, ours, theirs)
+        results[policy] = {k: p.grad.clone() for k, p in gm.named_parameters()}
+    # the two policies run the same arithmetic apart from the batch-norm backward flavour
+    for k in results["store_all"]:
+        assert _rel(results["low_memory"][k], results["store_all"][k]) < 2e-2, k
+
+
+def test_low_memory_policy_keeps_less(cuda):
+    from monet_b200 import runner
+    torch.manual_seed(0)
+    model = torchvision.models.resnet50(num_classes=10).to(cuda).train()
+    x = torch.randn(8, 3, 96, 96, device=cuda)
+    peaks = {}
+    for policy in ("store_all", "low_memory"):
+        r = runner.Runner(model, getattr(runner, policy))
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats()
+        base = torch.cuda.memory_allocated()
+        out = r.forward(x)
+        r.backward(torch.ones_like(out))
+        torch.cuda.synchronize()
+        peaks[policy] = torch.cuda.max_memory_allocated() - base
+        for p in model.parameters():
+            p.grad = None
+    assert peaks["low_memory"] < peaks["store_all"], peaks
