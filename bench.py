@@ -1,0 +1,334 @@
+#!/usr/bin/env python
+"""Benchmark: ResNet-50 (torchvision v1.5 layout) training step, batch 184 per GPU, fp32
+semantics (TF32 tensor-core convolutions), synthetic N(0,1) images and uniform labels,
+cross-entropy + SGD(lr 0.1, momentum 0.9), run entirely through the low-memory operators.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--schedule low_memory|store_all]
+  python bench.py --impl reference ...      # PyTorch CPU eager on the host cores
+
+One JSON line on stdout (rank 0).  `value` = images/s with the batch already resident in
+HBM; `e2e` = the same step fed from pinned host memory each step, loss read back each step.
+Under torchrun every rank trains its own batch (weak scaling) and weight gradients are
+all-reduced over NCCL.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "resnet50_bs184_train_images_per_s"
+WORKLOAD = "ResNet-50 v1.5, batch 184 per GPU, 3x224x224 fp32, CE + SGD momentum (BASELINE configs[1])"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--schedule", default="low_memory", choices=["low_memory", "store_all"])
+    ap.add_argument("--batch", type=int, default=184)
+    ap.add_argument("--cpu-batch", type=int, default=16, help="images per step of the CPU sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+# ------------------------------------------------------------------ reference arm (CPU)
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import cpu_baseline
+    steps = max(1, min(args.steps, 5))
+    ips, ms, threads = cpu_baseline.resnet50_train_steps(args.cpu_batch, steps, warmup=1)
+    sample = f"{steps} eager steps of batch {args.cpu_batch} (of 184) on {threads} host threads"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": ips, "unit": "images/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": 1, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": ips, "unit": "images/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": ips, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, smax, reasons = [], 0.0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); smax = max(smax, float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(names, r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------- algorithmic bytes / flops
+def family_costs(runner_obj, batch_shape):
+    """Per entry-point family: algorithmic HBM bytes and flops of ONE training step, from the
+    graph and the recorded shapes (fp32: 4 bytes per element).
+
+    conv pass: activations in + filter + activations out, 2*N*P*Q*K*C*R*S flops.
+    bn train fwd 12 B/el, bn cached-stat fwd 8, bn bwd 20, relu fwd 8 (+1/8 with mask),
+    relu bwd from a saved activation 12, add 12, max-pool 4*E_in + 4.5*E_out each way."""
+    import numpy as np
+    cost = {}
+
+    def add(fam, b, f=0.0):
+        c = cost.setdefault(fam, [0.0, 0.0])
+        c[0] += b; c[1] += f
+
+    shapes = runner_obj.shapes
+    for n in runner_obj.nodes:
+        out = shapes[n.id]
+        e_out = float(np.prod(out))
+        a0 = n.args[0]
+        in_shape = shapes[a0.value] if a0.kind == 'node' else (batch_shape if a0.kind == 'input' else None)
+        e_in = float(np.prod(in_shape)) if in_shape is not None else 0.0
+        ch = runner_obj.choices[n.id]
+        if n.op == 'aten::_convolution':
+            w = runner_obj._tensors[n.args[1].value]
+            e_w = float(w.numel())
+            fl = 2.0 * e_out * w.shape[1] * w.shape[2] * w.shape[3]
+            add("mb_conv2d_fprop", 4 * (e_in + e_w + e_out), fl)
+            add("mb_conv2d_wgrad", 4 * (e_in + e_w + e_out), fl)
+            if a0.kind == 'node':
+                add("mb_conv2d_dgrad", 4 * (e_in + e_w + e_out), fl)
+        elif n.op == 'aten::batch_norm':
+            add("mb_bn_fwd_train", 12 * e_out)
+            add("mb_bn_bwd_from_output" if ch.impl == 1 else "mb_bn_bwd_from_input", 20 * e_out)
+        elif n.op in ('aten::relu', 'aten::relu_'):
+            add("mb_relu_fwd", 8 * e_out * (2 if ch.recompute else 1))
+            add("mb_relu_bwd_act", 12 * e_out)
+        elif n.op in ('aten::add', 'aten::add_'):
+            add("mb_add_fwd", 12 * e_out)
+        elif n.op == 'aten::max_pool2d':
+            add("mb_maxpool2d_fwd", 4 * e_in + 4.5 * e_out)
+            add("mb_maxpool2d_bwd", 4 * e_in + 4.5 * e_out)
+    return cost
+
+
+# ----------------------------------------------------------------------------- ours
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import torchvision
+
+    from monet_b200 import _lib, build, runner
+    from monet_b200.lm_ops.softmax import SoftmaxCrossEntropy
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the operators)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    if not _lib.LIB_PATH.exists():
+        build.build()
+    api = _lib.lib()
+
+    torch.manual_seed(0)
+    model = torchvision.models.resnet50().to(dev).train()
+    model = model.to(memory_format=torch.channels_last)       # filters as [K][R][S][C]
+    params = [p for p in model.parameters()]
+    flat = torch.zeros(sum(p.numel() for p in params), device=dev)    # gradient bucket
+    off = 0
+    for p in params:
+        p.grad = flat[off:off + p.numel()].view(p.shape)
+        off += p.numel()
+    opt = torch.optim.SGD(params, lr=0.1, momentum=0.9)
+    policy = getattr(runner, args.schedule)
+    run = runner.Runner(model, policy)
+    ce = SoftmaxCrossEntropy()
+
+    B = args.batch
+    g = torch.Generator(device="cpu").manual_seed(1 + rank)
+    x_host = torch.randn(B, 3, 224, 224, generator=g).pin_memory()
+    y_host = torch.randint(0, 1000, (B,), generator=g).pin_memory()
+    x_dev = x_host.to(dev)
+    y_dev = y_host.to(dev)
+
+    def step(x, y):
+        flat.zero_()
+        out = run.forward(x)
+        loss = ce.forward(out, y)
+        run.backward(ce.backward())
+        if world > 1:
+            dist.all_reduce(flat)
+            flat.div_(world)
+        opt.step()
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- warm-up (first step also autotunes nothing: variants are fixed) + survey of families
+    fam_events = {}
+    stream = torch.cuda.current_stream()
+    watch = None
+
+    def before(name):
+        if watch is None or name in watch:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(stream)
+            fam_events.setdefault(name, []).append([ev, None])
+
+    def after(name):
+        if watch is None or name in watch:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(stream)
+            fam_events[name][-1][1] = ev
+
+    for i in range(max(args.warmup, 3)):
+        if i == max(args.warmup, 3) - 1:
+            _lib.set_probe(before, after)            # survey: every family, one untimed step
+        loss = step(x_dev, y_dev)
+    torch.cuda.synchronize()
+    _lib.set_probe()
+    survey = {k: sum(a.elapsed_time(b) for a, b in v) for k, v in fam_events.items()}
+    costs = family_costs(run, (B, 3, 224, 224))
+    dominant = max((k for k in survey if k in costs), key=lambda k: survey[k])
+    fam_events.clear()
+    watch = {dominant}
+
+    # ---- timed region 1: batch resident in HBM
+    sampler = ClockSampler(local)
+    sampler.start()
+    torch.cuda.reset_peak_memory_stats()
+    launches0 = api.mb_launch_count()
+    _lib.set_probe(before, after)
+    barrier()
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        loss = step(x_dev, y_dev)
+    t1.record()
+    barrier()
+    _lib.set_probe()
+    ms_dev = t0.elapsed_time(t1) / args.steps
+    launches = api.mb_launch_count() - launches0
+    peak = torch.cuda.max_memory_allocated()
+    dom_ms = sum(a.elapsed_time(b) for a, b in fam_events[dominant]) / args.steps
+    dom_calls = len(fam_events[dominant]) / args.steps
+
+    # ---- timed region 2: end to end from pinned host memory, loss read back every step
+    barrier()
+    w0 = time.perf_counter()
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    last = 0.0
+    for _ in range(args.steps):
+        x_dev.copy_(x_host, non_blocking=True)
+        y_dev.copy_(y_host, non_blocking=True)
+        last = float(step(x_dev, y_dev))             # device -> host read of the loss
+    e1.record()
+    barrier()
+    ms_e2e = max(e0.elapsed_time(e1), (time.perf_counter() - w0) * 1e3) / args.steps
+    clocks = sampler.stop()
+
+    if world > 1:
+        t = torch.tensor([ms_dev, ms_e2e], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_dev, ms_e2e = float(t[0]), float(t[1])
+
+    if rank == 0:
+        peaks_file = ROOT / "MEASURED_PEAKS.json"
+        if peaks_file.exists():
+            mp = json.loads(peaks_file.read_text())
+            hbm, tf32, which = mp["hbm_gbs"], mp["bf16_tflops_sustained"] / 2, "measured"
+        else:
+            hbm, tf32, which = 6650.0, 1590.0 / 2, "fallback"
+        b, f = costs[dominant]
+        t_hbm, t_tc = b / (hbm * 1e9), f / (tf32 * 1e12)
+        if t_hbm >= t_tc:
+            roof = {"bound": "hbm", "achieved": b / (dom_ms * 1e-3) / 1e9, "peak": hbm, "unit": "GB/s"}
+        else:
+            roof = {"bound": "tensor", "achieved": f / (dom_ms * 1e-3) / 1e12, "peak": tf32, "unit": "TFLOP/s"}
+        roof["frac"] = roof["achieved"] / roof["peak"]
+        roof.update({"traffic": None, "kernel": dominant, "launches_per_step": dom_calls,
+                     "ms_per_step": dom_ms, "peak_source": which,
+                     "note": "entry point timed with CUDA events inside the timed region; "
+                             "tensor peak = measured sustained bf16 / 2 (TF32)"})
+        line = {
+            "metric": METRIC, "value": B * world / (ms_dev * 1e-3), "unit": "images/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_dev,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32(tf32 conv)",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "schedule": args.schedule, "global_batch": B * world,
+                       "parallelism": f"dp{world}", "l2": "inputs and activations exceed L2 (126 MB) many times over"},
+            "peak_gb": peak / 2 ** 30, "loss": last,
+            "e2e": {"value": B * world / (ms_e2e * 1e-3), "unit": "images/s",
+                    "h2d_bytes_per_step": x_host.numel() * 4 + y_host.numel() * 8, "d2h_bytes_per_step": 4},
+            "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
+            "family_ms_survey": {k: round(v, 3) for k, v in sorted(survey.items(), key=lambda kv: -kv[1])[:12]},
+        }
+        if not args.no_cpu_baseline and world >= 1:
+            from oracle import cpu_baseline
+            ips, ms, threads = cpu_baseline.resnet50_train_steps(args.cpu_batch, 2, warmup=1)
+            line["cpu_baseline"] = {"value": ips, "unit": "images/s", "cores": threads, "kind": "port",
+                                    "sample": f"2 eager steps of batch {args.cpu_batch} (of 184), PyTorch CPU"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -82,9 +82,43 @@ PROTOTYPES = {
 }
 
 _lib = None
+_probe = None     # optional (before, after) callables invoked around every C-ABI call
 
 
-def lib() -> C.CDLL:
+def set_probe(before=None, after=None) -> None:
+    """Install hooks called as before(name) / after(name) around each entry point; used by
+    bench.py to bracket launches with CUDA events.  set_probe() removes them."""
+    global _probe
+    _probe = (before, after) if before is not None and after is not None else None
+
+
+class _Api:
+    """Typed entry points as attributes; routes through the probe hooks when set."""
+
+    def __init__(self, handle):
+        self._handle = handle
+        for name, (res, args) in PROTOTYPES.items():
+            fn = getattr(handle, name)     # AttributeError if the symbol is not exported
+            fn.restype = res
+            fn.argtypes = args
+            setattr(self, name, self._wrap(name, fn))
+
+    @staticmethod
+    def _wrap(name, fn):
+        def call(*a):
+            probe = _probe
+            if probe is None:
+                return fn(*a)
+            probe[0](name)
+            try:
+                return fn(*a)
+            finally:
+                probe[1](name)
+        call.__name__ = name
+        return call
+
+
+def lib() -> "_Api":
     """The loaded library with typed entry points; raises if it has not been built."""
     global _lib
     if _lib is None:
@@ -92,12 +126,7 @@ def lib() -> C.CDLL:
             raise RuntimeError(
                 f"{LIB_PATH} is missing: build it with `python -m monet_b200.build` "
                 "(there is no fallback path)")
-        handle = C.CDLL(str(LIB_PATH))
-        for name, (res, args) in PROTOTYPES.items():
-            fn = getattr(handle, name)     # AttributeError if the symbol is not exported
-            fn.restype = res
-            fn.argtypes = args
-        _lib = handle
+        _lib = _Api(C.CDLL(str(LIB_PATH)))
     return _lib
 
 

@@ -205,6 +205,7 @@ class Runner:
         self.input_requires_grad = input_requires_grad
         self.choices = [policy(self.nodes, n) for n in self.nodes]
         self.param_grads: Dict[str, torch.Tensor] = {}
+        self.shapes: Dict[int, tuple] = {}      # node id -> output shape, filled by forward()
         self._tensors = dict(model.state_dict(keep_vars=True))
         self._last_fwd_user = {n.id: (max(n.users) if n.users else -1) for n in self.nodes}
         self._validate()
@@ -293,6 +294,7 @@ class Runner:
                     out, self._inter[n.id] = out
                 del args
                 vals[n.id] = out
+                self.shapes[n.id] = tuple(out.shape)
                 if self.choices[n.id].inplace:
                     src = n.args[0]
                     if src.kind == 'node':
