@@ -238,6 +238,21 @@ int mb_conv2d_dgrad(const float* dy, const float* w, float* dx, const mb_conv_de
 int mb_conv2d_wgrad(const float* x, const float* dy, float* dw, float* dbias,
                     const mb_conv_desc* d, int variant, void* workspace, size_t workspace_bytes,
                     void* stream);
+/* Few-channel convolutions (C <= 4, filter width <= 8, stride <= 2: the network's first
+ * layer).  The input is copied once into a zero-padded 4-channel NHWC buffer
+ * xp[N][Hp][Wp][4] (Hp, Wp from mb_conv_smallc_geometry; N*Hp*Wp*16 bytes, the caller's
+ * workspace), the filter is given / returned as [K][R][8][4] (s, c; zero beyond S and C),
+ * and the GEMM K dimension becomes R x 32 instead of R*S x 32-with-28-zeros.
+ * `d` describes the logical convolution (C = real channel count).  They replace the
+ * same cuDNN calls as mb_conv2d_fprop / mb_conv2d_wgrad for that layer.             */
+int mb_conv_smallc_geometry(const mb_conv_desc* d, int* Hp, int* Wp);
+int mb_conv_smallc_pack_input(const float* x_nchw, float* xp, const mb_conv_desc* d, void* stream);
+int mb_conv2d_fprop_smallc(const float* xp, const float* wp, const float* bias, float* y,
+                           const mb_conv_desc* d, void* stream);
+size_t mb_conv_smallc_wgrad_workspace_bytes(const mb_conv_desc* d, int variant);
+int mb_conv2d_wgrad_smallc(const float* xp, const float* dy, float* dwp, float* dbias,
+                           const mb_conv_desc* d, int variant, void* workspace,
+                           size_t workspace_bytes, void* stream);
 /* Status word of the tensor-core kernels: 0 = healthy, otherwise the code of
  * the first pipeline wait that timed out (the kernel then gave up cleanly).
  * Synchronises the device.  reset != 0 clears it.                            */

@@ -196,15 +196,11 @@ __global__ void __launch_bounds__(256) transpose_filter(const float* __restrict_
 
 namespace mb {
 
-int wgrad_run(const char* who, const float* x, const float* dy, float* dw, float* dbias,
-              const mb_conv_desc* d, int variant, void* workspace, size_t workspace_bytes,
-              cudaStream_t st) {
-  const CUtensorMapSwizzle kWg = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;   // MN-major TF32 operands
-  wg::Plan pl;
-  if (!wg::make_plan(d, variant, &pl))
-    return fail(MB_ERR_UNSUPPORTED, "%s: geometry not supported by the tensor-core kernel", who);
+// Shared tail of the two wgrad entry points: zero / workspace set-up, launch, reduction.
+int wgrad_launch(const char* who, wg::Plan& pl, const CUtensorMap& mdy, const CUtensorMap* mx,
+                 const float* dy, float* dw, size_t dw_elems, float* dbias, const mb_conv_desc* d,
+                 int variant, void* workspace, size_t workspace_bytes, cudaStream_t st) {
   WgradParams& p = pl.p;
-  const size_t dw_elems = static_cast<size_t>(d->K) * d->R * d->S * d->C;
   int rc;
   if (variant == 0) {
     if (cudaMemsetAsync(dw, 0, dw_elems * sizeof(float), st) != cudaSuccess)
@@ -220,34 +216,6 @@ int wgrad_run(const char* who, const float* x, const float* dy, float* dw, float
       return fail(MB_ERR_LAUNCH, "%s: memset failed", who);
     p.out = static_cast<float*>(workspace);
     p.split_stride = static_cast<long long>(dw_elems);
-  }
-  CUtensorMap mdy, mx[4];
-  const long long K4 = static_cast<long long>(d->K) * 4, C4 = static_cast<long long>(d->C) * 4;
-  if (pl.flat) {
-    const long long pixels = static_cast<long long>(d->N) * d->P * d->Q;
-    rc = encode_act(who, &mdy, dy, d->K, pixels, 1, 1, K4, K4 * pixels, K4 * pixels, p.bw, 1, 1, kWg);
-    if (rc) return rc;
-    rc = encode_act(who, &mx[0], x, d->C, pixels, 1, 1, C4, C4 * pixels, C4 * pixels, p.bw, 1, 1, kWg);
-    if (rc) return rc;
-    mx[1] = mx[2] = mx[3] = mx[0];
-  } else {
-    rc = encode_act(who, &mdy, dy, d->K, d->Q, d->P, d->N, K4, K4 * d->Q, K4 * d->Q * d->P, p.bw,
-                    p.bh, p.bn, kWg);
-    if (rc) return rc;
-    int first = -1;
-    for (int mi = 0; mi < d->stride_h * d->stride_w; ++mi) {
-      if (!pl.map_used[mi]) continue;
-      const int a = mi / d->stride_w, b = mi % d->stride_w;
-      const long long Wv = (d->W - b + d->stride_w - 1) / d->stride_w;
-      const long long Hv = (d->H - a + d->stride_h - 1) / d->stride_h;
-      rc = encode_act(who, &mx[mi], x + (static_cast<long long>(a) * d->W + b) * d->C, d->C, Wv, Hv,
-                      d->N, C4 * d->stride_w, C4 * d->W * d->stride_h, C4 * d->W * d->H, p.bw, p.bh,
-                      p.bn, kWg);
-      if (rc) return rc;
-      if (first < 0) first = mi;
-    }
-    for (int mi = 0; mi < 4; ++mi)
-      if (mi >= d->stride_h * d->stride_w || !pl.map_used[mi]) mx[mi] = mx[first];
   }
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
@@ -277,6 +245,102 @@ int wgrad_run(const char* who, const float* x, const float* dy, float* dw, float
     if (rc) return rc;
   }
   return MB_OK;
+}
+
+int wgrad_run(const char* who, const float* x, const float* dy, float* dw, float* dbias,
+              const mb_conv_desc* d, int variant, void* workspace, size_t workspace_bytes,
+              cudaStream_t st) {
+  const CUtensorMapSwizzle kWg = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;   // MN-major TF32 operands
+  wg::Plan pl;
+  if (!wg::make_plan(d, variant, &pl))
+    return fail(MB_ERR_UNSUPPORTED, "%s: geometry not supported by the tensor-core kernel", who);
+  WgradParams& p = pl.p;
+  const size_t dw_elems = static_cast<size_t>(d->K) * d->R * d->S * d->C;
+  int rc;
+  CUtensorMap mdy, mx[4];
+  const long long K4 = static_cast<long long>(d->K) * 4, C4 = static_cast<long long>(d->C) * 4;
+  if (pl.flat) {
+    const long long pixels = static_cast<long long>(d->N) * d->P * d->Q;
+    rc = encode_act(who, &mdy, dy, d->K, pixels, 1, 1, K4, K4 * pixels, K4 * pixels, p.bw, 1, 1, kWg);
+    if (rc) return rc;
+    rc = encode_act(who, &mx[0], x, d->C, pixels, 1, 1, C4, C4 * pixels, C4 * pixels, p.bw, 1, 1, kWg);
+    if (rc) return rc;
+    mx[1] = mx[2] = mx[3] = mx[0];
+  } else {
+    rc = encode_act(who, &mdy, dy, d->K, d->Q, d->P, d->N, K4, K4 * d->Q, K4 * d->Q * d->P, p.bw,
+                    p.bh, p.bn, kWg);
+    if (rc) return rc;
+    int first = -1;
+    for (int mi = 0; mi < d->stride_h * d->stride_w; ++mi) {
+      if (!pl.map_used[mi]) continue;
+      const int a = mi / d->stride_w, b = mi % d->stride_w;
+      const long long Wv = (d->W - b + d->stride_w - 1) / d->stride_w;
+      const long long Hv = (d->H - a + d->stride_h - 1) / d->stride_h;
+      rc = encode_act(who, &mx[mi], x + (static_cast<long long>(a) * d->W + b) * d->C, d->C, Wv, Hv,
+                      d->N, C4 * d->stride_w, C4 * d->W * d->stride_h, C4 * d->W * d->H, p.bw, p.bh,
+                      p.bn, kWg);
+      if (rc) return rc;
+      if (first < 0) first = mi;
+    }
+    for (int mi = 0; mi < 4; ++mi)
+      if (mi >= d->stride_h * d->stride_w || !pl.map_used[mi]) mx[mi] = mx[first];
+  }
+  return wgrad_launch(who, pl, mdy, mx, dy, dw, dw_elems, dbias, d, variant, workspace, workspace_bytes, st);
+}
+
+// ------------------------------------------------------------- few-channel convolutions
+// A convolution with C <= 4 input channels (the network input) would waste 7/8 of every
+// 32-channel operand row.  Instead the input is copied once into a zero-padded NHWC buffer
+// with 4 channels, xp[N][Hp][Wp][4]; the 8 pixels x 4 channels to the right of any pixel
+// are then 32 contiguous floats, i.e. one whole operand row holding filter columns
+// s = 0..7 of filter row r.  A tensor map whose pixel stride (stride_w * 16 bytes) is smaller
+// than its 128-byte rows exposes exactly those overlapping windows, so the GEMM K dimension
+// becomes (r) x (s, c) = R x 32 and the generic kernels run with R "taps" and one chunk.
+bool smallc_ok(const mb_conv_desc* d) {
+  return d && d->groups == 1 && d->C <= 4 && d->S <= 8 && d->dil_w == 1 && d->dil_h == 1 &&
+         d->stride_h >= 1 && d->stride_h <= 2 && d->stride_w >= 1 && d->stride_w <= 2 &&
+         d->K % 4 == 0 && d->R <= kMaxTaps;
+}
+int smallc_Hp(const mb_conv_desc* d) { return d->H + 2 * d->pad_h; }
+int smallc_Wp(const mb_conv_desc* d) {
+  int need = d->stride_w * (d->Q - 1) + 8;           // last window must stay inside the row
+  const int full = d->W + 2 * d->pad_w;
+  if (need < full) need = full;
+  return (need + 3) / 4 * 4;
+}
+
+// Window view of phase `a` (rows a, a+stride_h, ...) of the padded input.
+int encode_smallc(const char* who, CUtensorMap* m, const float* xp, const mb_conv_desc* d, int a,
+                  int bw, int bh, int bn, CUtensorMapSwizzle sw) {
+  const long long Hp = smallc_Hp(d), Wp = smallc_Wp(d);
+  const long long Hv = (Hp - a + d->stride_h - 1) / d->stride_h;
+  return encode_act(who, m, xp + static_cast<long long>(a) * Wp * 4, 32, d->Q, Hv, d->N,
+                    16LL * d->stride_w, 16LL * Wp * d->stride_h, 16LL * Wp * Hp, bw, bh, bn, sw);
+}
+
+__global__ void __launch_bounds__(256) smallc_pack_input(const float* __restrict__ x,
+                                                         float* __restrict__ xp, int C, int H, int W,
+                                                         int ph, int pw, int Hp, int Wp,
+                                                         size_t total) {
+  // one thread per padded pixel: reads the C planes of the NCHW input, writes 4 floats
+  for (size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
+       t += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const int wq = static_cast<int>(t % Wp);
+    size_t r = t / Wp;
+    const int hq = static_cast<int>(r % Hp);
+    const size_t n = r / Hp;
+    const int h = hq - ph, w = wq - pw;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (h >= 0 && h < H && w >= 0 && w < W) {
+      const float* src = x + (n * C * H + h) * static_cast<size_t>(W) + w;
+      const size_t plane = static_cast<size_t>(H) * W;
+      v.x = __ldg(src);
+      if (C > 1) v.y = __ldg(src + plane);
+      if (C > 2) v.z = __ldg(src + 2 * plane);
+      if (C > 3) v.w = __ldg(src + 3 * plane);
+    }
+    reinterpret_cast<float4*>(xp)[t] = v;
+  }
 }
 
 }  // namespace mb
@@ -521,6 +585,105 @@ int mb_conv2d_wgrad(const float* x, const float* dy, float* dw, float* dbias,
   if (!aligned(x, 16) || !aligned(dy, 16) || !aligned(dw, 16))
     return fail(MB_ERR_INVALID_ARGUMENT, "%s: pointers must be 16-byte aligned", who);
   return wgrad_run(who, x, dy, dw, dbias, d, variant, workspace, workspace_bytes, as_stream(stream));
+}
+
+
+int mb_conv_smallc_geometry(const mb_conv_desc* d, int* Hp, int* Wp) {
+  if (!smallc_ok(d)) return MB_ERR_UNSUPPORTED;
+  if (Hp) *Hp = smallc_Hp(d);
+  if (Wp) *Wp = smallc_Wp(d);
+  return MB_OK;
+}
+
+int mb_conv_smallc_pack_input(const float* x_nchw, float* xp, const mb_conv_desc* d, void* stream) {
+  const char* who = "mb_conv_smallc_pack_input";
+  if (!smallc_ok(d)) return fail(MB_ERR_UNSUPPORTED, "%s: not a few-channel geometry", who);
+  if (!x_nchw || !xp || !aligned(xp, 16)) return fail(MB_ERR_INVALID_ARGUMENT, "%s: bad pointer", who);
+  const int Hp = smallc_Hp(d), Wp = smallc_Wp(d);
+  const size_t total = static_cast<size_t>(d->N) * Hp * Wp;
+  smallc_pack_input<<<grid_for(total, 256, 8), 256, 0, as_stream(stream)>>>(
+      x_nchw, xp, d->C, d->H, d->W, d->pad_h, d->pad_w, Hp, Wp, total);
+  return after_launch("conv_smallc_pack_input");
+}
+
+int mb_conv2d_fprop_smallc(const float* xp, const float* wp, const float* bias, float* y,
+                           const mb_conv_desc* d, void* stream) {
+  const char* who = "mb_conv2d_fprop_smallc";
+  if (!smallc_ok(d)) return fail(MB_ERR_UNSUPPORTED, "%s: not a few-channel geometry", who);
+  if (!xp || !wp || !y) return fail(MB_ERR_INVALID_ARGUMENT, "%s: null pointer", who);
+  if (!aligned(xp, 16) || !aligned(wp, 16) || !aligned(y, 16) || !aligned(bias, 16))
+    return fail(MB_ERR_INVALID_ARGUMENT, "%s: pointers must be 16-byte aligned", who);
+  GemmLaunch L;
+  std::memset(&L.p, 0, sizeof(L.p));
+  GemmParams& p = L.p;
+  p.out = y; p.bias = bias; p.Kout = d->K; p.kchunks = 1;
+  const TileShape ts = pick_tile(d->N, d->P, d->Q);
+  p.Nimg = d->N; p.P = d->P; p.Q = d->Q;
+  p.out_sw = d->K;
+  p.out_sh = static_cast<long long>(d->Q) * d->K;
+  p.out_sn = p.out_sh * d->P;
+  for (int r = 0; r < d->R; ++r) {
+    p.taps.dh[r] = static_cast<short>(r / d->stride_h);
+    p.taps.dw[r] = 0;
+    p.taps.map[r] = static_cast<unsigned char>(r % d->stride_h);
+    p.taps.btap[r] = static_cast<unsigned char>(r);
+  }
+  p.num_taps = d->R;
+  int rc;
+  for (int a = 0; a < 4; ++a) {
+    const int src = a < d->stride_h && a < d->R ? a : 0;
+    rc = encode_smallc(who, &L.a[a], xp, d, src, ts.bw, ts.bh, ts.bn, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+  }
+  p.bw = ts.bw; p.bh = ts.bh; p.bn = ts.bn;
+  p.tiles_w = (p.Q + ts.bw - 1) / ts.bw;
+  p.tiles_h = (p.P + ts.bh - 1) / ts.bh;
+  const long long m_tiles = static_cast<long long>(p.tiles_w) * p.tiles_h * ((p.Nimg + ts.bn - 1) / ts.bn);
+  pick_bn_stages(d->K, m_tiles, &p.BN, &p.stages, &L.smem);
+  p.tiles_c = (d->K + p.BN - 1) / p.BN;
+  const long long tiles = m_tiles * p.tiles_c;
+  if (tiles > 0x7fffffffLL) return fail(MB_ERR_UNSUPPORTED, "%s: too many tiles", who);
+  p.num_tiles = static_cast<int>(tiles);
+  rc = encode_filter(who, &L.b, wp, 32, d->R, d->K, p.BN);
+  if (rc) return rc;
+  L.grid = p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs;
+  return launch_gemm("conv_fprop_smallc_tcgen05", L, as_stream(stream));
+}
+
+size_t mb_conv_smallc_wgrad_workspace_bytes(const mb_conv_desc* d, int variant) {
+  if (!smallc_ok(d) || variant != 1) return 0;
+  wg::Plan pl;
+  if (!wg::make_plan(d, variant, &pl, true)) return 0;
+  return static_cast<size_t>(pl.p.splits) * d->K * d->R * 32 * sizeof(float);
+}
+
+int mb_conv2d_wgrad_smallc(const float* xp, const float* dy, float* dwp, float* dbias,
+                           const mb_conv_desc* d, int variant, void* workspace,
+                           size_t workspace_bytes, void* stream) {
+  const char* who = "mb_conv2d_wgrad_smallc";
+  if (!smallc_ok(d)) return fail(MB_ERR_UNSUPPORTED, "%s: not a few-channel geometry", who);
+  if (variant < 0 || variant > 1) return fail(MB_ERR_UNSUPPORTED, "%s: no variant %d", who, variant);
+  if (!xp || !dy || !dwp) return fail(MB_ERR_INVALID_ARGUMENT, "%s: null pointer", who);
+  if (!aligned(xp, 16) || !aligned(dy, 16) || !aligned(dwp, 16))
+    return fail(MB_ERR_INVALID_ARGUMENT, "%s: pointers must be 16-byte aligned", who);
+  const CUtensorMapSwizzle kWg = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
+  wg::Plan pl;
+  if (!wg::make_plan(d, variant, &pl, true))
+    return fail(MB_ERR_UNSUPPORTED, "%s: geometry not supported by the tensor-core kernel", who);
+  WgradParams& p = pl.p;
+  CUtensorMap mdy, mx[4];
+  const long long K4 = static_cast<long long>(d->K) * 4;
+  int rc = encode_act(who, &mdy, dy, d->K, d->Q, d->P, d->N, K4, K4 * d->Q, K4 * d->Q * d->P, p.bw,
+                      p.bh, p.bn, kWg);
+  if (rc) return rc;
+  for (int a = 0; a < 4; ++a) {
+    const int src = a < d->stride_h && a < d->R ? a : 0;
+    rc = encode_smallc(who, &mx[a], xp, d, src, p.bw, p.bh, p.bn, kWg);
+    if (rc) return rc;
+  }
+  const size_t dw_elems = static_cast<size_t>(d->K) * d->R * 32;
+  return wgrad_launch(who, pl, mdy, mx, dy, dwp, dw_elems, dbias, d, variant, workspace,
+                      workspace_bytes, as_stream(stream));
 }
 
 }  // extern "C"

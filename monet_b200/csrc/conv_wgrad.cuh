@@ -6,19 +6,24 @@
 // pixel x 32 channels (128 bytes).  For 32-bit MN-major operands the MMA only
 // accepts the 128-byte swizzle with a 32-byte base, so the wgrad tensor maps
 // use SWIZZLE_128B_ATOM_32B; four pixel rows form a 512-byte atom and one
-// K = 8 step consumes two of them.
+// K = 8 step consumes two of them.  Boxes of 32 channels sit back to back in
+// the slot, which is exactly the descriptor's leading-dimension stride, so ONE
+// MMA spans up to four dy boxes (M = 128) and up to eight x boxes (N = 256).
 //
-//   A  = dy tile : up to four boxes of 32 output channels (M = 128)
-//   B_u          : one box of 32 input channels of x, shifted by the filter
-//                  tap of "unit" u = (tap, 32-channel chunk); N = 32
-//   D_u          : 128 x 32 fp32 accumulator in tensor-memory columns 32u..
+//   A    = dy tile : KA boxes of 32 output channels (KA = 4 or 8 -> one or
+//                    two M = 128 halves)
+//   B_u            : one box of 32 input channels of x, shifted by the filter
+//                    tap of "unit" u = (tap, 32-channel chunk); eight units
+//                    form one N = 256 half
+//   D[mh][nh]      : 128 x 256 fp32 accumulators in tensor memory, at most two
+//                    (KA = 8 with up to 8 units, or KA = 4 with up to 16)
 //
-// One CTA owns a work item (tile of 128 output channels, group of up to U
-// units, range of pixel tiles) and keeps all U accumulators in tensor memory,
-// so the dy tile is loaded once and reused by every unit of the group.  The
-// pixel range is a split of the reduction; partial results are combined either
-// with red.global.add (variant 0, dw zeroed first) or through a workspace of
-// per-split partials and a deterministic reduction kernel (variant 1).
+// One CTA owns a work item (KA boxes of output channels, a group of U units, a
+// range of pixel tiles), so the CTA tile is 256 x 256 or 128 x 512 and each
+// operand byte fetched from L2 feeds 64 / 51 flop.  The pixel range is a split
+// of the reduction; partial results are combined either with red.global.add
+// (variant 0, dw zeroed first) or through a workspace of per-split partials
+// and a deterministic reduction kernel (variant 1).
 //
 // Pixel boxes always hold a multiple of 8 rows, and rows outside the image are
 // zero-filled by TMA in dy, so padding rows contribute nothing.
@@ -27,16 +32,15 @@
 
 namespace mb {
 
-constexpr int kWgMaxUnits = 12;     // accumulators (32 columns each) per CTA
-
 struct WgradParams {
   float* out;               // dw, or the partial-sum workspace
   long long split_stride;   // elements between the partials of two splits (0: atomics into dw)
   int K, C, T;              // output channels, input channels, filter taps R*S
   int ntaps;                // taps that touch the input at all
   int cchunks;              // ceil(C / 32)
-  int units, units_per_group, groups;
-  int k_tiles, splits;
+  int units, U, groups;     // units in total, per CTA, groups of units
+  int KA, k_tiles;          // dy boxes (of 32 channels) per CTA: 4 or 8
+  int splits;
   int bw, bh, bn, rows;     // pixel box, rows = bw*bh*bn (multiple of 8)
   int tiles_w, tiles_h;
   int pix_tiles;            // total pixel tiles
@@ -67,22 +71,24 @@ conv_wgrad_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_const
   wi /= p.splits;
   const int group = wi % p.groups;
   const int kt = wi / p.groups;
-  const int k0 = kt * kTileM;
-  const int u0 = group * p.units_per_group;
-  const int nu = (p.units - u0) < p.units_per_group ? (p.units - u0) : p.units_per_group;
-  int ka = (p.K - k0 + 31) / 32;          // boxes of 32 output channels that exist
-  if (ka > 4) ka = 4;
+  const int k0 = kt * p.KA * 32;
+  const int u0 = group * p.U;
+  const int nu = (p.units - u0) < p.U ? (p.units - u0) : p.U;
+  int ka = (p.K - k0 + 31) / 32;          // dy boxes that exist for this CTA
+  if (ka > p.KA) ka = p.KA;
+  const int mh_n = (ka + 3) / 4;          // M = 128 halves in use
+  const int nh_n = (nu + 7) / 8;          // N = 256 halves in use
+  const int NH = (p.U + 7) / 8;           // accumulator grid is [KA/4][NH]
   const int per = (p.pix_tiles + p.splits - 1) / p.splits;
   const int t_begin = split * per;
   const int t_end = (t_begin + per) < p.pix_tiles ? (t_begin + per) : p.pix_tiles;
   const int n_iter = t_end > t_begin ? t_end - t_begin : 0;
 
   const uint32_t box_bytes = static_cast<uint32_t>(p.rows) * 128u;
-  const uint32_t a_bytes = 4u * box_bytes;                 // slot layout is fixed: 4 A boxes
-  const uint32_t stage_bytes = a_bytes + static_cast<uint32_t>(p.units_per_group) * box_bytes;
+  const uint32_t a_bytes = static_cast<uint32_t>(p.KA) * box_bytes;     // fixed slot layout
+  const uint32_t stage_bytes = a_bytes + static_cast<uint32_t>(p.U) * box_bytes;
   const uint32_t tx_bytes = static_cast<uint32_t>(ka + nu) * box_bytes;
-  uint32_t tmem_cols = 32;
-  while (tmem_cols < 32u * p.units_per_group) tmem_cols <<= 1;
+  const uint32_t tmem_cols = 256u * (p.KA / 4) * NH;                     // 256 or 512
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
@@ -148,7 +154,6 @@ conv_wgrad_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_const
     }
   } else if (warp == 5) {
     if (lane == 0 && n_iter > 0) {
-      const uint32_t idesc = idesc_tf32(kTileM, 32, 1, 1);
       detail::Ring ring{0, 0u, p.stages};
       bool ok = true;
       const int ksteps = p.rows / 8;
@@ -159,13 +164,18 @@ conv_wgrad_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_const
         }
         tc_fence_after();
         const uint32_t a_addr = slots0 + static_cast<uint32_t>(ring.stage) * stage_bytes;
-        // A: 32-channel groups are box_bytes apart (LBO), 4-pixel atoms 512 bytes apart (SBO)
-        const uint64_t da = smem_desc(a_addr, box_bytes, 512, kSwizzle128BBase32B);
-        for (int u = 0; u < nu; ++u) {
-          const uint64_t db = smem_desc(a_addr + a_bytes + u * box_bytes, box_bytes, 512, kSwizzle128BBase32B);
-          const uint32_t d_tmem = tmem_base + 32u * u;
-          for (int k = 0; k < ksteps; ++k)   // 8 pixels = 1024 bytes (two atoms) per step
-            mma_tf32(d_tmem, da + 64u * k, db + 64u * k, idesc, (it | k) != 0 ? 1u : 0u);
+        for (int mh = 0; mh < mh_n; ++mh) {
+          // 32-channel boxes are box_bytes apart (LBO), 4-pixel atoms 512 bytes apart (SBO)
+          const uint64_t da = smem_desc(a_addr + mh * 4u * box_bytes, box_bytes, 512, kSwizzle128BBase32B);
+          for (int nh = 0; nh < nh_n; ++nh) {
+            const int n_units = (nu - 8 * nh) < 8 ? (nu - 8 * nh) : 8;
+            const uint32_t idesc = idesc_tf32(kTileM, 32 * n_units, 1, 1);
+            const uint64_t db = smem_desc(a_addr + a_bytes + nh * 8u * box_bytes, box_bytes, 512,
+                                          kSwizzle128BBase32B);
+            const uint32_t d_tmem = tmem_base + 256u * (mh * NH + nh);
+            for (int k = 0; k < ksteps; ++k)   // 8 pixels = 1024 bytes (two atoms) per step
+              mma_tf32(d_tmem, da + 64u * k, db + 64u * k, idesc, (it | k) != 0 ? 1u : 0u);
+          }
         }
         mma_commit(&empty[ring.stage]);
         ring.advance();
@@ -183,32 +193,35 @@ conv_wgrad_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_const
     got = __all_sync(0xffffffffu, got);
     if (got) {
       tc_fence_after();
-      const int k = k0 + warp * 32 + lane;
       float* base = p.out + static_cast<long long>(split) * p.split_stride;
-      for (int u = 0; u < nu; ++u) {
-        const int unit = u0 + u;
-        const int cc = unit / p.ntaps, ti = unit - cc * p.ntaps;
-        float v[32];
-        if (n_iter > 0) {
-          tmem_ld32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + 32u * u, v);
-          tmem_ld_wait();
-        } else {
+      for (int mh = 0; mh < mh_n; ++mh) {
+        const int k = k0 + mh * 128 + warp * 32 + lane;
+        for (int u = 0; u < nu; ++u) {
+          const int unit = u0 + u;
+          const int cc = unit / p.ntaps, ti = unit - cc * p.ntaps;
+          float v[32];
+          if (n_iter > 0) {
+            tmem_ld32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) +
+                          256u * (mh * NH + (u >> 3)) + 32u * (u & 7), v);
+            tmem_ld_wait();
+          } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = 0.f;
-        }
-        if (k < p.K) {
-          float* dst = base + (static_cast<long long>(k) * p.T + p.taps.btap[ti]) * p.C + cc * 32;
-          const int left = p.C - cc * 32;
+            for (int j = 0; j < 32; ++j) v[j] = 0.f;
+          }
+          if (k < p.K) {
+            float* dst = base + (static_cast<long long>(k) * p.T + p.taps.btap[ti]) * p.C + cc * 32;
+            const int left = p.C - cc * 32;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            if (4 * j < left) {
-              if (p.use_atomics) {
-                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * j),
-                             "f"(v[4 * j]), "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
-                             : "memory");
-              } else {
-                *reinterpret_cast<float4*>(dst + 4 * j) =
-                    make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            for (int j = 0; j < 8; ++j) {
+              if (4 * j < left) {
+                if (p.use_atomics) {
+                  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * j),
+                               "f"(v[4 * j]), "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
+                               : "memory");
+                } else {
+                  *reinterpret_cast<float4*>(dst + 4 * j) =
+                      make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                }
               }
             }
           }
@@ -273,17 +286,31 @@ inline int posmod_(int a, int b) { int m = a % b; return m < 0 ? m + b : m; }
 
 // Fills tap table, pixel box, unit grouping and split count.  Returns false if
 // the geometry is not supported.
-inline bool make_plan(const mb_conv_desc* d, int variant, Plan* pl) {
+// `smallc`: the few-channel layout where one "tap" is a whole filter row r and its 32
+// "channels" are the (s, c) pairs of a spatially pre-padded 4-channel input (see
+// mb_conv2d_wgrad_smallc); the gradient then has the shape [K][R][32].
+inline bool make_plan(const mb_conv_desc* d, int variant, Plan* pl, bool smallc = false) {
   WgradParams& p = pl->p;
   memset(&p, 0, sizeof(p));
   for (int i = 0; i < 4; ++i) pl->map_used[i] = 0;
-  p.K = d->K; p.C = d->C; p.T = d->R * d->S;
-  p.cchunks = (d->C + 31) / 32;
-  const bool flat = d->R == 1 && d->S == 1 && d->stride_h == 1 && d->stride_w == 1 &&
+  p.K = d->K; p.C = smallc ? 32 : d->C; p.T = smallc ? d->R : d->R * d->S;
+  p.cchunks = (p.C + 31) / 32;
+  const bool flat = !smallc && d->R == 1 && d->S == 1 && d->stride_h == 1 && d->stride_w == 1 &&
                     d->pad_h == 0 && d->pad_w == 0;
   pl->flat = flat;
   int nt = 0;
-  for (int r = 0; r < d->R; ++r) {
+  if (smallc) {
+    for (int r = 0; r < d->R; ++r) {     // the input is pre-padded: row r of the window is r itself
+      const int a = r % d->stride_h;
+      pl->map_used[a] = 1;
+      p.taps.dh[nt] = static_cast<short>(r / d->stride_h);
+      p.taps.dw[nt] = 0;
+      p.taps.map[nt] = static_cast<unsigned char>(a);
+      p.taps.btap[nt] = static_cast<unsigned char>(r);
+      ++nt;
+    }
+  }
+  for (int r = 0; !smallc && r < d->R; ++r) {
     const int oh = r * d->dil_h - d->pad_h;
     const int a = posmod_(oh, d->stride_h), dh = (oh - a) / d->stride_h;
     for (int s = 0; s < d->S; ++s) {
@@ -302,18 +329,17 @@ inline bool make_plan(const mb_conv_desc* d, int variant, Plan* pl) {
   if (nt == 0) return false;
   p.ntaps = nt;
   p.units = nt * p.cchunks;
-  // units per CTA: all taps of a channel chunk together when they fit
-  int U = nt <= kWgMaxUnits ? nt : kWgMaxUnits;
-  if (nt < kWgMaxUnits) {           // several chunks per group while they fit
-    U = (kWgMaxUnits / nt) * nt;
-    if (U > p.units) U = p.units;
-  }
-  p.units_per_group = U;
-  p.groups = (p.units + U - 1) / U;
-  p.k_tiles = (d->K + kTileM - 1) / kTileM;
-  // pixel box: rows multiple of 8, stage = (4 + U) * rows * 128 bytes, >= 2 stages
-  const int max_rows_smem = static_cast<int>((200 * 1024 / 2) / ((4 + U) * 128)) / 8 * 8;
-  int max_rows = max_rows_smem < 128 ? max_rows_smem : 128;
+  // CTA tile: 256 x 256 when there are more than 128 output channels, else 128 x 512
+  p.KA = d->K > 128 ? 8 : 4;
+  const int u_max = p.KA == 8 ? 8 : 16;
+  p.groups = (p.units + u_max - 1) / u_max;
+  p.U = (p.units + p.groups - 1) / p.groups;
+  p.groups = (p.units + p.U - 1) / p.U;
+  p.k_tiles = (d->K + 32 * p.KA - 1) / (32 * p.KA);
+  // pixel box: rows multiple of 8, slot = (KA + U) * rows * 128 bytes, at least 2 slots
+  const int boxes = p.KA + p.U;
+  int max_rows = static_cast<int>((212 * 1024 / 2) / (boxes * 128)) / 8 * 8;
+  if (max_rows > 128) max_rows = 128;
   if (max_rows < 8) return false;
   if (flat) {
     const long long pixels = static_cast<long long>(d->N) * d->P * d->Q;
@@ -323,27 +349,33 @@ inline bool make_plan(const mb_conv_desc* d, int variant, Plan* pl) {
     p.tiles_h = 1;
     p.pix_tiles = p.tiles_w;
   } else {
-    // widest run along w (<= 64), then rows of h until bw*bh is a multiple of 8
-    int bw = d->Q < 64 ? d->Q : 64;
-    if (d->Q > 64) bw = 56;
-    int bh = 1;
-    while ((bw * bh) % 8) ++bh;
-    if (bw * bh > max_rows) {       // fall back to a run of 8k pixels along w
-      bw = max_rows < 64 ? max_rows : 64;
-      bw = bw / 8 * 8;
-      bh = 1;
-    } else {
-      while (bw * bh * 2 <= max_rows && bw * bh * 2 <= 64 && bh * 2 <= d->P) bh *= 2;
-    }
-    p.bw = bw; p.bh = bh; p.bn = 1;
-    p.tiles_w = (d->Q + bw - 1) / bw;
-    p.tiles_h = (d->P + bh - 1) / bh;
-    const long long tiles = static_cast<long long>(p.tiles_w) * p.tiles_h * d->N;
+    // exhaustive search over boxes {bw, bh, bn}: highest fraction of real pixels per
+    // loaded row, larger boxes on ties; bh may exceed P (rows past the image are zero)
+    double best = -1.0;
+    const int cap = max_rows < 64 ? max_rows : 64;
+    for (int bn = 1; bn <= 4 && bn <= d->N; ++bn)
+      for (int bh = 1; bh <= d->P + 7 && bh <= 64; ++bh)
+        for (int bw = 1; bw <= d->Q && bw <= 128; ++bw) {
+          const int rows = bw * bh * bn;
+          if (rows % 8 || rows > cap) continue;
+          if (bn > 1 && bh < d->P) continue;       // several images only with whole images
+          const double tiles = static_cast<double>((d->Q + bw - 1) / bw) * ((d->P + bh - 1) / bh) *
+                               ((d->N + bn - 1) / bn);
+          const double score = static_cast<double>(d->N) * d->P * d->Q / (tiles * rows) + 1e-3 * rows / 128.0;
+          if (score > best) {
+            best = score;
+            p.bw = bw; p.bh = bh; p.bn = bn;
+          }
+        }
+    if (best < 0) return false;
+    p.tiles_w = (d->Q + p.bw - 1) / p.bw;
+    p.tiles_h = (d->P + p.bh - 1) / p.bh;
+    const long long tiles = static_cast<long long>(p.tiles_w) * p.tiles_h * ((d->N + p.bn - 1) / p.bn);
     if (tiles > 0x7fffffffLL) return false;
     p.pix_tiles = static_cast<int>(tiles);
   }
   p.rows = p.bw * p.bh * p.bn;
-  const size_t stage = static_cast<size_t>(4 + U) * p.rows * 128;
+  const size_t stage = static_cast<size_t>(boxes) * p.rows * 128;
   int st = static_cast<int>((216 * 1024) / stage);
   if (st > 8) st = 8;
   if (st < 2) return false;

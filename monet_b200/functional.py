@@ -502,10 +502,42 @@ def _workspace(conv_pass: int, variant: int, d: ConvDesc, device) -> torch.Tenso
     return torch.empty(max(n, 16), dtype=torch.uint8, device=device)
 
 
+def _smallc_geometry(d: ConvDesc):
+    """(Hp, Wp) of the padded 4-channel input when the few-channel kernels apply, else None."""
+    if d.C > 4 or d.K % 4 or d.groups != 1:
+        return None
+    hp, wp = C.c_int(0), C.c_int(0)
+    if lib().mb_conv_smallc_geometry(C.byref(d), C.byref(hp), C.byref(wp)) != 0:
+        return None
+    return hp.value, wp.value
+
+
+def _smallc_input(x: torch.Tensor, d: ConvDesc, geom) -> torch.Tensor:
+    xc = x.detach().contiguous()
+    xp = torch.empty((d.N, geom[0], geom[1], 4), dtype=x.dtype, device=x.device)
+    check(lib().mb_conv_smallc_pack_input(xc.data_ptr(), xp.data_ptr(), C.byref(d), _stream()),
+          "conv_smallc_pack_input")
+    return xp
+
+
 def conv2d_fprop(x, w, bias, stride, padding, dilation, groups=1, variant: int = 0):
     """y = conv2d(x, w) + bias; y is a channels_last tensor of logical shape N x K x P x Q."""
     _need_cuda(x, w, bias); _f32(x, "x"); _f32(w, "w")
     d0 = conv_desc(x.shape, w.shape, stride, padding, dilation, groups)
+    geom = _smallc_geometry(d0)
+    if geom is not None:
+        if variant != 0:
+            raise RuntimeError("monet_b200.conv2d_fprop: no variant %d for a few-channel input" % variant)
+        xp = _smallc_input(x, d0, geom)
+        wp = torch.zeros((d0.K, d0.R, 8, 4), dtype=w.dtype, device=w.device)
+        wp[:, :, :d0.S, :d0.C] = w.detach().permute(0, 2, 3, 1)
+        y = torch.empty((d0.N, d0.K, d0.P, d0.Q), dtype=x.dtype, device=x.device,
+                        memory_format=torch.channels_last)
+        b = bias.detach().contiguous() if bias is not None else None
+        check(lib().mb_conv2d_fprop_smallc(xp.data_ptr(), wp.data_ptr(),
+                                           b.data_ptr() if b is not None else None, y.data_ptr(),
+                                           C.byref(d0), _stream()), "conv2d_fprop_smallc")
+        return y
     d = _padded_desc(d0)
     xa, wk = _act_nhwc(x), _filter_krsc(w)
     b = None
@@ -546,6 +578,19 @@ def conv2d_wgrad(x, dy, w_shape, stride, padding, dilation, groups=1, variant: i
     d = _padded_desc(d0)
     if tuple(dy.shape) != (d0.N, d0.K, d0.P, d0.Q):
         raise RuntimeError("monet_b200.conv2d_wgrad: gradient shape does not match the geometry")
+    geom = _smallc_geometry(d0)
+    if geom is not None:
+        xp = _smallc_input(x, d0, geom)
+        ga = to_nhwc(dy)
+        dwp = torch.empty((d0.K, d0.R, 8, 4), dtype=x.dtype, device=x.device)
+        db = torch.empty(d0.K, dtype=x.dtype, device=x.device) if need_bias else None
+        n = lib().mb_conv_smallc_wgrad_workspace_bytes(C.byref(d0), int(variant))
+        ws = torch.empty(max(n, 16), dtype=torch.uint8, device=x.device)
+        check(lib().mb_conv2d_wgrad_smallc(xp.data_ptr(), ga.data_ptr(), dwp.data_ptr(),
+                                           db.data_ptr() if db is not None else None,
+                                           C.byref(d0), int(variant), ws.data_ptr(), ws.numel(),
+                                           _stream()), "conv2d_wgrad_smallc")
+        return dwp[:, :, :d0.S, :d0.C].permute(0, 3, 1, 2), db
     xa, ga = _act_nhwc(x), _act_nhwc(dy)
     dw = torch.empty((d.K, d.C, d.R, d.S), dtype=x.dtype, device=x.device,
                      memory_format=torch.channels_last)

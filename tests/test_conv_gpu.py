@@ -23,7 +23,10 @@ CASES = [
     (2, 128, 14, 14, 256, 1, 2, 0, 1),   # 1x1 stride 2 (downsample)
     (2, 32, 13, 13, 32, 3, 1, 2, 2),     # dilation 2
     (1, 4, 20, 20, 8, 5, 1, 2, 1),       # 5x5
-    (2, 3, 32, 32, 64, 7, 2, 3, 1),      # the stem geometry: C = 3 padded to 4
+    (2, 3, 32, 32, 64, 7, 2, 3, 1),      # the stem geometry: few-channel kernels
+    (3, 3, 37, 41, 32, 7, 2, 3, 1),      # stem, odd extents
+    (2, 1, 20, 20, 16, 5, 1, 2, 1),      # one input channel, stride 1
+    (2, 4, 18, 18, 24, 3, 2, 1, 1),      # four input channels
     (2, 16, 9, 9, 2, 1, 1, 0, 1),        # K = 2 padded to 4
     (1, 260, 5, 5, 36, 1, 1, 0, 1),      # C spans several 32-channel chunks with a tail
 ]
