@@ -179,12 +179,14 @@ def run_ours(args):
     model = torchvision.models.resnet50().to(dev).train()
     model = model.to(memory_format=torch.channels_last)       # filters as [K][R][S][C]
     params = [p for p in model.parameters()]
-    flat = torch.zeros(sum(p.numel() for p in params), device=dev)    # gradient bucket
-    off = 0
-    for p in params:
-        p.grad = flat[off:off + p.numel()].view(p.shape)
-        off += p.numel()
     opt = torch.optim.SGD(params, lr=0.1, momentum=0.9)
+    flat, views = None, None
+    if world > 1:                      # one flat bucket for the NCCL all-reduce of the gradients
+        flat = torch.zeros(sum(p.numel() for p in params), device=dev)
+        views, off = [], 0
+        for p in params:
+            views.append(flat[off:off + p.numel()].view(p.shape))
+            off += p.numel()
     policy = getattr(runner, args.schedule)
     run = runner.Runner(model, policy)
     ce = SoftmaxCrossEntropy()
@@ -197,13 +199,17 @@ def run_ours(args):
     y_dev = y_host.to(dev)
 
     def step(x, y):
-        flat.zero_()
+        for p in params:
+            p.grad = None              # the backward hands over freshly written gradients
         out = run.forward(x)
         loss = ce.forward(out, y)
         run.backward(ce.backward())
         if world > 1:
+            torch._foreach_copy_(views, [p.grad for p in params])
             dist.all_reduce(flat)
             flat.div_(world)
+            for p, v in zip(params, views):
+                p.grad = v
         opt.step()
         return loss
 

@@ -9,8 +9,8 @@
 //            writes one partial per channel to the workspace  ws[2][S][C].
 //            Many CTAs per channel: a 64-channel layer still fills 148 SMs
 //            (the reference runs one CTA per channel, lrbn.cu:228-232).
-//   finalize one warp-column per channel sums the S partials in fp64 and writes
-//            the per-channel constants the sweep needs.
+//   finalize 32 channels x 32 stripes per CTA sum the S partials (fp64 at the end)
+//            and write the per-channel constants the sweep needs.
 //   sweep    element-wise, 128-bit, grid-stride.
 //
 // Forward statistics are accumulated around a per-channel shift K = the first
@@ -60,7 +60,7 @@ Geometry make_geometry(const mb_bn_desc* d) {
     size_t want = (g.M + rows_per_cta_min - 1) / rows_per_cta_min;
     size_t cap = static_cast<size_t>(kNumSMs) * 6 / g.slabs;
     if (cap < 1) cap = 1;
-    g.S = static_cast<int>(want < cap ? want : cap);
+    g.S = static_cast<int>(want < cap ? want : cap);   // at most 888 partials per channel
   } else {
     g.vec = 1;
     g.tx = g.ty = 0;
@@ -244,32 +244,43 @@ __global__ void __launch_bounds__(kBlock) bn_reduce_nchw(const float* __restrict
 }
 
 // ---------------------------------------------------------------- finalize
-// block (32 channels, 8 chunk stripes); fp64 accumulation of the partials.
+// block = 32 channels (lanes) x 32 chunk stripes (warps).  Every thread sums its stripe
+// of the S partials with four independent loads in flight (the loop is latency-bound:
+// one dependent chain over all S partials costs tens of microseconds), then the 32
+// stripes of a channel are combined in fp64 through shared memory.
+constexpr int kFinStripes = 32;
 template <int MODE>
-__global__ void __launch_bounds__(256) bn_finalize(const float* __restrict__ ws_part,
-                                                   float* __restrict__ ws_const,
-                                                   const float* __restrict__ first_elems,
-                                                   size_t first_stride, int C, size_t M, int S,
-                                                   float eps, float momentum,
-                                                   float* __restrict__ running_mean,
-                                                   float* __restrict__ running_var,
-                                                   float* __restrict__ out0,
-                                                   float* __restrict__ out1) {
-  __shared__ double red[2][8][32];
+__global__ void __launch_bounds__(32 * kFinStripes) bn_finalize(
+    const float* __restrict__ ws_part, float* __restrict__ ws_const,
+    const float* __restrict__ first_elems, size_t first_stride, int C, size_t M, int S, float eps,
+    float momentum, float* __restrict__ running_mean, float* __restrict__ running_var,
+    float* __restrict__ out0, float* __restrict__ out1) {
+  __shared__ double red[2][kFinStripes][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + tx;
-  double s1 = 0.0, s2 = 0.0;
+  float a1[4] = {0.f, 0.f, 0.f, 0.f}, a2[4] = {0.f, 0.f, 0.f, 0.f};
   if (c < C) {
-    for (int s = ty; s < S; s += 8) {
-      s1 += static_cast<double>(ws_part[static_cast<size_t>(s) * C + c]);
-      s2 += static_cast<double>(ws_part[(static_cast<size_t>(S) + s) * C + c]);
+    const float* p1 = ws_part + c;
+    const float* p2 = ws_part + static_cast<size_t>(S) * C + c;
+    int s = ty;
+    for (; s + 3 * kFinStripes < S; s += 4 * kFinStripes) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        a1[j] += __ldg(p1 + static_cast<size_t>(s + j * kFinStripes) * C);
+        a2[j] += __ldg(p2 + static_cast<size_t>(s + j * kFinStripes) * C);
+      }
+    }
+    for (; s < S; s += kFinStripes) {
+      a1[0] += __ldg(p1 + static_cast<size_t>(s) * C);
+      a2[0] += __ldg(p2 + static_cast<size_t>(s) * C);
     }
   }
-  red[0][ty][tx] = s1;
-  red[1][ty][tx] = s2;
+  red[0][ty][tx] = (static_cast<double>(a1[0]) + a1[1]) + (static_cast<double>(a1[2]) + a1[3]);
+  red[1][ty][tx] = (static_cast<double>(a2[0]) + a2[1]) + (static_cast<double>(a2[2]) + a2[3]);
   __syncthreads();
   if (ty == 0 && c < C) {
-    for (int j = 1; j < 8; ++j) {
+    double s1 = 0.0, s2 = 0.0;
+    for (int j = 0; j < kFinStripes; ++j) {
       s1 += red[0][j][tx];
       s2 += red[1][j][tx];
     }
@@ -472,7 +483,7 @@ int bwd_common(const char* who, const float* dy, const float* v, const float* ga
   cudaStream_t st = as_stream(stream);
   rc = run_reduce<kBwd>("bn_bwd_reduce", d, g, dy, v, p0v, p1v, p1_is_gamma, ws, st);
   if (rc) return rc;
-  bn_finalize<kBwd><<<(g.C + 31) / 32, 256, 0, st>>>(ws, ws_const, nullptr, 0, g.C, g.M, g.S, 0.f,
+  bn_finalize<kBwd><<<(g.C + 31) / 32, 32 * kFinStripes, 0, st>>>(ws, ws_const, nullptr, 0, g.C, g.M, g.S, 0.f,
                                                     0.f, nullptr, nullptr, dgamma, dbeta);
   rc = after_launch("bn_bwd_finalize");
   if (rc) return rc;
@@ -511,7 +522,7 @@ int mb_bn_fwd_train(const float* x, const float* gamma, const float* beta, float
   rc = run_reduce<kFwd>("bn_fwd_reduce", d, g, x, nullptr, nullptr, nullptr, 0, ws, st);
   if (rc) return rc;
   const size_t first_stride = d->layout == MB_NHWC ? 1 : static_cast<size_t>(d->HW);
-  bn_finalize<kFwd><<<(g.C + 31) / 32, 256, 0, st>>>(ws, nullptr, x, first_stride, g.C, g.M, g.S,
+  bn_finalize<kFwd><<<(g.C + 31) / 32, 32 * kFinStripes, 0, st>>>(ws, nullptr, x, first_stride, g.C, g.M, g.S,
                                                     d->eps, d->momentum, running_mean,
                                                     running_var, save_mean, save_invstd);
   rc = after_launch("bn_fwd_finalize");
