@@ -13,6 +13,7 @@
 //   wgrad  dw = x (*) dy, db = sum dy   see conv_wgrad.cuh
 #include "conv_gemm.cuh"
 #include "conv_wgrad.cuh"
+#include "conv_wgrad_halo.cuh"
 
 #include <cstring>
 #include <mutex>
@@ -196,39 +197,36 @@ __global__ void __launch_bounds__(256) transpose_filter(const float* __restrict_
 
 namespace mb {
 
-// Shared tail of the two wgrad entry points: zero / workspace set-up, launch, reduction.
-int wgrad_launch(const char* who, wg::Plan& pl, const CUtensorMap& mdy, const CUtensorMap* mx,
-                 const float* dy, float* dw, size_t dw_elems, float* dbias, const mb_conv_desc* d,
-                 int variant, void* workspace, size_t workspace_bytes, cudaStream_t st) {
-  WgradParams& p = pl.p;
-  int rc;
+// Shared head and tail of the wgrad entry points.  `prepare` zeroes dw (variant 0) or checks
+// the partial-sum workspace (variant 1) and says where the kernel writes; `finish` reduces the
+// partials and computes the bias gradient.
+int wgrad_prepare(const char* who, int variant, int splits, bool all_taps_written, float* dw,
+                  size_t dw_elems, void* workspace, size_t workspace_bytes, cudaStream_t st,
+                  float** out, long long* split_stride) {
   if (variant == 0) {
     if (cudaMemsetAsync(dw, 0, dw_elems * sizeof(float), st) != cudaSuccess)
       return fail(MB_ERR_LAUNCH, "%s: memset failed", who);
-    p.out = dw;
-    p.split_stride = 0;
-  } else {
-    const size_t need = static_cast<size_t>(p.splits) * dw_elems * sizeof(float);
-    if (!workspace || workspace_bytes < need || !aligned(workspace, 16))
-      return fail(MB_ERR_WORKSPACE, "%s: workspace of %zu bytes needed, %zu given", who, need,
-                  workspace ? workspace_bytes : size_t(0));
-    if (p.ntaps < p.T && cudaMemsetAsync(workspace, 0, need, st) != cudaSuccess)
-      return fail(MB_ERR_LAUNCH, "%s: memset failed", who);
-    p.out = static_cast<float*>(workspace);
-    p.split_stride = static_cast<long long>(dw_elems);
+    *out = dw;
+    *split_stride = 0;
+    return MB_OK;
   }
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(conv_wgrad_tcgen05, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-  });
-  if (attr_err != cudaSuccess)
-    return fail(MB_ERR_LAUNCH, "%s: cannot raise the shared-memory limit: %s", who, cudaGetErrorString(attr_err));
-  conv_wgrad_tcgen05<<<pl.grid, 192, pl.smem, st>>>(mdy, mx[0], mx[1], mx[2], mx[3], p);
-  rc = after_launch("conv_wgrad_tcgen05");
-  if (rc) return rc;
+  const size_t need = static_cast<size_t>(splits) * dw_elems * sizeof(float);
+  if (!workspace || workspace_bytes < need || !aligned(workspace, 16))
+    return fail(MB_ERR_WORKSPACE, "%s: workspace of %zu bytes needed, %zu given", who, need,
+                workspace ? workspace_bytes : size_t(0));
+  if (!all_taps_written && cudaMemsetAsync(workspace, 0, need, st) != cudaSuccess)
+    return fail(MB_ERR_LAUNCH, "%s: memset failed", who);
+  *out = static_cast<float*>(workspace);
+  *split_stride = static_cast<long long>(dw_elems);
+  return MB_OK;
+}
+
+int wgrad_finish(const char* who, int variant, int splits, const float* dy, float* dw,
+                 size_t dw_elems, float* dbias, const mb_conv_desc* d, const void* workspace,
+                 cudaStream_t st) {
+  int rc;
   if (variant == 1) {
-    wgrad_reduce_splits<<<grid_for(dw_elems, 256, 8), 256, 0, st>>>(static_cast<const float*>(workspace), dw, dw_elems, p.splits);
+    wgrad_reduce_splits<<<grid_for(dw_elems, 256, 8), 256, 0, st>>>(static_cast<const float*>(workspace), dw, dw_elems, splits);
     rc = after_launch("conv_wgrad_reduce");
     if (rc) return rc;
   }
@@ -247,10 +245,64 @@ int wgrad_launch(const char* who, wg::Plan& pl, const CUtensorMap& mdy, const CU
   return MB_OK;
 }
 
+template <class Kernel>
+int raise_smem_limit(const char* who, Kernel kernel) {
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (e != cudaSuccess)
+    return fail(MB_ERR_LAUNCH, "%s: cannot raise the shared-memory limit: %s", who, cudaGetErrorString(e));
+  return MB_OK;
+}
+
+int wgrad_launch(const char* who, wg::Plan& pl, const CUtensorMap& mdy, const CUtensorMap* mx,
+                 const float* dy, float* dw, size_t dw_elems, float* dbias, const mb_conv_desc* d,
+                 int variant, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  WgradParams& p = pl.p;
+  int rc = wgrad_prepare(who, variant, p.splits, p.ntaps >= p.T, dw, dw_elems, workspace,
+                         workspace_bytes, st, &p.out, &p.split_stride);
+  if (rc) return rc;
+  static const int attr_rc = raise_smem_limit(who, conv_wgrad_tcgen05);
+  if (attr_rc) return attr_rc;
+  conv_wgrad_tcgen05<<<pl.grid, 192, pl.smem, st>>>(mdy, mx[0], mx[1], mx[2], mx[3], p);
+  rc = after_launch("conv_wgrad_tcgen05");
+  if (rc) return rc;
+  return wgrad_finish(who, variant, p.splits, dy, dw, dw_elems, dbias, d, workspace, st);
+}
+
+// Stride-1 multi-tap filters: the halo kernel (one x box per tile, taps by descriptor offset).
+int wgrad_run_halo(const char* who, wgh::Plan& pl, const float* x, const float* dy, float* dw,
+                   float* dbias, const mb_conv_desc* d, int variant, void* workspace,
+                   size_t workspace_bytes, cudaStream_t st) {
+  const CUtensorMapSwizzle kWg = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
+  WgHaloParams& p = pl.p;
+  const size_t dw_elems = static_cast<size_t>(d->K) * d->R * d->S * d->C;
+  int rc = wgrad_prepare(who, variant, p.splits, true, dw, dw_elems, workspace, workspace_bytes, st,
+                         &p.out, &p.split_stride);
+  if (rc) return rc;
+  CUtensorMap mdy, mx;
+  const long long K4 = static_cast<long long>(d->K) * 4, C4 = static_cast<long long>(d->C) * 4;
+  rc = encode_act(who, &mdy, dy, d->K, d->Q, d->P, d->N, K4, K4 * d->Q, K4 * d->Q * d->P, p.Wh, p.bh,
+                  1, kWg);
+  if (rc) return rc;
+  rc = encode_act(who, &mx, x, d->C, d->W, d->H, d->N, C4, C4 * d->W, C4 * d->W * d->H, p.Wh, p.bhB,
+                  1, kWg);
+  if (rc) return rc;
+  static const int attr_rc = raise_smem_limit(who, conv_wgrad_halo_tcgen05);
+  if (attr_rc) return attr_rc;
+  conv_wgrad_halo_tcgen05<<<pl.grid, 192, pl.smem, st>>>(mdy, mx, p);
+  rc = after_launch("conv_wgrad_halo_tcgen05");
+  if (rc) return rc;
+  return wgrad_finish(who, variant, p.splits, dy, dw, dw_elems, dbias, d, workspace, st);
+}
+
 int wgrad_run(const char* who, const float* x, const float* dy, float* dw, float* dbias,
               const mb_conv_desc* d, int variant, void* workspace, size_t workspace_bytes,
               cudaStream_t st) {
   const CUtensorMapSwizzle kWg = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;   // MN-major TF32 operands
+  {
+    wgh::Plan hp;
+    if (wgh::make_plan(d, variant, &hp))
+      return wgrad_run_halo(who, hp, x, dy, dw, dbias, d, variant, workspace, workspace_bytes, st);
+  }
   wg::Plan pl;
   if (!wg::make_plan(d, variant, &pl))
     return fail(MB_ERR_UNSUPPORTED, "%s: geometry not supported by the tensor-core kernel", who);

@@ -396,13 +396,6 @@ inline bool make_plan(const mb_conv_desc* d, int variant, Plan* pl, bool smallc 
 
 }  // namespace wg
 
-inline size_t wgrad_workspace_bytes(const mb_conv_desc* d, int variant) {
-  if (variant != 1) return 0;
-  wg::Plan pl;
-  if (d->groups != 1 || !wg::make_plan(d, variant, &pl)) return 0;
-  return static_cast<size_t>(pl.p.splits) * d->K * d->R * d->S * d->C * sizeof(float);
-}
-
 // Defined in conv.cu (needs the tensor-map helpers).
 int wgrad_run(const char* who, const float* x, const float* dy, float* dw, float* dbias,
               const mb_conv_desc* d, int variant, void* workspace, size_t workspace_bytes,

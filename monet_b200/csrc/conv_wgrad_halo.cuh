@@ -1,0 +1,313 @@
+// Backward-weight for stride-1 filters with several taps (3x3, 5x5, dilated...):
+// the input tile is fetched ONCE with its halo and every filter tap reads it
+// through a shifted shared-memory descriptor.
+//
+// Both operands are laid out in "halo-width" pixel order: a pixel row index is
+//     i = h * Wh + w,   Wh = Q + (S-1)*dil_w   (output width plus the halo)
+// The dy box {32 ch, Wh, bh} is loaded at w = 0, so its columns w >= Q are
+// out of bounds and arrive as zeros; the x box {32 ch, Wh, bh + (R-1)*dil_h}
+// is loaded at (-pad_w, p0 - pad_h).  For tap (r, s) the input pixel paired
+// with dy row i is simply x row i + r*dil_h*Wh + s*dil_w: a start-address
+// offset of whole 128-byte rows, which the address-based swizzle of the MMA
+// accepts unchanged.  The S taps of one filter row are dil_w rows apart, which
+// is a legal leading-dimension stride, so ONE MMA (N = 32*S) covers a filter
+// row and writes the accumulators of its S taps side by side.
+//
+// Compared with fetching one shifted x box per tap this cuts the x traffic
+// from R*S boxes to (bh + halo)/bh boxes per tile.
+//
+// Work item: (128 output channels, one 32-channel chunk of x, a range of pixel
+// tiles); tensor memory holds the R*S accumulators of 128 x 32.  Rows that pad
+// a box up to a multiple of 8 (the MMA's K step) are zeroed once at kernel
+// start and never written again.
+#pragma once
+#include "conv_wgrad.cuh"
+
+namespace mb {
+
+struct WgHaloParams {
+  float* out;
+  long long split_stride;
+  int K, C, T;              // output channels, input channels, taps R*S
+  int R, S;
+  int tap_row_pitch;        // rows between filter rows: dil_h * Wh
+  int tap_col_pitch;        // rows between filter columns: dil_w
+  int cchunks, k_tiles, splits;
+  int Wh, bh;               // box width (pixels incl. halo) and output rows per tile
+  int rowsA, rowsA_alloc;   // dy box rows (Wh*bh) and its allocation (multiple of 8)
+  int rowsB, rowsB_alloc;   // x box rows (Wh*(bh+(R-1)*dil_h)) and its allocation
+  int bhB;                  // x box height
+  int tiles_h, pix_tiles;
+  int pad_h, pad_w;
+  int stages;
+  int use_atomics;
+};
+
+__global__ void __launch_bounds__(192, 1)
+conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_constant__ CUtensorMap mapX,
+                        const __grid_constant__ WgHaloParams p) {
+  using namespace sm100;
+  extern __shared__ uint8_t smem_raw[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw);
+  uint64_t* empty = full + 16;
+  uint64_t* acc_full = empty + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t slots0 = (smem_u32(smem_raw) + 512u + 1023u) & ~1023u;
+  uint8_t* slots_ptr = smem_raw + (slots0 - smem_u32(smem_raw));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  int wi = blockIdx.x;
+  const int split = wi % p.splits;
+  wi /= p.splits;
+  const int cc = wi % p.cchunks;
+  const int kt = wi / p.cchunks;
+  const int k0 = kt * kTileM;
+  int ka = (p.K - k0 + 31) / 32;
+  if (ka > 4) ka = 4;
+  const int per = (p.pix_tiles + p.splits - 1) / p.splits;
+  const int t_begin = split * per;
+  const int t_end = (t_begin + per) < p.pix_tiles ? (t_begin + per) : p.pix_tiles;
+  const int n_iter = t_end > t_begin ? t_end - t_begin : 0;
+
+  const uint32_t a_box = static_cast<uint32_t>(p.rowsA_alloc) * 128u;
+  const uint32_t a_bytes = 4u * a_box;
+  const uint32_t b_bytes = static_cast<uint32_t>(p.rowsB_alloc) * 128u;
+  const uint32_t stage_bytes = a_bytes + b_bytes;
+  const uint32_t tx_bytes = static_cast<uint32_t>(ka * p.rowsA + p.rowsB) * 128u;
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < 32u * p.T) tmem_cols <<= 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(&acc_full[0], 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  // zero the padding rows of every slot (TMA never touches them)
+  for (int s = 0; s < p.stages; ++s) {
+    uint8_t* slot = slots_ptr + static_cast<size_t>(s) * stage_bytes;
+    const int padA = (p.rowsA_alloc - p.rowsA) * 32;          // floats per box
+    for (int j = 0; j < 4; ++j) {
+      float* z = reinterpret_cast<float*>(slot + j * a_box + p.rowsA * 128);
+      for (int i = threadIdx.x; i < padA; i += blockDim.x) z[i] = 0.f;
+    }
+    float* zb = reinterpret_cast<float*>(slot + a_bytes + p.rowsB * 128);
+    const int padB = (p.rowsB_alloc - p.rowsB) * 32;
+    for (int i = threadIdx.x; i < padB; i += blockDim.x) zb[i] = 0.f;
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // visible to the tensor core
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    if (lane == 0 && n_iter > 0) {
+      prefetch_tensormap(&mapDy);
+      prefetch_tensormap(&mapX);
+      detail::Ring ring{0, 0u, p.stages};
+      uint32_t armed[16];
+      for (int s = 0; s < 16; ++s) armed[s] = 0;
+      bool ok = true;
+      for (int t = t_begin; ok && t < t_end; ++t) {
+        const int ht = t % p.tiles_h, n0 = t / p.tiles_h;
+        const int p0 = ht * p.bh;
+        if (!mbar_wait(&empty[ring.stage], ring.phase ^ 1u, abort_flag)) {
+          ok = false;
+          break;
+        }
+        uint8_t* slot = slots_ptr + static_cast<size_t>(ring.stage) * stage_bytes;
+        mbar_arrive_expect_tx(&full[ring.stage], tx_bytes);
+        armed[ring.stage] = 1u + ring.phase;
+        for (int j = 0; j < ka; ++j)
+          tma_load_4d(&mapDy, slot + j * a_box, &full[ring.stage], k0 + 32 * j, 0, p0, n0);
+        tma_load_4d(&mapX, slot + a_bytes, &full[ring.stage], cc * 32, -p.pad_w, p0 - p.pad_h, n0);
+        ring.advance();
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        atomicCAS(&g_conv_status, 0, 21);
+        for (int s = 0; s < p.stages; ++s) {
+          if (!armed[s]) continue;
+          const long long t0 = clock64();
+          while (!mbar_try_wait(&full[s], armed[s] - 1u) && clock64() - t0 < 20000000LL) {
+          }
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0 && n_iter > 0) {
+      detail::Ring ring{0, 0u, p.stages};
+      bool ok = true;
+      const int ksteps = p.rowsA_alloc / 8;
+      const uint32_t idesc = idesc_tf32(kTileM, 32 * p.S, 1, 1);
+      for (int it = 0; it < n_iter; ++it) {
+        if (!mbar_wait(&full[ring.stage], ring.phase, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t a_addr = slots0 + static_cast<uint32_t>(ring.stage) * stage_bytes;
+        const uint64_t da = smem_desc(a_addr, a_box, 512, kSwizzle128BBase32B);
+        for (int r = 0; r < p.R; ++r) {
+          // the S taps of filter row r: column groups tap_col_pitch rows apart (the LBO)
+          const uint64_t db = smem_desc(a_addr + a_bytes + static_cast<uint32_t>(r * p.tap_row_pitch) * 128u,
+                                        static_cast<uint32_t>(p.tap_col_pitch) * 128u, 512,
+                                        kSwizzle128BBase32B);
+          const uint32_t d_tmem = tmem_base + 32u * (r * p.S);
+          for (int k = 0; k < ksteps; ++k)
+            mma_tf32(d_tmem, da + 64u * k, db + 64u * k, idesc, (it | k) != 0 ? 1u : 0u);
+        }
+        mma_commit(&empty[ring.stage]);
+        ring.advance();
+      }
+      if (ok) {
+        mma_commit(&acc_full[0]);
+      } else {
+        *abort_flag = 1;
+        atomicCAS(&g_conv_status, 0, 22);
+      }
+    }
+  } else if (n_iter > 0 || !p.use_atomics) {
+    bool got = n_iter > 0 ? mbar_wait(&acc_full[0], 0, abort_flag) : true;
+    got = __all_sync(0xffffffffu, got);
+    if (got) {
+      tc_fence_after();
+      float* base = p.out + static_cast<long long>(split) * p.split_stride;
+      const int k = k0 + warp * 32 + lane;
+      for (int t = 0; t < p.T; ++t) {
+        float v[32];
+        if (n_iter > 0) {
+          tmem_ld32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + 32u * t, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        }
+        if (k < p.K) {
+          float* dst = base + (static_cast<long long>(k) * p.T + t) * p.C + cc * 32;
+          const int left = p.C - cc * 32;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (4 * j < left) {
+              if (p.use_atomics) {
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * j),
+                             "f"(v[4 * j]), "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
+                             : "memory");
+              } else {
+                *reinterpret_cast<float4*>(dst + 4 * j) =
+                    make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              }
+            }
+          }
+        }
+      }
+    } else if (lane == 0) {
+      *abort_flag = 1;
+      atomicCAS(&g_conv_status, 0, 23);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem_base, tmem_cols);
+}
+
+namespace wgh {
+
+struct Plan {
+  WgHaloParams p;
+  size_t smem;
+  int grid;
+};
+
+inline bool eligible(const mb_conv_desc* d) {
+  const int Wh = d->Q + (d->S - 1) * d->dil_w;
+  return d->stride_h == 1 && d->stride_w == 1 && d->R * d->S > 1 && d->R * d->S <= 16 && d->S <= 8 &&
+         Wh <= 256 && d->groups == 1;
+}
+
+inline bool make_plan(const mb_conv_desc* d, int variant, Plan* pl) {
+  if (!eligible(d)) return false;
+  WgHaloParams& p = pl->p;
+  memset(&p, 0, sizeof(p));
+  p.K = d->K; p.C = d->C; p.T = d->R * d->S; p.R = d->R; p.S = d->S;
+  p.Wh = d->Q + (d->S - 1) * d->dil_w;
+  p.tap_row_pitch = d->dil_h * p.Wh;
+  p.tap_col_pitch = d->dil_w;
+  p.cchunks = (d->C + 31) / 32;
+  p.k_tiles = (d->K + kTileM - 1) / kTileM;
+  p.pad_h = d->pad_h; p.pad_w = d->pad_w;
+  const int halo_h = (d->R - 1) * d->dil_h;
+  auto sizes = [&](int bh, int* ra, int* raa, int* rb, int* rba) {
+    *ra = p.Wh * bh;
+    *raa = (*ra + 7) / 8 * 8;
+    *rb = p.Wh * (bh + halo_h);
+    // the last tap of the last (padding) dy row reads up to raa + halo rows + (S-1)*dil_w
+    const int reach = *raa + halo_h * p.Wh + (d->S - 1) * d->dil_w;
+    *rba = ((reach > *rb ? reach : *rb) + 7) / 8 * 8;
+  };
+  int best_bh = 0;
+  for (int bh = d->P; bh >= 1; --bh) {
+    int ra, raa, rb, rba;
+    sizes(bh, &ra, &raa, &rb, &rba);
+    if (bh + halo_h > 256) continue;
+    const size_t stage = static_cast<size_t>(4 * raa + rba) * 128;
+    if (stage <= 72 * 1024) { best_bh = bh; break; }
+  }
+  if (!best_bh) {
+    int ra, raa, rb, rba;
+    sizes(1, &ra, &raa, &rb, &rba);
+    if (static_cast<size_t>(4 * raa + rba) * 128 > 107 * 1024) return false;
+    best_bh = 1;
+  }
+  p.tiles_h = (d->P + best_bh - 1) / best_bh;
+  p.bh = (d->P + p.tiles_h - 1) / p.tiles_h;          // balanced tiles
+  p.bhB = p.bh + halo_h;
+  sizes(p.bh, &p.rowsA, &p.rowsA_alloc, &p.rowsB, &p.rowsB_alloc);
+  const long long tiles = static_cast<long long>(p.tiles_h) * d->N;
+  if (tiles > 0x7fffffffLL) return false;
+  p.pix_tiles = static_cast<int>(tiles);
+  const size_t stage = static_cast<size_t>(4 * p.rowsA_alloc + p.rowsB_alloc) * 128;
+  int st = static_cast<int>((216 * 1024) / stage);
+  if (st > 8) st = 8;
+  if (st < 2) return false;
+  p.stages = st;
+  pl->smem = 512 + 1024 + stage * st;
+  const int items = p.k_tiles * p.cchunks;
+  // one wave of CTAs: the kernel is bound by MMA issue, a second wave would only repeat the
+  // set-up and double the number of partial results to combine
+  int splits = kNumSMs / items;
+  const int max_splits = (p.pix_tiles + 3) / 4;
+  if (splits > max_splits) splits = max_splits;
+  if (splits < 1) splits = 1;
+  if (variant == 1 && splits > 64) splits = 64;
+  p.splits = splits;
+  p.use_atomics = variant == 0;
+  pl->grid = items * splits;
+  return true;
+}
+
+}  // namespace wgh
+
+// Workspace of the deterministic variant: one partial dw per split of whichever kernel runs.
+inline size_t wgrad_workspace_bytes(const mb_conv_desc* d, int variant) {
+  if (variant != 1 || d->groups != 1) return 0;
+  const size_t dw_bytes = static_cast<size_t>(d->K) * d->R * d->S * d->C * sizeof(float);
+  wgh::Plan hp;
+  if (wgh::make_plan(d, variant, &hp)) return hp.p.splits * dw_bytes;
+  wg::Plan pl;
+  if (!wg::make_plan(d, variant, &pl)) return 0;
+  return pl.p.splits * dw_bytes;
+}
+
+}  // namespace mb
