@@ -138,6 +138,16 @@ size_t mb_bn_workspace_bytes(const mb_bn_desc* d);
 int mb_bn_fwd_train(const float* x, const float* gamma, const float* beta, float* running_mean,
                     float* running_var, float* y, float* save_mean, float* save_invstd,
                     const mb_bn_desc* d, void* workspace, size_t workspace_bytes, void* stream);
+/* No counterpart in the reference.  mb_bn_fwd_train for callers that must not allocate
+ * at run time (a schedule executing inside a solved memory budget, a host whose pool owns
+ * the whole device): the statistics scratch is an 8 MiB array built into the library
+ * instead of a workspace argument, and the call performs no cudaMalloc / cudaFree.  Shapes
+ * needing more scratch than that return MB_ERR_WORKSPACE.  The first call on a device
+ * resolves the array's address (do it before any stream capture); all calls on a device
+ * share the array, so calls that overlap on the GPU race.                                  */
+int mb_bn_fwd_train_noalloc(const float* x, const float* gamma, const float* beta,
+                            float* running_mean, float* running_var, float* y, float* save_mean,
+                            float* save_invstd, const mb_bn_desc* d, void* stream);
 /* y = gamma*(x-mean)*invstd + beta with given statistics: the recompute
  * forward of bn.py:33-34 (with the exact saved invstd, i.e. without that
  * path's second +eps).  y may alias x.                                      */

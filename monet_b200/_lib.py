@@ -62,6 +62,7 @@ PROTOTYPES = {
     "mb_maxpool2d_bwd": (C.c_int, [c_f, c_f, c_f, C.POINTER(PoolDesc), c_f]),
     "mb_bn_workspace_bytes": (c_sz, [C.POINTER(BnDesc)]),
     "mb_bn_fwd_train": (C.c_int, [c_f] * 8 + [C.POINTER(BnDesc), c_f, c_sz, c_f]),
+    "mb_bn_fwd_train_noalloc": (C.c_int, [c_f] * 8 + [C.POINTER(BnDesc), c_f]),
     "mb_bn_fwd_apply": (C.c_int, [c_f] * 6 + [C.POINTER(BnDesc), c_f]),
     "mb_bn_bwd_from_output": (C.c_int, [c_f] * 8 + [C.POINTER(BnDesc), c_f, c_sz, c_f]),
     "mb_bn_bwd_from_input": (C.c_int, [c_f] * 8 + [C.POINTER(BnDesc), c_f, c_sz, c_f]),

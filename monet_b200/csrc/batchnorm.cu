@@ -24,6 +24,8 @@
 // dbeta = S1  (lrbn.cu:176-208 written in terms of xhat).
 #include "common.cuh"
 
+#include <mutex>
+
 namespace mb {
 namespace {
 
@@ -559,6 +561,69 @@ int mb_bn_bwd_from_input(const float* dy, const float* x, const float* gamma,
                          size_t workspace_bytes, void* stream) {
   return bwd_common("mb_bn_bwd_from_input", dy, x, gamma, save_mean, save_invstd, 0, save_invstd,
                     dx, dgamma, dbeta, d, workspace, workspace_bytes, stream);
+}
+
+
+// ---- statistics scratch that lives inside the library -----------------------------------
+// 2 Mi floats = 8 MiB per GPU that loads the library, held until the process exits.
+constexpr size_t kStaticScratchFloats = size_t(2) << 20;
+static __device__ __align__(256) float g_bn_static_scratch[kStaticScratchFloats];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+float* g_scratch_ptr[kMaxDevices] = {};   // device address of the array, per device ordinal
+}  // namespace
+
+// Same result as mb_bn_fwd_train, for hosts that must not allocate while a step runs: the
+// statistics scratch is the array above instead of a caller-provided workspace.
+//
+// Who needs it.  MONeT executes a schedule whose every byte was planned by its solver under a
+// fixed memory budget, and serving / training loops built that way often hand the whole
+// device to one pool up front.  In such a host a kernel that asks for "a few more megabytes"
+// at run time either cannot get them (the pool owns the device) or breaks the plan it runs
+// under, and cudaMalloc / cudaFree would also stall every stream of the device.  This entry
+// point therefore calls no cudaMalloc, cudaFree or any allocating library routine.
+//
+// Set-up.  `g_bn_static_scratch` names a host-side handle, not a device address; the first
+// call on each device (with that device current) resolves it with cudaGetSymbolAddress and
+// caches the pointer.  Make that first call before starting any stream capture.
+//
+// Limits.  Shapes whose scratch need (mb_bn_workspace_bytes) exceeds 8 MiB are rejected with
+// MB_ERR_WORKSPACE.  All calls on a device share the one array: it keeps whatever the last
+// call left there (nothing in it has to start at zero - every partial sum that is read is
+// written first by the same call), and two calls that overlap on the GPU, e.g. on different
+// streams, race on it.  Serialise them, or use mb_bn_fwd_train with separate workspaces.
+int mb_bn_fwd_train_noalloc(const float* x, const float* gamma, const float* beta,
+                            float* running_mean, float* running_var, float* y, float* save_mean,
+                            float* save_invstd, const mb_bn_desc* d, void* stream) {
+  const char* who = "mb_bn_fwd_train_noalloc";
+  int rc = check(who, d);
+  if (rc) return rc;
+  const size_t need = mb_bn_workspace_bytes(d);
+  if (need == 0 || need > kStaticScratchFloats * sizeof(float))
+    return fail(MB_ERR_WORKSPACE,
+                "%s: this shape needs %zu bytes of scratch, the built-in array holds %zu; use "
+                "mb_bn_fwd_train with a workspace of your own",
+                who, need, kStaticScratchFloats * sizeof(float));
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    return fail(MB_ERR_LAUNCH, "%s: cannot identify the current device: %s", who, cudaGetErrorString(e));
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (!g_scratch_ptr[dev]) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_bn_static_scratch);
+      if (e != cudaSuccess || !p)
+        return fail(MB_ERR_LAUNCH, "%s: cudaGetSymbolAddress failed: %s", who, cudaGetErrorString(e));
+      g_scratch_ptr[dev] = static_cast<float*>(p);
+    }
+    scratch = g_scratch_ptr[dev];
+  }
+  return mb_bn_fwd_train(x, gamma, beta, running_mean, running_var, y, save_mean, save_invstd, d,
+                         scratch, kStaticScratchFloats * sizeof(float), stream);
 }
 
 }  // extern "C"
