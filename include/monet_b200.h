@@ -248,6 +248,12 @@ int mb_conv2d_dgrad(const float* dy, const float* w, float* dx, const mb_conv_de
 int mb_conv2d_wgrad(const float* x, const float* dy, float* dw, float* dbias,
                     const mb_conv_desc* d, int variant, void* workspace, size_t workspace_bytes,
                     void* stream);
+/* Diagnostics.  When `device_buffer` (16 x int64, device memory) is non-NULL the
+ * stride-1 multi-tap forward / backward-data kernel's first CTA records how many SM
+ * cycles each of its roles spent waiting ([0] total, [1] input tile, [2] filter tile,
+ * [3] accumulator free, [4]/[5] producer on free slots, [6] epilogue on results,
+ * [7] epilogue busy, [8] work items).  NULL switches it off (the default).            */
+int mb_conv_debug_counters(long long* device_buffer);
 /* Few-channel convolutions (C <= 4, filter width <= 8, stride <= 2: the network's first
  * layer).  The input is copied once into a zero-padded 4-channel NHWC buffer
  * xp[N][Hp][Wp][4] (Hp, Wp from mb_conv_smallc_geometry; N*Hp*Wp*16 bytes, the caller's

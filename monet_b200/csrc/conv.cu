@@ -12,6 +12,7 @@
 //                                       in the workspace
 //   wgrad  dw = x (*) dy, db = sum dy   see conv_wgrad.cuh
 #include "conv_gemm.cuh"
+#include "conv_gemm_halo.cuh"
 #include "conv_wgrad.cuh"
 #include "conv_wgrad_halo.cuh"
 
@@ -112,26 +113,28 @@ int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
 // Tile width along N and pipeline depth for `kout` output channels.
 void pick_bn_stages(int kout, long long m_tiles, int* BN, int* stages, size_t* smem) {
-  int bn = round_up(kout < 256 ? kout : 256, 16);
+  int bn = round_up(kout < 256 ? kout : 256, 32);   // whole 32-column chunks for the TMA-store epilogue
   // prefer more, narrower tiles when the wide ones would leave SMs idle in the last wave
   auto eff = [&](int b) {
     const double tiles = static_cast<double>(m_tiles) * ((kout + b - 1) / b);
     const double waves = (tiles + kNumSMs - 1) / kNumSMs;
     return tiles / (static_cast<double>(static_cast<long long>(waves)) * kNumSMs);
   };
-  while (bn > 64 && bn % 32 == 0 && eff(bn / 2) > eff(bn) * 1.15) bn /= 2;
+  while (bn > 64 && bn % 64 == 0 && eff(bn / 2) > eff(bn) * 1.15) bn /= 2;
   const size_t stage = kAStageBytes + static_cast<size_t>(bn) * 128;
-  int st = static_cast<int>((220 * 1024 - 2048) / stage);
+  const size_t staging = 2 * kAStageBytes;            // TMA-store epilogue buffers
+  int st = static_cast<int>((220 * 1024 - 2048 - staging) / stage);
   if (st > 8) st = 8;
   if (st < 2) st = 2;
   *BN = bn;
   *stages = st;
-  *smem = 512 + 1024 + stage * st;
+  *smem = 512 + 1024 + stage * st + staging;
 }
 
 struct GemmLaunch {
   CUtensorMap a[4];
   CUtensorMap b;
+  CUtensorMap out;
   GemmParams p;
   size_t smem;
   int grid;
@@ -145,8 +148,124 @@ int launch_gemm(const char* who, GemmLaunch& L, cudaStream_t st) {
   });
   if (attr_err != cudaSuccess)
     return fail(MB_ERR_LAUNCH, "%s: cannot raise the shared-memory limit: %s", who, cudaGetErrorString(attr_err));
-  conv_gemm_kmajor<<<L.grid, 192, L.smem, st>>>(L.a[0], L.a[1], L.a[2], L.a[3], L.b, L.p);
+  // output view {Kout, Q, P, N} with the tile's box: the epilogue stores whole tiles with TMA
+  {
+    GemmParams& p = L.p;
+    const long long e = 4;
+    long long sw = p.out_sw * e, sh = p.out_sh * e, sn = p.out_sn * e;
+    if (sh == 0) sh = sw * p.Q;
+    if (sn == 0) sn = sh * p.P;
+    p.tma_store = (p.BN % 32 == 0 && sw % 16 == 0 && sh % 16 == 0 && sn % 16 == 0) ? 1 : 0;
+    if (p.tma_store) {
+      int rc = encode_act(who, &L.out, p.out, p.Kout, p.Q, p.P, p.Nimg, sw, sh, sn, p.bw, p.bh, p.bn);
+      if (rc) return rc;
+    } else {
+      L.out = L.b;
+    }
+  }
+  conv_gemm_kmajor<<<L.grid, 192, L.smem, st>>>(L.a[0], L.a[1], L.a[2], L.a[3], L.b, L.out, L.p);
   return after_launch(who);
+}
+
+template <class Kernel>
+int raise_smem_limit(const char* who, Kernel kernel) {
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (e != cudaSuccess)
+    return fail(MB_ERR_LAUNCH, "%s: cannot raise the shared-memory limit: %s", who, cudaGetErrorString(e));
+  return MB_OK;
+}
+
+long long* g_conv_prof = nullptr;   // diagnostics: device buffer for cycle counters (or null)
+
+// ----------------------------------------------------------- halo kernel (stride 1, many taps)
+struct HaloTap { int dh, dw, btap; };
+
+// Runs out = sum_t shift(in, dh_t, dw_t) * filter[:, btap_t, :] with the halo kernel.
+// Returns MB_ERR_UNSUPPORTED (without setting an error message the caller must keep) when the
+// geometry does not fit, so that the caller can fall back to the per-tap kernel.
+int run_halo(const char* who, const float* in, int Cin, int Win, int Hin, const float* filt, int T,
+             float* out, int Kout, int Qo, int Po, int N, const HaloTap* taps, int ntaps,
+             const float* bias, cudaStream_t st) {
+  if (ntaps < 2 || ntaps > kMaxTaps) return MB_ERR_UNSUPPORTED;
+  int min_dh = taps[0].dh, max_dh = taps[0].dh, min_dw = taps[0].dw, max_dw = taps[0].dw;
+  for (int t = 1; t < ntaps; ++t) {
+    if (taps[t].dh < min_dh) min_dh = taps[t].dh;
+    if (taps[t].dh > max_dh) max_dh = taps[t].dh;
+    if (taps[t].dw < min_dw) min_dw = taps[t].dw;
+    if (taps[t].dw > max_dw) max_dw = taps[t].dw;
+  }
+  const int halo_h = max_dh - min_dh, halo_w = max_dw - min_dw;
+  HaloParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.Wh = Qo + halo_w;
+  if (p.Wh > 256) return MB_ERR_UNSUPPORTED;
+  const int rows_cap = 2 * kTileM;
+  if ((Po + halo_h) * p.Wh <= rows_cap) {        // whole (padded) images, several per super-tile
+    p.Hb = Po + halo_h;
+    p.bn = rows_cap / (p.Hb * p.Wh);
+    if (p.bn > N) p.bn = N;
+    p.bh = Po;
+    p.tiles_h = 1;
+    p.Hout = p.bn > 1 ? p.Hb : p.bh;
+  } else {
+    p.bn = 1;
+    const int bh_max = rows_cap / p.Wh;
+    if (bh_max < 1) return MB_ERR_UNSUPPORTED;
+    p.tiles_h = (Po + bh_max - 1) / bh_max;
+    p.bh = (Po + p.tiles_h - 1) / p.tiles_h;
+    p.Hb = p.bh + halo_h;
+    p.Hout = p.bh;
+  }
+  if (p.Hb > 256) return MB_ERR_UNSUPPORTED;
+  p.tiles_n = (N + p.bn - 1) / p.bn;
+  p.box_rows = p.Wh * p.Hb * p.bn;
+  p.out_rows = p.Wh * p.Hout * p.bn;
+  const int span = ((p.bn - 1) * p.Hb + p.bh) * p.Wh;
+  p.MT = ((span > p.out_rows ? span : p.out_rows) + kTileM - 1) / kTileM;
+  if (p.MT > 2) return MB_ERR_UNSUPPORTED;
+  const int max_off = halo_h * p.Wh + halo_w;
+  int need_rows = p.MT * kTileM + max_off;
+  if (need_rows < p.box_rows) need_rows = p.box_rows;
+  p.a_rows_alloc = (need_rows + 7) / 8 * 8;
+  p.bias = bias;
+  p.Kout = Kout;
+  p.BN = Kout >= 256 ? 256 : round_up(Kout, 32);
+  p.tiles_c = (Kout + p.BN - 1) / p.BN;
+  p.kchunks = (Cin + kChunkK - 1) / kChunkK;
+  p.num_taps = ntaps;
+  p.org_w = min_dw; p.org_h = min_dh;
+  for (int t = 0; t < ntaps; ++t) {
+    p.tap_off[t] = static_cast<short>((taps[t].dh - min_dh) * p.Wh + (taps[t].dw - min_dw));
+    p.btap[t] = static_cast<unsigned char>(taps[t].btap);
+  }
+  p.acc_bufs = 2 * p.MT * p.BN <= 512 ? 2 : 1;
+  p.prof = g_conv_prof;
+  p.a_stages = 2;
+  const size_t a_slot = static_cast<size_t>(p.a_rows_alloc) * 128, b_slot = static_cast<size_t>(p.BN) * 128;
+  const size_t staging = (static_cast<size_t>(p.out_rows) * 128 + 1023) / 1024 * 1024;
+  const size_t budget = 222 * 1024 - 2048;
+  if (2 * a_slot + staging + 2 * b_slot > budget) return MB_ERR_UNSUPPORTED;
+  int bs = static_cast<int>((budget - 2 * a_slot - staging) / b_slot);
+  if (bs > 16) bs = 16;
+  p.b_stages = bs;
+  const long long items = static_cast<long long>(p.tiles_h) * p.tiles_n * p.tiles_c;
+  if (items > 0x7fffffffLL) return MB_ERR_UNSUPPORTED;
+  p.num_items = static_cast<int>(items);
+  const size_t smem = 512 + 1024 + 2 * a_slot + bs * b_slot + staging;
+
+  CUtensorMap ma, mb_, mo;
+  const long long C4 = static_cast<long long>(Cin) * 4, K4 = static_cast<long long>(Kout) * 4;
+  int rc = encode_act(who, &ma, in, Cin, Win, Hin, N, C4, C4 * Win, C4 * Win * Hin, p.Wh, p.Hb, p.bn);
+  if (rc) return rc;
+  rc = encode_filter(who, &mb_, filt, Cin, T, Kout, p.BN);
+  if (rc) return rc;
+  rc = encode_act(who, &mo, out, Kout, Qo, Po, N, K4, K4 * Qo, K4 * Qo * Po, p.Wh, p.Hout, p.bn);
+  if (rc) return rc;
+  static const int attr_rc = raise_smem_limit(who, conv_gemm_halo);
+  if (attr_rc) return attr_rc;
+  const int grid = p.num_items < kNumSMs ? p.num_items : kNumSMs;
+  conv_gemm_halo<<<grid, 192, smem, st>>>(ma, mb_, mo, p);
+  return after_launch("conv_gemm_halo");
 }
 
 int floordiv(int a, int b) { return (a >= 0) ? a / b : -((-a + b - 1) / b); }
@@ -242,14 +361,6 @@ int wgrad_finish(const char* who, int variant, int splits, const float* dy, floa
     rc = after_launch("conv_bias_grad");
     if (rc) return rc;
   }
-  return MB_OK;
-}
-
-template <class Kernel>
-int raise_smem_limit(const char* who, Kernel kernel) {
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-  if (e != cudaSuccess)
-    return fail(MB_ERR_LAUNCH, "%s: cannot raise the shared-memory limit: %s", who, cudaGetErrorString(e));
   return MB_OK;
 }
 
@@ -440,6 +551,16 @@ int mb_conv2d_fprop(const float* x, const float* w, const float* bias, float* y,
     return fail(MB_ERR_INVALID_ARGUMENT, "%s: pointers must be 16-byte aligned", who);
   (void)workspace; (void)workspace_bytes;
 
+  if (d->stride_h == 1 && d->stride_w == 1 && d->R * d->S > 1) {
+    HaloTap taps[kMaxTaps];
+    int nt = 0;
+    for (int r = 0; r < d->R; ++r)
+      for (int s = 0; s < d->S; ++s)
+        taps[nt++] = HaloTap{r * d->dil_h - d->pad_h, s * d->dil_w - d->pad_w, r * d->S + s};
+    rc = run_halo(who, x, d->C, d->W, d->H, w, d->R * d->S, y, d->K, d->Q, d->P, d->N, taps, nt, bias,
+                  as_stream(stream));
+    if (rc != MB_ERR_UNSUPPORTED) return rc;
+  }
   GemmLaunch L;
   std::memset(&L.p, 0, sizeof(L.p));
   GemmParams& p = L.p;
@@ -541,6 +662,15 @@ int mb_conv2d_dgrad(const float* dy, const float* w, float* dx, const mb_conv_de
     transpose_filter<<<grid_for(total, 256, 8), 256, 0, st>>>(w, wt, d->K, T, d->C);
     rc = after_launch("conv_transpose_filter");
     if (rc) return rc;
+  }
+  if (d->stride_h == 1 && d->stride_w == 1 && T > 1) {
+    HaloTap taps[kMaxTaps];
+    int nt = 0;
+    for (int r = 0; r < d->R; ++r)
+      for (int s = 0; s < d->S; ++s)
+        taps[nt++] = HaloTap{d->pad_h - r * d->dil_h, d->pad_w - s * d->dil_w, r * d->S + s};
+    rc = run_halo(who, dy, d->K, d->Q, d->P, wt, T, dx, d->C, d->W, d->H, d->N, taps, nt, nullptr, st);
+    if (rc != MB_ERR_UNSUPPORTED) return rc;
   }
   const long long K4 = static_cast<long long>(d->K) * 4;
   const int sh = d->stride_h, sw = d->stride_w;
@@ -736,6 +866,12 @@ int mb_conv2d_wgrad_smallc(const float* xp, const float* dy, float* dwp, float* 
   const size_t dw_elems = static_cast<size_t>(d->K) * d->R * 32;
   return wgrad_launch(who, pl, mdy, mx, dy, dwp, dw_elems, dbias, d, variant, workspace,
                       workspace_bytes, as_stream(stream));
+}
+
+
+int mb_conv_debug_counters(long long* device_buffer) {
+  g_conv_prof = device_buffer;
+  return MB_OK;
 }
 
 }  // extern "C"

@@ -52,6 +52,7 @@ struct GemmParams {
   int kchunks;                  // ceil(input channels / 32)
   int num_taps;
   int stages;
+  int tma_store;                // epilogue stages tiles in shared memory and stores them with TMA
   Taps taps;
 };
 
@@ -77,7 +78,8 @@ struct Ring {
 __global__ void __launch_bounds__(192, 1)
 conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUtensorMap mapA1,
                  const __grid_constant__ CUtensorMap mapA2, const __grid_constant__ CUtensorMap mapA3,
-                 const __grid_constant__ CUtensorMap mapB, const __grid_constant__ GemmParams p) {
+                 const __grid_constant__ CUtensorMap mapB, const __grid_constant__ CUtensorMap mapOut,
+                 const __grid_constant__ GemmParams p) {
   using namespace sm100;
   extern __shared__ uint8_t smem_raw[];
   // control block first, then 1024-byte aligned operand slots
@@ -87,10 +89,13 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
   uint64_t* acc_empty = acc_full + 2;                               // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* epi_ok = abort_flag + 1;                            // [4], one per epilogue warp
   const uint32_t slots0 = (smem_u32(smem_raw) + 512u + 1023u) & ~1023u;
   const uint32_t b_stage_bytes = static_cast<uint32_t>(p.BN) * 128u;
   const uint32_t stage_bytes = kAStageBytes + b_stage_bytes;
   uint8_t* slots_ptr = smem_raw + (slots0 - smem_u32(smem_raw));
+  // two 16 KiB staging buffers for the TMA-store epilogue sit behind the operand slots
+  uint8_t* stage_out = slots_ptr + static_cast<size_t>(p.stages) * stage_bytes;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // two accumulators of BN columns; the epilogue reads whole 32-column groups, so the
@@ -221,6 +226,7 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
     // ---------------------------------------------------------------- epilogue
     bool ok = true;
     int it = 0;
+    int chunk_no = 0;             // counts staged 32-column chunks (selects the staging buffer)
     for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
@@ -230,31 +236,68 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
       const int wi = m % p.bw, hi = (m / p.bw) % p.bh, ni = m / (p.bw * p.bh);
       const bool valid = m < box_rows && (n0 + ni) < p.Nimg && (p0 + hi) < p.P && (q0 + wi) < p.Q;
       float* orow = p.out + (n0 + ni) * p.out_sn + (p0 + hi) * p.out_sh + (q0 + wi) * p.out_sw + c0;
-      // the whole warp must agree before the warp-collective tensor-memory loads
+      // all four epilogue warps must agree before the warp-collective tensor-memory loads and
+      // the named barriers of the store path: every warp always reaches this barrier
       const bool got = mbar_wait(&acc_full[acc], acc_phase, abort_flag);
-      if (!__all_sync(0xffffffffu, got)) {
+      const bool warp_ok = __all_sync(0xffffffffu, got);
+      if (lane == 0) epi_ok[warp] = warp_ok ? 1 : 0;
+      named_barrier(1, 128);
+      if (!(epi_ok[0] && epi_ok[1] && epi_ok[2] && epi_ok[3])) {
         ok = false;
         break;
       }
+      named_barrier(1, 128);      // flags are read before the next tile overwrites them
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) +
                              static_cast<uint32_t>(acc * p.BN);
-      for (int col = 0; col < p.BN && c0 + col < p.Kout; col += 32) {
-        float v[32];
-        tmem_ld32(t_row + col, v);
-        tmem_ld_wait();
-        if (valid) {
-          // columns of this tile that exist: bounded by the tile width and by Kout
-          const int left = min(p.Kout - (c0 + col), p.BN - col);
+      if (p.tma_store) {
+        // Each thread owns one output pixel row.  Writing it straight to global memory would
+        // touch 32 different cache lines per warp instruction; instead the 128 x 32 chunk is
+        // laid out in shared memory in the 128-byte swizzle and one TMA store writes whole
+        // lines (and clips what lies outside the tensor).
+        for (int col = 0; col < p.BN && c0 + col < p.Kout; col += 32) {
+          float v[32];
+          tmem_ld32(t_row + col, v);
+          tmem_ld_wait();
+          uint8_t* buf = stage_out + static_cast<size_t>(chunk_no & 1) * kAStageBytes;
+          if (threadIdx.x == 0) tma_store_wait_read<1>();     // the store that last read `buf` is done
+          named_barrier(1, 128);
+          float4* rowp = reinterpret_cast<float4*>(buf + m * 128);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            if (j * 4 < left) {
-              float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-              if (p.bias) {
-                const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + col + 4 * j));
-                o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
+            float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            if (p.bias && c0 + col + 4 * j < p.Kout) {
+              const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + col + 4 * j));
+              o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
+            }
+            rowp[j ^ (m & 7)] = o;
+          }
+          fence_async_smem();
+          named_barrier(1, 128);
+          if (threadIdx.x == 0) {
+            tma_store_4d(&mapOut, buf, c0 + col, q0, p0, n0);
+            tma_store_commit();
+          }
+          ++chunk_no;
+        }
+      } else {
+        for (int col = 0; col < p.BN && c0 + col < p.Kout; col += 32) {
+          float v[32];
+          tmem_ld32(t_row + col, v);
+          tmem_ld_wait();
+          if (valid) {
+            // columns of this tile that exist: bounded by the tile width and by Kout
+            const int left = min(p.Kout - (c0 + col), p.BN - col);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (j * 4 < left) {
+                float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                if (p.bias) {
+                  const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + col + 4 * j));
+                  o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
+                }
+                *reinterpret_cast<float4*>(orow + col + 4 * j) = o;
               }
-              *reinterpret_cast<float4*>(orow + col + 4 * j) = o;
             }
           }
         }
@@ -262,6 +305,7 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
       tc_fence_before();
       mbar_arrive(&acc_empty[acc]);
     }
+    if (p.tma_store && threadIdx.x == 0) tma_store_wait_read<0>();   // staging must outlive the stores
     if (!ok && lane == 0) {
       *abort_flag = 1;
       atomicCAS(&g_conv_status, 0, 3);
