@@ -40,7 +40,86 @@ def parse():
     ap.add_argument("--batch", type=int, default=184)
     ap.add_argument("--cpu-batch", type=int, default=16, help="images per step of the CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--micro", default=None, choices=sorted(MICRO),
+                    help="time ONE operator on one ResNet-50 layer's tensors (for ncu captures)")
+    ap.add_argument("--micro-batch", type=int, default=184)
     return ap.parse_args()
+
+
+# ------------------------------------------------------------------------ micro cases
+# name -> (kind, C, H, K, R, stride, pad): one operator on one layer of the workload
+MICRO = {
+    "fprop3x3_c64": ("fprop", 64, 56, 64, 3, 1, 1), "dgrad3x3_c64": ("dgrad", 64, 56, 64, 3, 1, 1),
+    "wgrad3x3_c64": ("wgrad", 64, 56, 64, 3, 1, 1), "wgrad3x3_c128": ("wgrad", 128, 28, 128, 3, 1, 1),
+    "fprop3x3_c256": ("fprop", 256, 14, 256, 3, 1, 1), "wgrad3x3_c256": ("wgrad", 256, 14, 256, 3, 1, 1),
+    "fprop1x1_c64_k256": ("fprop", 64, 56, 256, 1, 1, 0), "dgrad1x1_c64_k256": ("dgrad", 64, 56, 256, 1, 1, 0),
+    "wgrad1x1_c64_k256": ("wgrad", 64, 56, 256, 1, 1, 0), "fprop1x1_c1024_k256": ("fprop", 1024, 14, 256, 1, 1, 0),
+    "fprop3x3s2_c128": ("fprop", 128, 56, 128, 3, 2, 1), "wgrad3x3s2_c128": ("wgrad", 128, 56, 128, 3, 2, 1),
+    "stem_fprop": ("fprop", 3, 224, 64, 7, 2, 3), "stem_wgrad": ("wgrad", 3, 224, 64, 7, 2, 3),
+    "bn_fwd": ("bn_fwd", 256, 56, 0, 0, 0, 0), "bn_bwd": ("bn_bwd", 256, 56, 0, 0, 0, 0),
+    "relu_fwd": ("relu_fwd", 256, 56, 0, 0, 0, 0), "relu_fwd_mask": ("relu_fwd_mask", 256, 56, 0, 0, 0, 0),
+    "relu_bwd": ("relu_bwd", 256, 56, 0, 0, 0, 0), "add": ("add", 256, 56, 0, 0, 0, 0),
+    "maxpool_fwd": ("maxpool_fwd", 64, 112, 0, 0, 0, 0), "maxpool_bwd": ("maxpool_bwd", 64, 112, 0, 0, 0, 0),
+}
+
+
+def run_micro(args):
+    """One operator, `--steps` timed calls after `--warmup`, CUDA events; one JSON line."""
+    import torch
+    from monet_b200 import functional as F
+    kind, Cc, H, K, R, s, p = MICRO[args.micro]
+    dev = torch.device("cuda", 0)
+    N = args.micro_batch
+    torch.manual_seed(0)
+    cl = torch.channels_last
+    x = torch.randn(N, Cc, H, H, device=dev)
+    x = x.contiguous(memory_format=cl) if Cc % 4 == 0 else x
+    if kind in ("fprop", "dgrad", "wgrad"):
+        w = (torch.randn(K, Cc, R, R, device=dev) * 0.05).contiguous(memory_format=cl)
+        y = F.conv2d_fprop(x, w, None, s, p, 1)
+        dy = torch.randn_like(y)
+        nbytes = 4.0 * (x.numel() + w.numel() + y.numel())
+        flops = 2.0 * y.numel() * Cc * R * R
+        fn = {"fprop": lambda: F.conv2d_fprop(x, w, None, s, p, 1),
+              "dgrad": lambda: F.conv2d_dgrad(dy, w, x.shape, s, p, 1),
+              "wgrad": lambda: F.conv2d_wgrad(x, dy, w.shape, s, p, 1)}[kind]
+    else:
+        flops = 0.0
+        E = float(x.numel())
+        g, b = torch.ones(Cc, device=dev), torch.zeros(Cc, device=dev)
+        dy = torch.randn_like(x)
+        if kind == "bn_fwd":
+            nbytes, fn = 12 * E, lambda: F.bn_fwd_train(x, g, b, None, None, 0.1, 1e-5)
+        elif kind == "bn_bwd":
+            yb, _, iv = F.bn_fwd_train(x, g, b, None, None, 0.1, 1e-5)
+            nbytes, fn = 20 * E, lambda: F.bn_bwd_from_output(dy, yb, g, b, iv)
+        elif kind == "relu_fwd":
+            nbytes, fn = 8 * E, lambda: F.relu(x)
+        elif kind == "relu_fwd_mask":
+            nbytes, fn = 8.125 * E, lambda: F.relu_mask(x)
+        elif kind == "relu_bwd":
+            nbytes, fn = 12 * E, lambda: F.relu_bwd_act(dy, x, 0.0, inplace=False)
+        elif kind == "add":
+            nbytes, fn = 12 * E, lambda: F.add(x, dy, 1.0)
+        elif kind == "maxpool_fwd":
+            yp, _, _ = F.maxpool2d(x, 3, 2, 1, 1, False)
+            nbytes, fn = 4 * E + 4.5 * yp.numel(), lambda: F.maxpool2d(x, 3, 2, 1, 1, False)
+        else:
+            yp, nib, d = F.maxpool2d(x, 3, 2, 1, 1, False)
+            dyp = torch.randn_like(yp)
+            nbytes, fn = 4 * E + 4.5 * yp.numel(), lambda: F.maxpool2d_bwd(dyp, nib, d)
+    for _ in range(max(args.warmup, 1)):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({"micro": args.micro, "batch": N, "ms": ms, "algorithmic_GBps": nbytes / ms / 1e6,
+                      "TFLOPps": flops / ms / 1e9, "conv_status": F.conv_device_status()}), flush=True)
 
 
 # ------------------------------------------------------------------ reference arm (CPU)
@@ -330,7 +409,9 @@ def run_ours(args):
 
 def main():
     args = parse()
-    if args.impl == "reference":
+    if args.micro:
+        run_micro(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -248,6 +248,16 @@ int mb_conv2d_dgrad(const float* dy, const float* w, float* dx, const mb_conv_de
 int mb_conv2d_wgrad(const float* x, const float* dy, float* dw, float* dbias,
                     const mb_conv_desc* d, int variant, void* workspace, size_t workspace_bytes,
                     void* stream);
+/* Depthwise convolution (groups == C == K; replaces convolution_main / backward_depthwise,
+ * conv.cpp:704-726, which defer to ATen's depthwise kernels).  NHWC activations; the filter
+ * and its gradient are [R*S][C] (channel innermost).  fp32 FMA, HBM-bound.  C % 4 == 0;
+ * backward-filter is built for 1x1, 3x3 and 5x5 windows and zeroes dw / dbias itself.     */
+int mb_depthwise_fprop(const float* x, const float* w_tc, const float* bias, float* y,
+                       const mb_conv_desc* d, void* stream);
+int mb_depthwise_dgrad(const float* dy, const float* w_tc, float* dx, const mb_conv_desc* d,
+                       void* stream);
+int mb_depthwise_wgrad(const float* x, const float* dy, float* dw_tc, float* dbias,
+                       const mb_conv_desc* d, void* stream);
 /* Diagnostics.  When `device_buffer` (16 x int64, device memory) is non-NULL the
  * stride-1 multi-tap forward / backward-data kernel's first CTA records how many SM
  * cycles each of its roles spent waiting ([0] total, [1] input tile, [2] filter tile,

@@ -77,6 +77,9 @@ PROTOTYPES = {
     "mb_conv2d_fprop": (C.c_int, [c_f, c_f, c_f, c_f, C.POINTER(ConvDesc), C.c_int, c_f, c_sz, c_f]),
     "mb_conv2d_dgrad": (C.c_int, [c_f, c_f, c_f, C.POINTER(ConvDesc), C.c_int, c_f, c_sz, c_f]),
     "mb_conv2d_wgrad": (C.c_int, [c_f, c_f, c_f, c_f, C.POINTER(ConvDesc), C.c_int, c_f, c_sz, c_f]),
+    "mb_depthwise_fprop": (C.c_int, [c_f, c_f, c_f, c_f, C.POINTER(ConvDesc), c_f]),
+    "mb_depthwise_dgrad": (C.c_int, [c_f, c_f, c_f, C.POINTER(ConvDesc), c_f]),
+    "mb_depthwise_wgrad": (C.c_int, [c_f, c_f, c_f, c_f, C.POINTER(ConvDesc), c_f]),
     "mb_conv_device_status": (C.c_int, [C.c_int]),
     "mb_conv_debug_counters": (C.c_int, [c_f]),
     "mb_conv_smallc_geometry": (C.c_int, [C.POINTER(ConvDesc), C.POINTER(C.c_int), C.POINTER(C.c_int)]),

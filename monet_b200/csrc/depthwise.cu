@@ -1,0 +1,221 @@
+// Depthwise convolution (groups == C, one filter per channel; MobileNetV2's 3x3 layers),
+// NHWC, fp32 FMA.  These layers move 8 bytes per output element for ~18 flops, so they are
+// HBM-bound and run as vectorised SIMT kernels rather than on the tensor cores:
+//   forward        thread = output pixel x 4 channels, R*S float4 taps
+//   backward-data  thread = input pixel x 4 channels, gathers the taps that reach it
+//   backward-filter per-channel reduction over all pixels: each CTA accumulates its share of
+//                  rows in registers, combines over its row lanes in shared memory and adds
+//                  the result to dw with atomics (dw zeroed first)
+// Filters are given as [R*S][C] (channel innermost).  Replaces the ATen depthwise kernels
+// the reference defers to (conv.cpp:704-726).
+#include "common.cuh"
+
+namespace mb {
+namespace {
+
+struct DwP {
+  int N, C, H, W, P, Q, R, S, sh, sw, ph, pw, dh, dw;
+};
+
+constexpr int kMaxDwTaps = 25;
+
+__global__ void __launch_bounds__(256) dw_fprop(const float* __restrict__ x, const float* __restrict__ w,
+                                                const float* __restrict__ bias, float* __restrict__ y,
+                                                DwP p, size_t total) {
+  const int cg = p.C / 4;
+  for (size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
+       t += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const int g = static_cast<int>(t % cg);
+    size_t pix = t / cg;
+    const int q = static_cast<int>(pix % p.Q);
+    pix /= p.Q;
+    const int pp = static_cast<int>(pix % p.P);
+    const int n = static_cast<int>(pix / p.P);
+    float4 acc = bias ? __ldg(reinterpret_cast<const float4*>(bias) + g) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float* xn = x + static_cast<size_t>(n) * p.H * p.W * p.C + g * 4;
+    for (int r = 0; r < p.R; ++r) {
+      const int h = pp * p.sh - p.ph + r * p.dh;
+      if (h < 0 || h >= p.H) continue;
+      for (int s = 0; s < p.S; ++s) {
+        const int ww = q * p.sw - p.pw + s * p.dw;
+        if (ww < 0 || ww >= p.W) continue;
+        const float4 a = __ldg(reinterpret_cast<const float4*>(xn + (static_cast<size_t>(h) * p.W + ww) * p.C));
+        const float4 f = __ldg(reinterpret_cast<const float4*>(w + static_cast<size_t>(r * p.S + s) * p.C) + g);
+        acc.x = fmaf(a.x, f.x, acc.x); acc.y = fmaf(a.y, f.y, acc.y);
+        acc.z = fmaf(a.z, f.z, acc.z); acc.w = fmaf(a.w, f.w, acc.w);
+      }
+    }
+    reinterpret_cast<float4*>(y)[t] = acc;
+  }
+}
+
+__global__ void __launch_bounds__(256) dw_dgrad(const float* __restrict__ dy, const float* __restrict__ w,
+                                                float* __restrict__ dx, DwP p, size_t total) {
+  const int cg = p.C / 4;
+  for (size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
+       t += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const int g = static_cast<int>(t % cg);
+    size_t pix = t / cg;
+    const int ww = static_cast<int>(pix % p.W);
+    pix /= p.W;
+    const int h = static_cast<int>(pix % p.H);
+    const int n = static_cast<int>(pix / p.H);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float* dn = dy + static_cast<size_t>(n) * p.P * p.Q * p.C + g * 4;
+    for (int r = 0; r < p.R; ++r) {
+      const int hn = h + p.ph - r * p.dh;
+      if (hn < 0 || hn % p.sh) continue;
+      const int pp = hn / p.sh;
+      if (pp >= p.P) continue;
+      for (int s = 0; s < p.S; ++s) {
+        const int wn = ww + p.pw - s * p.dw;
+        if (wn < 0 || wn % p.sw) continue;
+        const int q = wn / p.sw;
+        if (q >= p.Q) continue;
+        const float4 a = __ldg(reinterpret_cast<const float4*>(dn + (static_cast<size_t>(pp) * p.Q + q) * p.C));
+        const float4 f = __ldg(reinterpret_cast<const float4*>(w + static_cast<size_t>(r * p.S + s) * p.C) + g);
+        acc.x = fmaf(a.x, f.x, acc.x); acc.y = fmaf(a.y, f.y, acc.y);
+        acc.z = fmaf(a.z, f.z, acc.z); acc.w = fmaf(a.w, f.w, acc.w);
+      }
+    }
+    reinterpret_cast<float4*>(dx)[t] = acc;
+  }
+}
+
+// block = (tx channel groups of 4) x (ty row lanes); grid = (row chunks, channel slabs).
+// A "row" is one output pixel.  TAPS = R*S is a template parameter so that the per-tap
+// accumulators live in registers.
+template <int TAPS>
+__global__ void __launch_bounds__(256) dw_wgrad(const float* __restrict__ x, const float* __restrict__ dy,
+                                                float* __restrict__ dwt, float* __restrict__ db, DwP p,
+                                                size_t pixels, int chunks, int tx_n, int ty_n) {
+  extern __shared__ float sm[];   // [ty_n][tx_n][4]
+  const int tx = threadIdx.x % tx_n, ty = threadIdx.x / tx_n;
+  const int g = blockIdx.y * tx_n + tx;
+  const bool live = g * 4 < p.C;
+  float4 acc[TAPS];
+  float4 accb = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int t = 0; t < TAPS; ++t) acc[t] = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (live) {
+    const size_t per = (pixels + chunks - 1) / chunks;
+    const size_t r0 = static_cast<size_t>(blockIdx.x) * per;
+    const size_t r1 = (r0 + per) < pixels ? (r0 + per) : pixels;
+    for (size_t row = r0 + ty; row < r1; row += ty_n) {
+      const int q = static_cast<int>(row % p.Q);
+      size_t rr = row / p.Q;
+      const int pp = static_cast<int>(rr % p.P);
+      const int n = static_cast<int>(rr / p.P);
+      const float4 d = __ldg(reinterpret_cast<const float4*>(dy + row * p.C) + g);
+      accb.x += d.x; accb.y += d.y; accb.z += d.z; accb.w += d.w;
+      const float* xn = x + static_cast<size_t>(n) * p.H * p.W * p.C + g * 4;
+#pragma unroll
+      for (int t = 0; t < TAPS; ++t) {
+        const int r = t / p.S, s = t - r * p.S;
+        const int h = pp * p.sh - p.ph + r * p.dh, ww = q * p.sw - p.pw + s * p.dw;
+        if (h < 0 || h >= p.H || ww < 0 || ww >= p.W) continue;
+        const float4 a = __ldg(reinterpret_cast<const float4*>(xn + (static_cast<size_t>(h) * p.W + ww) * p.C));
+        acc[t].x = fmaf(a.x, d.x, acc[t].x); acc[t].y = fmaf(a.y, d.y, acc[t].y);
+        acc[t].z = fmaf(a.z, d.z, acc[t].z); acc[t].w = fmaf(a.w, d.w, acc[t].w);
+      }
+    }
+  }
+  // combine the row lanes of each channel group, one tap at a time
+  float4* mine = reinterpret_cast<float4*>(sm) + ty * tx_n + tx;
+  for (int t = 0; t <= TAPS; ++t) {
+    *mine = t < TAPS ? acc[t] : accb;
+    __syncthreads();
+    if (ty == 0 && live && (t < TAPS || db)) {
+      float4 s = *mine;
+      for (int j = 1; j < ty_n; ++j) {
+        const float4 o = reinterpret_cast<float4*>(sm)[j * tx_n + tx];
+        s.x += o.x; s.y += o.y; s.z += o.z; s.w += o.w;
+      }
+      float* dst = t < TAPS ? dwt + static_cast<size_t>(t) * p.C + g * 4 : db + g * 4;
+      atomicAdd(dst + 0, s.x); atomicAdd(dst + 1, s.y); atomicAdd(dst + 2, s.z); atomicAdd(dst + 3, s.w);
+    }
+    __syncthreads();
+  }
+}
+
+int check(const char* who, const mb_conv_desc* d, DwP* p) {
+  if (!d) return fail(MB_ERR_INVALID_ARGUMENT, "%s: null descriptor", who);
+  if (d->groups != d->C || d->K != d->C)
+    return fail(MB_ERR_UNSUPPORTED, "%s: only groups == C == K (one filter per channel)", who);
+  if (d->C % 4) return fail(MB_ERR_UNSUPPORTED, "%s: C=%d must be a multiple of 4", who, d->C);
+  if (d->R * d->S > kMaxDwTaps) return fail(MB_ERR_UNSUPPORTED, "%s: more than %d taps", who, kMaxDwTaps);
+  const int P = (d->H + 2 * d->pad_h - d->dil_h * (d->R - 1) - 1) / d->stride_h + 1;
+  const int Q = (d->W + 2 * d->pad_w - d->dil_w * (d->S - 1) - 1) / d->stride_w + 1;
+  if (P != d->P || Q != d->Q || P <= 0 || Q <= 0)
+    return fail(MB_ERR_INVALID_ARGUMENT, "%s: output extent does not match the geometry", who);
+  *p = DwP{d->N, d->C, d->H, d->W, d->P, d->Q, d->R, d->S, d->stride_h, d->stride_w, d->pad_h,
+           d->pad_w, d->dil_h, d->dil_w};
+  return MB_OK;
+}
+
+}  // namespace
+}  // namespace mb
+
+using namespace mb;
+
+extern "C" {
+
+int mb_depthwise_fprop(const float* x, const float* w_tc, const float* bias, float* y,
+                       const mb_conv_desc* d, void* stream) {
+  DwP p;
+  int rc = check("mb_depthwise_fprop", d, &p);
+  if (rc) return rc;
+  if (!x || !w_tc || !y || !aligned(x, 16) || !aligned(w_tc, 16) || !aligned(y, 16) || !aligned(bias, 16))
+    return fail(MB_ERR_INVALID_ARGUMENT, "mb_depthwise_fprop: null or misaligned pointer");
+  const size_t total = static_cast<size_t>(p.N) * p.P * p.Q * (p.C / 4);
+  dw_fprop<<<grid_for(total, 256, 8), 256, 0, as_stream(stream)>>>(x, w_tc, bias, y, p, total);
+  return after_launch("depthwise_fprop");
+}
+
+int mb_depthwise_dgrad(const float* dy, const float* w_tc, float* dx, const mb_conv_desc* d,
+                       void* stream) {
+  DwP p;
+  int rc = check("mb_depthwise_dgrad", d, &p);
+  if (rc) return rc;
+  if (!dy || !w_tc || !dx || !aligned(dy, 16) || !aligned(w_tc, 16) || !aligned(dx, 16))
+    return fail(MB_ERR_INVALID_ARGUMENT, "mb_depthwise_dgrad: null or misaligned pointer");
+  const size_t total = static_cast<size_t>(p.N) * p.H * p.W * (p.C / 4);
+  dw_dgrad<<<grid_for(total, 256, 8), 256, 0, as_stream(stream)>>>(dy, w_tc, dx, p, total);
+  return after_launch("depthwise_dgrad");
+}
+
+int mb_depthwise_wgrad(const float* x, const float* dy, float* dw_tc, float* dbias,
+                       const mb_conv_desc* d, void* stream) {
+  const char* who = "mb_depthwise_wgrad";
+  DwP p;
+  int rc = check(who, d, &p);
+  if (rc) return rc;
+  if (!x || !dy || !dw_tc || !aligned(x, 16) || !aligned(dy, 16))
+    return fail(MB_ERR_INVALID_ARGUMENT, "%s: null or misaligned pointer", who);
+  cudaStream_t st = as_stream(stream);
+  const int taps = p.R * p.S;
+  if (cudaMemsetAsync(dw_tc, 0, static_cast<size_t>(taps) * p.C * sizeof(float), st) != cudaSuccess ||
+      (dbias && cudaMemsetAsync(dbias, 0, static_cast<size_t>(p.C) * sizeof(float), st) != cudaSuccess))
+    return fail(MB_ERR_LAUNCH, "%s: memset failed", who);
+  const int groups = p.C / 4;
+  int tx = 1;
+  while (tx < groups && tx < 64) tx <<= 1;
+  const int ty = 256 / tx;
+  const int slabs = (groups + tx - 1) / tx;
+  const size_t pixels = static_cast<size_t>(p.N) * p.P * p.Q;
+  int chunks = static_cast<int>((pixels + ty * 8 - 1) / (static_cast<size_t>(ty) * 8));
+  const int cap = kNumSMs * 4 / slabs > 0 ? kNumSMs * 4 / slabs : 1;
+  if (chunks > cap) chunks = cap;
+  if (chunks < 1) chunks = 1;
+  dim3 grid(chunks, slabs);
+  const size_t smem = 256 * sizeof(float4);
+  switch (taps) {
+    case 1: dw_wgrad<1><<<grid, 256, smem, st>>>(x, dy, dw_tc, dbias, p, pixels, chunks, tx, ty); break;
+    case 9: dw_wgrad<9><<<grid, 256, smem, st>>>(x, dy, dw_tc, dbias, p, pixels, chunks, tx, ty); break;
+    case 25: dw_wgrad<25><<<grid, 256, smem, st>>>(x, dy, dw_tc, dbias, p, pixels, chunks, tx, ty); break;
+    default: return fail(MB_ERR_UNSUPPORTED, "%s: %dx%d filters (1x1, 3x3 and 5x5 are built)", who, p.R, p.S);
+  }
+  return after_launch("depthwise_wgrad");
+}
+
+}  // extern "C"

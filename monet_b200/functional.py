@@ -608,3 +608,47 @@ def conv2d_wgrad(x, dy, w_shape, stride, padding, dilation, groups=1, variant: i
 def conv_device_status(reset: bool = True) -> int:
     """0 when no tensor-core kernel has reported a pipeline time-out (synchronises)."""
     return lib().mb_conv_device_status(int(reset))
+
+
+# ---------------------------------------------------------------------- depthwise
+def _dw_filter(w: torch.Tensor) -> torch.Tensor:
+    """[C, 1, R, S] -> [R*S][C] (tiny; torch copy)."""
+    Cc, _, R, S = w.shape
+    return w.detach().reshape(Cc, R * S).t().contiguous()
+
+
+def depthwise_fprop(x, w, bias, stride, padding, dilation, groups):
+    """Depthwise conv2d (groups == channels); NHWC output."""
+    _need_cuda(x, w, bias); _f32(x, "x"); _f32(w, "w")
+    d = conv_desc(x.shape, (w.shape[0], w.shape[1], w.shape[2], w.shape[3]), stride, padding, dilation, groups)
+    if groups != d.C or w.shape[0] != d.C or w.shape[1] != 1:
+        raise RuntimeError("monet_b200: grouped convolution is supported only as depthwise (groups == C == K)")
+    xa = to_nhwc(x)
+    y = torch.empty((d.N, d.K, d.P, d.Q), dtype=x.dtype, device=x.device, memory_format=torch.channels_last)
+    b = bias.detach().contiguous() if bias is not None else None
+    check(lib().mb_depthwise_fprop(xa.data_ptr(), _dw_filter(w).data_ptr(),
+                                   b.data_ptr() if b is not None else None, y.data_ptr(), C.byref(d),
+                                   _stream()), "depthwise_fprop")
+    return y
+
+
+def depthwise_bwd(dy, x, w, stride, padding, dilation, groups, need=(True, True, False)):
+    """(dx, dw, db) of a depthwise convolution; entries not asked for are None."""
+    _need_cuda(dy, x, w); _f32(dy, "dy")
+    d = conv_desc(x.shape, w.shape, stride, padding, dilation, groups)
+    ga = to_nhwc(dy)
+    dx = dw = db = None
+    if need[0]:
+        dx = torch.empty((d.N, d.C, d.H, d.W), dtype=dy.dtype, device=dy.device,
+                         memory_format=torch.channels_last)
+        check(lib().mb_depthwise_dgrad(ga.data_ptr(), _dw_filter(w).data_ptr(), dx.data_ptr(),
+                                       C.byref(d), _stream()), "depthwise_dgrad")
+    if need[1] or need[2]:
+        xa = to_nhwc(x)
+        dwt = torch.empty((d.R * d.S, d.C), dtype=dy.dtype, device=dy.device)
+        db = torch.empty(d.C, dtype=dy.dtype, device=dy.device) if need[2] else None
+        check(lib().mb_depthwise_wgrad(xa.data_ptr(), ga.data_ptr(), dwt.data_ptr(),
+                                       db.data_ptr() if db is not None else None, C.byref(d),
+                                       _stream()), "depthwise_wgrad")
+        dw = dwt.t().reshape(d.C, 1, d.R, d.S) if need[1] else None
+    return dx, dw, db

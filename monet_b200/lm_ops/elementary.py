@@ -17,12 +17,17 @@ class NativeOP(OP):
         with torch.enable_grad():
             r = self.op(input_.requires_grad_(True), *args, **kwargs)
         if r.grad_fn is None:
-            raise RuntimeError(f"{type(self).__name__}: result has no grad_fn")
+            if r is not input_:
+                raise RuntimeError(f"{type(self).__name__}: result has no grad_fn")
+            self.grad_fn = None        # the op returned its input unchanged (e.g. dropout with p = 0)
+            return r.detach()
         self.grad_fn = r.grad_fn
         return r.detach()
 
     def backward(self, grad_output, stored, nodel=False):
         assert len(stored) == 0
+        if self.grad_fn is None:
+            return grad_output
         return self.grad_fn(grad_output)
 
 
