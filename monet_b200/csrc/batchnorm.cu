@@ -60,9 +60,10 @@ Geometry make_geometry(const mb_bn_desc* d) {
     g.slabs = (groups + g.tx - 1) / g.tx;
     size_t rows_per_cta_min = static_cast<size_t>(g.ty) * 8;
     size_t want = (g.M + rows_per_cta_min - 1) / rows_per_cta_min;
-    size_t cap = static_cast<size_t>(kNumSMs) * 6 / g.slabs;
+    // one wave: 4 CTAs of 256 threads are resident per SM at the kernels' register use
+    size_t cap = static_cast<size_t>(kNumSMs) * 4 / g.slabs;
     if (cap < 1) cap = 1;
-    g.S = static_cast<int>(want < cap ? want : cap);   // at most 888 partials per channel
+    g.S = static_cast<int>(want < cap ? want : cap);   // at most 592 partials per channel
   } else {
     g.vec = 1;
     g.tx = g.ty = 0;

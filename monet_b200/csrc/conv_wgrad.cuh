@@ -381,9 +381,10 @@ inline bool make_plan(const mb_conv_desc* d, int variant, Plan* pl, bool smallc 
   if (st < 2) return false;
   p.stages = st;
   pl->smem = 512 + 1024 + stage * st;
-  // splits: fill the machine about twice over, at least 4 pixel tiles per split
+  // splits: one wave of CTAs (every extra CTA adds a full tile of atomics / partials to
+  // combine), at least 4 pixel tiles per split
   const int items = p.k_tiles * p.groups;
-  int splits = (2 * kNumSMs + items - 1) / items;
+  int splits = kNumSMs / items;
   const int max_splits = (p.pix_tiles + 3) / 4;
   if (splits > max_splits) splits = max_splits;
   if (splits < 1) splits = 1;
