@@ -379,30 +379,42 @@ int wgrad_launch(const char* who, wg::Plan& pl, const CUtensorMap& mdy, const CU
   return wgrad_finish(who, variant, p.splits, dy, dw, dw_elems, dbias, d, workspace, st);
 }
 
-// Stride-1 multi-tap filters: the halo kernel (one x box per tile, taps by descriptor offset).
-int wgrad_run_halo(const char* who, wgh::Plan& pl, const float* x, const float* dy, float* dw,
+// Multi-tap filters: the halo kernel (one x box per tile, taps by descriptor offset), one
+// launch per stride phase.
+int wgrad_run_halo(const char* who, wgh::Launches& hl, const float* x, const float* dy, float* dw,
                    float* dbias, const mb_conv_desc* d, int variant, void* workspace,
                    size_t workspace_bytes, cudaStream_t st) {
   const CUtensorMapSwizzle kWg = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
-  WgHaloParams& p = pl.p;
   const size_t dw_elems = static_cast<size_t>(d->K) * d->R * d->S * d->C;
-  int rc = wgrad_prepare(who, variant, p.splits, true, dw, dw_elems, workspace, workspace_bytes, st,
-                         &p.out, &p.split_stride);
-  if (rc) return rc;
-  CUtensorMap mdy, mx;
-  const long long K4 = static_cast<long long>(d->K) * 4, C4 = static_cast<long long>(d->C) * 4;
-  rc = encode_act(who, &mdy, dy, d->K, d->Q, d->P, d->N, K4, K4 * d->Q, K4 * d->Q * d->P, p.Wh, p.bh,
-                  1, kWg);
-  if (rc) return rc;
-  rc = encode_act(who, &mx, x, d->C, d->W, d->H, d->N, C4, C4 * d->W, C4 * d->W * d->H, p.Wh, p.bhB,
-                  1, kWg);
+  float* out = nullptr;
+  long long split_stride = 0;
+  int covered = 0;
+  for (int i = 0; i < hl.n; ++i) covered += hl.plan[i].p.ntaps;
+  int rc = wgrad_prepare(who, variant, hl.plan[0].p.splits, covered >= d->R * d->S, dw, dw_elems, workspace,
+                         workspace_bytes, st, &out, &split_stride);
   if (rc) return rc;
   static const int attr_rc = raise_smem_limit(who, conv_wgrad_halo_tcgen05);
   if (attr_rc) return attr_rc;
-  conv_wgrad_halo_tcgen05<<<pl.grid, 192, pl.smem, st>>>(mdy, mx, p);
-  rc = after_launch("conv_wgrad_halo_tcgen05");
-  if (rc) return rc;
-  return wgrad_finish(who, variant, p.splits, dy, dw, dw_elems, dbias, d, workspace, st);
+  const long long K4 = static_cast<long long>(d->K) * 4, C4 = static_cast<long long>(d->C) * 4;
+  for (int i = 0; i < hl.n; ++i) {
+    WgHaloParams& p = hl.plan[i].p;
+    p.out = out;
+    p.split_stride = split_stride;
+    const int a = hl.phase_a[i], b = hl.phase_b[i];
+    CUtensorMap mdy, mx;
+    rc = encode_act(who, &mdy, dy, d->K, d->Q, d->P, d->N, K4, K4 * d->Q, K4 * d->Q * d->P, p.Wh, p.bh,
+                    1, kWg);
+    if (rc) return rc;
+    const long long Wv = (d->W - b + d->stride_w - 1) / d->stride_w;
+    const long long Hv = (d->H - a + d->stride_h - 1) / d->stride_h;
+    rc = encode_act(who, &mx, x + (static_cast<long long>(a) * d->W + b) * d->C, d->C, Wv, Hv, d->N,
+                    C4 * d->stride_w, C4 * d->W * d->stride_h, C4 * d->W * d->H, p.Wh, p.bhB, 1, kWg);
+    if (rc) return rc;
+    conv_wgrad_halo_tcgen05<<<hl.plan[i].grid, 192, hl.plan[i].smem, st>>>(mdy, mx, p);
+    rc = after_launch("conv_wgrad_halo_tcgen05");
+    if (rc) return rc;
+  }
+  return wgrad_finish(who, variant, hl.plan[0].p.splits, dy, dw, dw_elems, dbias, d, workspace, st);
 }
 
 int wgrad_run(const char* who, const float* x, const float* dy, float* dw, float* dbias,
@@ -410,9 +422,9 @@ int wgrad_run(const char* who, const float* x, const float* dy, float* dw, float
               cudaStream_t st) {
   const CUtensorMapSwizzle kWg = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;   // MN-major TF32 operands
   {
-    wgh::Plan hp;
-    if (wgh::make_plan(d, variant, &hp))
-      return wgrad_run_halo(who, hp, x, dy, dw, dbias, d, variant, workspace, workspace_bytes, st);
+    wgh::Launches hl;
+    if (wgh::make_plans(d, variant, &hl))
+      return wgrad_run_halo(who, hl, x, dy, dw, dbias, d, variant, workspace, workspace_bytes, st);
   }
   wg::Plan pl;
   if (!wg::make_plan(d, variant, &pl))

@@ -1,6 +1,7 @@
-// Backward-weight for stride-1 filters with several taps (3x3, 5x5, dilated...):
-// the input tile is fetched ONCE with its halo and every filter tap reads it
-// through a shifted shared-memory descriptor.
+// Backward-weight for filters with several taps (3x3, 5x5, dilated, and - one
+// launch per stride phase - strided ones): the input tile is fetched ONCE with
+// its halo and every filter tap reads it through a shifted shared-memory
+// descriptor.
 //
 // Both operands are laid out in "halo-width" pixel order: a pixel row index is
 //     i = h * Wh + w,   Wh = Q + (S-1)*dil_w   (output width plus the halo)
@@ -12,6 +13,11 @@
 // accepts unchanged.  The S taps of one filter row are dil_w rows apart, which
 // is a legal leading-dimension stride, so ONE MMA (N = 32*S) covers a filter
 // row and writes the accumulators of its S taps side by side.
+//
+// Stride 2: the input is seen as four phase tensors x[:, a::2, b::2]; the taps
+// whose (row, column) parity selects phase (a, b) form a small stride-1 filter
+// on that tensor, so each phase is one launch of this kernel with its own tap
+// list, all adding into the same dw.
 //
 // Compared with fetching one shifted x box per tap this cuts the x traffic
 // from R*S boxes to (bh + halo)/bh boxes per tile.
@@ -28,17 +34,21 @@ namespace mb {
 struct WgHaloParams {
   float* out;
   long long split_stride;
-  int K, C, T;              // output channels, input channels, taps R*S
-  int R, S;
-  int tap_row_pitch;        // rows between filter rows: dil_h * Wh
-  int tap_col_pitch;        // rows between filter columns: dil_w
+  int K, C, T;              // output channels, input channels, taps R*S of the whole filter
+  int ntaps;                // taps handled by this launch (accumulators in tensor memory)
+  int ngroups;              // MMA groups: runs of taps that are `tap_col_pitch` rows apart
+  int tap_col_pitch;        // rows between neighbouring taps of a group
+  short grp_off[16];        // first operand row offset of each group
+  unsigned char grp_n[16];  // taps in the group (N = 32 * grp_n)
+  unsigned char grp_first[16];  // index of the group's first tap among this launch's taps
+  unsigned char btap[16];   // filter tap (r*S + s) of each of this launch's taps
   int cchunks, k_tiles, splits;
   int Wh, bh;               // box width (pixels incl. halo) and output rows per tile
   int rowsA, rowsA_alloc;   // dy box rows (Wh*bh) and its allocation (multiple of 8)
   int rowsB, rowsB_alloc;   // x box rows (Wh*(bh+(R-1)*dil_h)) and its allocation
   int bhB;                  // x box height
   int tiles_h, pix_tiles;
-  int pad_h, pad_w;
+  int org_h, org_w;         // x box origin relative to the dy box origin (in x-view pixels)
   int stages;
   int use_atomics;
 };
@@ -77,7 +87,7 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
   const uint32_t stage_bytes = a_bytes + b_bytes;
   const uint32_t tx_bytes = static_cast<uint32_t>(ka * p.rowsA + p.rowsB) * 128u;
   uint32_t tmem_cols = 32;
-  while (tmem_cols < 32u * p.T) tmem_cols <<= 1;
+  while (tmem_cols < 32u * p.ntaps) tmem_cols <<= 1;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
@@ -130,7 +140,7 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
         armed[ring.stage] = 1u + ring.phase;
         for (int j = 0; j < ka; ++j)
           tma_load_4d(&mapDy, slot + j * a_box, &full[ring.stage], k0 + 32 * j, 0, p0, n0);
-        tma_load_4d(&mapX, slot + a_bytes, &full[ring.stage], cc * 32, -p.pad_w, p0 - p.pad_h, n0);
+        tma_load_4d(&mapX, slot + a_bytes, &full[ring.stage], cc * 32, p.org_w, p0 + p.org_h, n0);
         ring.advance();
       }
       if (!ok) {
@@ -149,7 +159,6 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
       detail::Ring ring{0, 0u, p.stages};
       bool ok = true;
       const int ksteps = p.rowsA_alloc / 8;
-      const uint32_t idesc = idesc_tf32(kTileM, 32 * p.S, 1, 1);
       for (int it = 0; it < n_iter; ++it) {
         if (!mbar_wait(&full[ring.stage], ring.phase, abort_flag)) {
           ok = false;
@@ -158,12 +167,13 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
         tc_fence_after();
         const uint32_t a_addr = slots0 + static_cast<uint32_t>(ring.stage) * stage_bytes;
         const uint64_t da = smem_desc(a_addr, a_box, 512, kSwizzle128BBase32B);
-        for (int r = 0; r < p.R; ++r) {
-          // the S taps of filter row r: column groups tap_col_pitch rows apart (the LBO)
-          const uint64_t db = smem_desc(a_addr + a_bytes + static_cast<uint32_t>(r * p.tap_row_pitch) * 128u,
+        for (int g = 0; g < p.ngroups; ++g) {
+          // the taps of a group are tap_col_pitch rows apart, which is the descriptor's LBO
+          const uint32_t idesc = idesc_tf32(kTileM, 32 * p.grp_n[g], 1, 1);
+          const uint64_t db = smem_desc(a_addr + a_bytes + static_cast<uint32_t>(p.grp_off[g]) * 128u,
                                         static_cast<uint32_t>(p.tap_col_pitch) * 128u, 512,
                                         kSwizzle128BBase32B);
-          const uint32_t d_tmem = tmem_base + 32u * (r * p.S);
+          const uint32_t d_tmem = tmem_base + 32u * p.grp_first[g];
           for (int k = 0; k < ksteps; ++k)
             mma_tf32(d_tmem, da + 64u * k, db + 64u * k, idesc, (it | k) != 0 ? 1u : 0u);
         }
@@ -184,7 +194,7 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
       tc_fence_after();
       float* base = p.out + static_cast<long long>(split) * p.split_stride;
       const int k = k0 + warp * 32 + lane;
-      for (int t = 0; t < p.T; ++t) {
+      for (int t = 0; t < p.ntaps; ++t) {
         float v[32];
         if (n_iter > 0) {
           tmem_ld32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + 32u * t, v);
@@ -194,7 +204,7 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
           for (int j = 0; j < 32; ++j) v[j] = 0.f;
         }
         if (k < p.K) {
-          float* dst = base + (static_cast<long long>(k) * p.T + t) * p.C + cc * 32;
+          float* dst = base + (static_cast<long long>(k) * p.T + p.btap[t]) * p.C + cc * 32;
           const int left = p.C - cc * 32;
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
@@ -230,34 +240,62 @@ struct Plan {
   int grid;
 };
 
-inline bool eligible(const mb_conv_desc* d) {
-  const int Wh = d->Q + (d->S - 1) * d->dil_w;
-  return d->stride_h == 1 && d->stride_w == 1 && d->R * d->S > 1 && d->R * d->S <= 16 && d->S <= 8 &&
-         Wh <= 256 && d->groups == 1;
-}
+struct Tap { int dh, dw, btap; };   // x pixel = dy pixel + (dh, dw) in the x view; filter tap index
 
-inline bool make_plan(const mb_conv_desc* d, int variant, Plan* pl) {
-  if (!eligible(d)) return false;
+// One launch: dy grid P x Q (x N images), an x view, and the taps that read that view.
+// `taps` must be sorted by (dh, dw).  Returns false when the geometry does not fit.
+inline bool plan_launch(int K, int C, int T, int N, int P, int Q, const Tap* taps, int ntaps,
+                        int variant, Plan* pl) {
+  if (ntaps < 1 || ntaps > 16) return false;
   WgHaloParams& p = pl->p;
   memset(&p, 0, sizeof(p));
-  p.K = d->K; p.C = d->C; p.T = d->R * d->S; p.R = d->R; p.S = d->S;
-  p.Wh = d->Q + (d->S - 1) * d->dil_w;
-  p.tap_row_pitch = d->dil_h * p.Wh;
-  p.tap_col_pitch = d->dil_w;
-  p.cchunks = (d->C + 31) / 32;
-  p.k_tiles = (d->K + kTileM - 1) / kTileM;
-  p.pad_h = d->pad_h; p.pad_w = d->pad_w;
-  const int halo_h = (d->R - 1) * d->dil_h;
+  p.K = K; p.C = C; p.T = T; p.ntaps = ntaps;
+  int min_dh = taps[0].dh, max_dh = taps[0].dh, min_dw = taps[0].dw, max_dw = taps[0].dw;
+  for (int t = 1; t < ntaps; ++t) {
+    if (taps[t].dh < min_dh) min_dh = taps[t].dh;
+    if (taps[t].dh > max_dh) max_dh = taps[t].dh;
+    if (taps[t].dw < min_dw) min_dw = taps[t].dw;
+    if (taps[t].dw > max_dw) max_dw = taps[t].dw;
+  }
+  const int halo_h = max_dh - min_dh, halo_w = max_dw - min_dw;
+  p.Wh = Q + halo_w;
+  if (p.Wh > 256) return false;
+  p.org_h = min_dh; p.org_w = min_dw;
+  // column pitch: smallest positive dw difference inside a row of taps
+  int pitch = 0;
+  for (int t = 1; t < ntaps; ++t)
+    if (taps[t].dh == taps[t - 1].dh && (pitch == 0 || taps[t].dw - taps[t - 1].dw < pitch))
+      pitch = taps[t].dw - taps[t - 1].dw;
+  if (pitch <= 0) pitch = 1;
+  p.tap_col_pitch = pitch;
+  int ng = 0;
+  for (int t = 0; t < ntaps; ++t) {
+    p.btap[t] = static_cast<unsigned char>(taps[t].btap);
+    const bool extend = ng > 0 && taps[t].dh == taps[t - 1].dh && taps[t].dw - taps[t - 1].dw == pitch &&
+                        p.grp_n[ng - 1] < 8;
+    if (extend) {
+      ++p.grp_n[ng - 1];
+    } else {
+      if (ng >= 16) return false;
+      p.grp_off[ng] = static_cast<short>((taps[t].dh - min_dh) * p.Wh + (taps[t].dw - min_dw));
+      p.grp_n[ng] = 1;
+      p.grp_first[ng] = static_cast<unsigned char>(t);
+      ++ng;
+    }
+  }
+  p.ngroups = ng;
+  p.cchunks = (C + 31) / 32;
+  p.k_tiles = (K + kTileM - 1) / kTileM;
   auto sizes = [&](int bh, int* ra, int* raa, int* rb, int* rba) {
     *ra = p.Wh * bh;
     *raa = (*ra + 7) / 8 * 8;
     *rb = p.Wh * (bh + halo_h);
-    // the last tap of the last (padding) dy row reads up to raa + halo rows + (S-1)*dil_w
-    const int reach = *raa + halo_h * p.Wh + (d->S - 1) * d->dil_w;
+    // the last tap of the last (padding) dy row reads up to raa + halo rows + halo columns
+    const int reach = *raa + halo_h * p.Wh + halo_w;
     *rba = ((reach > *rb ? reach : *rb) + 7) / 8 * 8;
   };
   int best_bh = 0;
-  for (int bh = d->P; bh >= 1; --bh) {
+  for (int bh = P; bh >= 1; --bh) {
     int ra, raa, rb, rba;
     sizes(bh, &ra, &raa, &rb, &rba);
     if (bh + halo_h > 256) continue;
@@ -270,11 +308,11 @@ inline bool make_plan(const mb_conv_desc* d, int variant, Plan* pl) {
     if (static_cast<size_t>(4 * raa + rba) * 128 > 107 * 1024) return false;
     best_bh = 1;
   }
-  p.tiles_h = (d->P + best_bh - 1) / best_bh;
-  p.bh = (d->P + p.tiles_h - 1) / p.tiles_h;          // balanced tiles
+  p.tiles_h = (P + best_bh - 1) / best_bh;
+  p.bh = (P + p.tiles_h - 1) / p.tiles_h;          // balanced tiles
   p.bhB = p.bh + halo_h;
   sizes(p.bh, &p.rowsA, &p.rowsA_alloc, &p.rowsB, &p.rowsB_alloc);
-  const long long tiles = static_cast<long long>(p.tiles_h) * d->N;
+  const long long tiles = static_cast<long long>(p.tiles_h) * N;
   if (tiles > 0x7fffffffLL) return false;
   p.pix_tiles = static_cast<int>(tiles);
   const size_t stage = static_cast<size_t>(4 * p.rowsA_alloc + p.rowsB_alloc) * 128;
@@ -297,14 +335,71 @@ inline bool make_plan(const mb_conv_desc* d, int variant, Plan* pl) {
   return true;
 }
 
+// The launches of a whole convolution: one for stride 1, one per non-empty stride phase
+// otherwise.  `phase[i]` says which input phase (a, b) launch i reads.
+struct Launches {
+  int n;
+  Plan plan[4];
+  int phase_a[4], phase_b[4];
+};
+
+// Stride 1 always; stride 2 only for large maps: a strided filter needs one launch per phase
+// and about twice the MMAs per pixel, which on small maps costs more than the per-tap boxes
+// of conv_wgrad.cuh (measured: 56->28 wins 2x, 28->14 and 14->7 lose 20 %).
+inline bool eligible(const mb_conv_desc* d) {
+  if (d->groups != 1 || d->R * d->S <= 1 || d->R * d->S > 16) return false;
+  if (d->stride_h == 1 && d->stride_w == 1) return true;
+  return d->stride_h <= 2 && d->stride_w <= 2 && d->Q >= 24 && d->P >= 24;
+}
+
+inline bool make_plans(const mb_conv_desc* d, int variant, Launches* L) {
+  if (!eligible(d)) return false;
+  L->n = 0;
+  for (int a = 0; a < d->stride_h; ++a)
+    for (int b = 0; b < d->stride_w; ++b) {
+      if (a >= d->H || b >= d->W) continue;
+      Tap taps[16];
+      int nt = 0;
+      for (int r = 0; r < d->R; ++r) {
+        const int oh = r * d->dil_h - d->pad_h;
+        if (((oh % d->stride_h) + d->stride_h) % d->stride_h != a) continue;
+        for (int s = 0; s < d->S; ++s) {
+          const int ow = s * d->dil_w - d->pad_w;
+          if (((ow % d->stride_w) + d->stride_w) % d->stride_w != b) continue;
+          taps[nt++] = Tap{(oh - a) / d->stride_h, (ow - b) / d->stride_w, r * d->S + s};
+        }
+      }
+      if (nt == 0) continue;
+      if (!plan_launch(d->K, d->C, d->R * d->S, d->N, d->P, d->Q, taps, nt, variant, &L->plan[L->n]))
+        return false;
+      L->phase_a[L->n] = a;
+      L->phase_b[L->n] = b;
+      ++L->n;
+    }
+  if (L->n == 0) return false;
+  if (variant == 1) {
+    // the deterministic variant sums per-split partials: every launch must use the same split
+    // count and together they must write every tap
+    for (int i = 1; i < L->n; ++i)
+      if (L->plan[i].p.splits != L->plan[0].p.splits) {
+        const int s0 = L->plan[0].p.splits < L->plan[i].p.splits ? L->plan[0].p.splits : L->plan[i].p.splits;
+        for (int j = 0; j < L->n; ++j) {
+          L->plan[j].p.splits = s0;
+          L->plan[j].grid = L->plan[j].p.k_tiles * L->plan[j].p.cchunks * s0;
+        }
+      }
+  }
+  return true;
+}
+
 }  // namespace wgh
 
 // Workspace of the deterministic variant: one partial dw per split of whichever kernel runs.
 inline size_t wgrad_workspace_bytes(const mb_conv_desc* d, int variant) {
   if (variant != 1 || d->groups != 1) return 0;
   const size_t dw_bytes = static_cast<size_t>(d->K) * d->R * d->S * d->C * sizeof(float);
-  wgh::Plan hp;
-  if (wgh::make_plan(d, variant, &hp)) return hp.p.splits * dw_bytes;
+  wgh::Launches hl;
+  if (wgh::make_plans(d, variant, &hl)) return hl.plan[0].p.splits * dw_bytes;
   wg::Plan pl;
   if (!wg::make_plan(d, variant, &pl)) return 0;
   return pl.p.splits * dw_bytes;
