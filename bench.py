@@ -231,6 +231,18 @@ def family_costs(runner_obj, batch_shape):
     return cost
 
 
+# DRAM traffic measured by ncu on one layer per kernel family, as a fraction of that layer's
+# algorithmic bytes (profiles/conv_bn_pointwise_kernels_ncu_full.md).  A whole step is too large to
+# capture under ncu, and every one of these kernels streams its operands once, so the traffic
+# of a step's launches is taken to grow in proportion to their algorithmic bytes.
+TRAFFIC_RATIO = {
+    "mb_conv2d_fprop": 679.8 / 738.7, "mb_conv2d_dgrad": 679.8 / 738.7, "mb_conv2d_wgrad": 742.9 / 738.7,
+    "mb_bn_bwd_from_output": 1740.8 / 1772.0, "mb_bn_bwd_from_input": 1740.8 / 1772.0,
+    "mb_bn_fwd_train": 594.7 / 591.0, "mb_relu_fwd": 1136.5 / 1182.0, "mb_relu_bwd_act": 1744.0 / 1772.0,
+    "mb_add_fwd": 1743.8 / 1772.0, "mb_maxpool2d_bwd": 710.5 / 756.0,
+}
+
+
 # ----------------------------------------------------------------------------- ours
 def run_ours(args):
     import torch
@@ -380,7 +392,9 @@ def run_ours(args):
         else:
             roof = {"bound": "tensor", "achieved": f / (dom_ms * 1e-3) / 1e12, "peak": tf32, "unit": "TFLOP/s"}
         roof["frac"] = roof["achieved"] / roof["peak"]
-        roof.update({"traffic": None, "kernel": dominant, "launches_per_step": dom_calls,
+        ratio = TRAFFIC_RATIO.get(dominant)
+        roof.update({"traffic": (ratio * b / dom_calls / 1e9) if ratio else None, "traffic_unit": "GB per launch (ncu ratio x algorithmic bytes)",
+                     "algorithmic_gb_per_launch": b / dom_calls / 1e9, "kernel": dominant, "launches_per_step": dom_calls,
                      "ms_per_step": dom_ms, "peak_source": which,
                      "note": "entry point timed with CUDA events inside the timed region; "
                              "tensor peak = measured sustained bf16 / 2 (TF32)"})
