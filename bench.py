@@ -37,6 +37,9 @@ def parse():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--schedule", default="low_memory", choices=["low_memory", "store_all"])
+    ap.add_argument("--no-fuse", action="store_true",
+                    help="run batch norm, residual add and ReLU as separate operators, as the "
+                         "reference's graph does")
     ap.add_argument("--batch", type=int, default=184)
     ap.add_argument("--cpu-batch", type=int, default=16, help="images per step of the CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -59,6 +62,8 @@ MICRO = {
     "bn_fwd": ("bn_fwd", 256, 56, 0, 0, 0, 0), "bn_bwd": ("bn_bwd", 256, 56, 0, 0, 0, 0),
     "relu_fwd": ("relu_fwd", 256, 56, 0, 0, 0, 0), "relu_fwd_mask": ("relu_fwd_mask", 256, 56, 0, 0, 0, 0),
     "relu_bwd": ("relu_bwd", 256, 56, 0, 0, 0, 0), "add": ("add", 256, 56, 0, 0, 0, 0),
+    "bn_relu_fwd": ("bn_relu_fwd", 256, 56, 0, 0, 0, 0), "bn_add_relu_fwd": ("bn_add_relu_fwd", 256, 56, 0, 0, 0, 0),
+    "bn_relu_bwd": ("bn_relu_bwd", 256, 56, 0, 0, 0, 0), "relu_bwd2": ("relu_bwd2", 256, 56, 0, 0, 0, 0),
     "maxpool_fwd": ("maxpool_fwd", 64, 112, 0, 0, 0, 0), "maxpool_bwd": ("maxpool_bwd", 64, 112, 0, 0, 0, 0),
 }
 
@@ -93,6 +98,16 @@ def run_micro(args):
         elif kind == "bn_bwd":
             yb, _, iv = F.bn_fwd_train(x, g, b, None, None, 0.1, 1e-5)
             nbytes, fn = 20 * E, lambda: F.bn_bwd_from_output(dy, yb, g, b, iv)
+        elif kind == "bn_relu_fwd":
+            nbytes, fn = 12 * E, lambda: F.bn_act_fwd_train(x, None, True, g, b, None, None, 0.1, 1e-5)
+        elif kind == "bn_add_relu_fwd":
+            nbytes, fn = 16 * E, lambda: F.bn_act_fwd_train(x, dy, True, g, b, None, None, 0.1, 1e-5)
+        elif kind == "bn_relu_bwd":
+            _, mu, iv = F.bn_fwd_train(x, g, b, None, None, 0.1, 1e-5)
+            nbytes, fn = 20 * E, lambda: F.bn_relu_bwd_from_input(dy, x, g, b, mu, iv)
+        elif kind == "relu_bwd2":
+            dy2 = torch.randn_like(x)
+            nbytes, fn = 16 * E, lambda: F.relu_bwd_act2(dy, dy2, x)
         elif kind == "relu_fwd":
             nbytes, fn = 8 * E, lambda: F.relu(x)
         elif kind == "relu_fwd_mask":
@@ -192,8 +207,10 @@ def family_costs(runner_obj, batch_shape):
     graph and the recorded shapes (fp32: 4 bytes per element).
 
     conv pass: activations in + filter + activations out, 2*N*P*Q*K*C*R*S flops.
-    bn train fwd 12 B/el, bn cached-stat fwd 8, bn bwd 20, relu fwd 8 (+1/8 with mask),
-    relu bwd from a saved activation 12, add 12, max-pool 4*E_in + 4.5*E_out each way."""
+    bn train fwd 12 B/el (16 with a residual operand), bn cached-stat fwd 8, bn bwd 20 (also
+    when it gates by the recomputed ReLU), relu fwd 8 (+1/8 with mask), relu bwd from a saved
+    activation 12 (16 when it also sums two gradients), add 12, max-pool 4*E_in + 4.5*E_out
+    each way."""
     import numpy as np
     cost = {}
 
@@ -220,6 +237,16 @@ def family_costs(runner_obj, batch_shape):
         elif n.op == 'aten::batch_norm':
             add("mb_bn_fwd_train", 12 * e_out)
             add("mb_bn_bwd_from_output" if ch.impl == 1 else "mb_bn_bwd_from_input", 20 * e_out)
+        elif n.op == 'monet::batch_norm_relu':
+            add("mb_bn_act_fwd_train", 12 * e_out)
+            if ch.recompute:
+                add("mb_bn_act_fwd_apply", 8 * e_out)
+            add("mb_bn_relu_bwd_from_input", 20 * e_out)
+        elif n.op == 'monet::batch_norm_add_relu':
+            add("mb_bn_act_fwd_train", 16 * e_out)
+            add("mb_relu_bwd_act2" if len(n.users) == 2 else "mb_relu_bwd_act",
+                (16 if len(n.users) == 2 else 12) * e_out)
+            add("mb_bn_bwd_from_input", 20 * e_out)
         elif n.op in ('aten::relu', 'aten::relu_'):
             add("mb_relu_fwd", 8 * e_out * (2 if ch.recompute else 1))
             add("mb_relu_bwd_act", 12 * e_out)
@@ -238,7 +265,8 @@ def family_costs(runner_obj, batch_shape):
 TRAFFIC_RATIO = {
     "mb_conv2d_fprop": 679.8 / 738.7, "mb_conv2d_dgrad": 679.8 / 738.7, "mb_conv2d_wgrad": 742.9 / 738.7,
     "mb_bn_bwd_from_output": 1740.8 / 1772.0, "mb_bn_bwd_from_input": 1740.8 / 1772.0,
-    "mb_bn_fwd_train": 594.7 / 591.0, "mb_relu_fwd": 1136.5 / 1182.0, "mb_relu_bwd_act": 1744.0 / 1772.0,
+    "mb_bn_relu_bwd_from_input": 1740.8 / 1772.0,
+    "mb_bn_fwd_train": 594.7 / 591.0, "mb_bn_act_fwd_train": 594.7 / 591.0, "mb_relu_fwd": 1136.5 / 1182.0, "mb_relu_bwd_act": 1744.0 / 1772.0,
     "mb_add_fwd": 1743.8 / 1772.0, "mb_maxpool2d_bwd": 710.5 / 756.0,
 }
 
@@ -279,7 +307,7 @@ def run_ours(args):
             views.append(flat[off:off + p.numel()].view(p.shape))
             off += p.numel()
     policy = getattr(runner, args.schedule)
-    run = runner.Runner(model, policy)
+    run = runner.Runner(model, policy, fuse=not args.no_fuse)
     ce = SoftmaxCrossEntropy()
 
     B = args.batch
@@ -347,8 +375,10 @@ def run_ours(args):
     barrier()
     t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
     t0.record()
+    h0 = time.perf_counter()
     for _ in range(args.steps):
         loss = step(x_dev, y_dev)
+    host_ms = (time.perf_counter() - h0) * 1e3 / args.steps   # host time to enqueue one step
     t1.record()
     barrier()
     _lib.set_probe()
@@ -403,12 +433,13 @@ def run_ours(args):
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_dev,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32(tf32 conv)",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD, "schedule": args.schedule, "global_batch": B * world,
+            "config": {"workload": WORKLOAD, "schedule": args.schedule,
+                       "fused_bn_add_relu": not args.no_fuse, "global_batch": B * world,
                        "parallelism": f"dp{world}", "l2": "inputs and activations exceed L2 (126 MB) many times over"},
             "peak_gb": peak / 2 ** 30, "loss": last,
             "e2e": {"value": B * world / (ms_e2e * 1e-3), "unit": "images/s",
                     "h2d_bytes_per_step": x_host.numel() * 4 + y_host.numel() * 8, "d2h_bytes_per_step": 4},
-            "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
+            "host_enqueue_ms": host_ms, "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
             "family_ms_survey": {k: round(v, 3) for k, v in sorted(survey.items(), key=lambda kv: -kv[1])[:12]},
         }
         if not args.no_cpu_baseline and world >= 1:

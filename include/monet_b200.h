@@ -67,6 +67,12 @@ int mb_relu_bwd_mask(const float* dy, const uint8_t* mask, float* dx, size_t n, 
  * works in place on dy, lrrelu.cpp:14-15).                                  */
 int mb_relu_bwd_act(const float* dy, const float* act, float threshold, float* dx, size_t n,
                     void* stream);
+/* dx = act > threshold ? dy1 + dy2 : 0.  A tensor read by two consumers (a
+ * residual block's input) receives two gradients; the reference's executor sums
+ * them with a separate add (schedule.py:296-301) before relu.py's backward.
+ * dx may alias dy1 or dy2.                                                  */
+int mb_relu_bwd_act2(const float* dy1, const float* dy2, const float* act, float threshold,
+                     float* dx, size_t n, void* stream);
 
 /* ---- bit / nibble packing (replaces pack.cpp:38-131, pack.cu:3-50) ------ */
 
@@ -91,6 +97,8 @@ int mb_hardtanh_bwd(const float* dy, const float* act, float lo, float hi, float
 
 /* y = a + alpha * b.  y may alias a (AddIP with op.inplace).                */
 int mb_add_fwd(const float* a, const float* b, float alpha, float* y, size_t n, void* stream);
+/* y = relu(a + alpha * b): funcs.py add followed by relu.py forward in one pass. */
+int mb_add_relu_fwd(const float* a, const float* b, float alpha, float* y, size_t n, void* stream);
 /* y = alpha * x  (the `grad_output * s` of Add.backward when s != 1).       */
 int mb_scale(const float* x, float alpha, float* y, size_t n, void* stream);
 
@@ -165,6 +173,28 @@ int mb_bn_bwd_from_input(const float* dy, const float* x, const float* gamma,
                          const float* save_mean, const float* save_invstd, float* dx,
                          float* dgamma, float* dbeta, const mb_bn_desc* d, void* workspace,
                          size_t workspace_bytes, void* stream);
+
+/* Fused forms.  The reference runs batch norm, the residual add and ReLU as
+ * three operators (bn.py, funcs.py add, relu.py), i.e. three passes over the
+ * activation; these do the same arithmetic in the batch-norm sweep.
+ *   y = act(bn(x) + residual),  residual may be null, act = ReLU when relu != 0.
+ * Same statistics, workspace and aliasing rules as mb_bn_fwd_train / _apply
+ * (y may alias x or residual).                                                */
+int mb_bn_act_fwd_train(const float* x, const float* residual, int relu, const float* gamma,
+                        const float* beta, float* running_mean, float* running_var, float* y,
+                        float* save_mean, float* save_invstd, const mb_bn_desc* d, void* workspace,
+                        size_t workspace_bytes, void* stream);
+int mb_bn_act_fwd_apply(const float* x, const float* residual, int relu, const float* gamma,
+                        const float* beta, const float* mean, const float* invstd, float* y,
+                        const mb_bn_desc* d, void* stream);
+/* Backward through y = relu(bn(x)) from the stored INPUT x: relu.py's backward
+ * (dy gated by y > 0) followed by cudnn_backward (lrbn.cpp:43-70) in one reduce
+ * and one sweep.  The gate is re-evaluated from x with the forward's own
+ * expression, so neither y nor a mask has to be kept.  dx may alias dy.       */
+int mb_bn_relu_bwd_from_input(const float* dy, const float* x, const float* gamma,
+                              const float* beta, const float* save_mean, const float* save_invstd,
+                              float* dx, float* dgamma, float* dbeta, const mb_bn_desc* d,
+                              void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---- softmax / cross-entropy (replaces softmax.cpp:11-33, softmax.cu) --- */
 

@@ -48,6 +48,7 @@ PROTOTYPES = {
     "mb_relu_fwd_mask": (C.c_int, [c_f, c_f, c_f, c_sz, c_f]),
     "mb_relu_bwd_mask": (C.c_int, [c_f, c_f, c_f, c_sz, c_f]),
     "mb_relu_bwd_act": (C.c_int, [c_f, c_f, C.c_float, c_f, c_sz, c_f]),
+    "mb_relu_bwd_act2": (C.c_int, [c_f, c_f, c_f, C.c_float, c_f, c_sz, c_f]),
     "mb_pack_bits": (C.c_int, [c_f, c_f, c_sz, c_f]),
     "mb_unpack_bits": (C.c_int, [c_f, c_f, c_sz, c_f]),
     "mb_unpack_multiply": (C.c_int, [c_f, c_f, c_f, c_sz, c_f]),
@@ -56,6 +57,7 @@ PROTOTYPES = {
     "mb_hardtanh_fwd": (C.c_int, [c_f, c_f, C.c_float, C.c_float, c_sz, c_f]),
     "mb_hardtanh_bwd": (C.c_int, [c_f, c_f, C.c_float, C.c_float, c_f, c_sz, c_f]),
     "mb_add_fwd": (C.c_int, [c_f, c_f, C.c_float, c_f, c_sz, c_f]),
+    "mb_add_relu_fwd": (C.c_int, [c_f, c_f, C.c_float, c_f, c_sz, c_f]),
     "mb_scale": (C.c_int, [c_f, C.c_float, c_f, c_sz, c_f]),
     "mb_pool_out_size": (C.c_int, [C.c_int] * 6),
     "mb_maxpool2d_fwd": (C.c_int, [c_f, c_f, c_f, C.POINTER(PoolDesc), c_f]),
@@ -66,6 +68,9 @@ PROTOTYPES = {
     "mb_bn_fwd_apply": (C.c_int, [c_f] * 6 + [C.POINTER(BnDesc), c_f]),
     "mb_bn_bwd_from_output": (C.c_int, [c_f] * 8 + [C.POINTER(BnDesc), c_f, c_sz, c_f]),
     "mb_bn_bwd_from_input": (C.c_int, [c_f] * 8 + [C.POINTER(BnDesc), c_f, c_sz, c_f]),
+    "mb_bn_act_fwd_train": (C.c_int, [c_f, c_f, C.c_int] + [c_f] * 7 + [C.POINTER(BnDesc), c_f, c_sz, c_f]),
+    "mb_bn_act_fwd_apply": (C.c_int, [c_f, c_f, C.c_int] + [c_f] * 5 + [C.POINTER(BnDesc), c_f]),
+    "mb_bn_relu_bwd_from_input": (C.c_int, [c_f] * 9 + [C.POINTER(BnDesc), c_f, c_sz, c_f]),
     "mb_softmax_fwd": (C.c_int, [c_f, c_f, c_sz, C.c_int, c_sz, C.c_int, c_f]),
     "mb_softmax_bwd": (C.c_int, [c_f, c_f, c_f, c_sz, C.c_int, c_sz, C.c_int, c_f]),
     "mb_softmax_ce_fwd_bwd": (C.c_int, [c_f, c_f, c_f, c_f, c_sz, C.c_int, c_sz, C.c_float, c_f]),

@@ -22,6 +22,13 @@
 //   from output: xhat = (y - beta) / gamma          (lrbn.cu:153-175)
 // and then   dx = (dy - xhat*S2/M - S1/M) * invstd * gamma,  dgamma = S2,
 // dbeta = S1  (lrbn.cu:176-208 written in terms of xhat).
+//
+// Fused forms (one sweep instead of two or three element-wise passes):
+//   forward   y = act(bn(x) [+ residual]),  act = ReLU or identity
+//   backward  through y = relu(bn(x)) from the stored INPUT x: the ReLU gate z > 0 is
+//             re-evaluated from x with exactly the forward's expression
+//             z = fma(x - mean, invstd*gamma, beta), so no mask and no output is kept and
+//             dy is gated on the fly in both the reduce and the sweep.
 #include "common.cuh"
 
 #include <mutex>
@@ -80,29 +87,35 @@ Geometry make_geometry(const mb_bn_desc* d) {
 // workspace: partials [2][S][C] floats, then constants [2][C] floats
 size_t ws_floats(const Geometry& g) { return (2 * static_cast<size_t>(g.S) + 2) * g.C; }
 
-enum { kFwd = 0, kBwd = 1 };
+enum { kFwd = 0, kBwd = 1, kBwdRelu = 2, kFwdRes = 3 };
 
 // ------------------------------------------------------------- NHWC reduce
 // MODE kFwd: a = x;          accumulates (x-K), (x-K)^2
 // MODE kBwd: a = dy, b = v;  accumulates dy, dy*(v-p0)*p1
+// MODE kBwdRelu: a = dy, b = x, p0 = mean, p1 = invstd; dy is first gated by
+//                fma(x-mean, invstd*gamma, beta) > 0
 template <int MODE, int VEC>
 __global__ void __launch_bounds__(kBlock) bn_reduce_nhwc(const float* __restrict__ a,
                                                          const float* __restrict__ b,
                                                          const float* __restrict__ p0v,
                                                          const float* __restrict__ p1v,
-                                                         int p1_is_gamma, float* __restrict__ ws,
+                                                         int p1_is_gamma,
+                                                         const float* __restrict__ gv,
+                                                         const float* __restrict__ bv,
+                                                         float* __restrict__ ws,
                                                          int C, size_t M, int S, int tx_n,
                                                          int ty_n) {
   extern __shared__ float sm[];  // [ty_n][tx_n][2*VEC]
   const int tx = threadIdx.x % tx_n, ty = threadIdx.x / tx_n;
   const int c0 = (blockIdx.y * tx_n + tx) * VEC;
   const bool live = c0 < C;
-  float s1[VEC], s2[VEC], p0[VEC], p1[VEC];
+  float s1[VEC], s2[VEC], p0[VEC], p1[VEC], pg[VEC], pb[VEC];
 #pragma unroll
   for (int k = 0; k < VEC; ++k) {
     s1[k] = s2[k] = 0.f;
     p0[k] = 0.f;
     p1[k] = 1.f;
+    pg[k] = pb[k] = 0.f;
   }
   if (live) {
 #pragma unroll
@@ -113,6 +126,10 @@ __global__ void __launch_bounds__(kBlock) bn_reduce_nhwc(const float* __restrict
         p0[k] = __ldg(p0v + c0 + k);
         float t = __ldg(p1v + c0 + k);
         p1[k] = p1_is_gamma ? 1.f / t : t;
+        if (MODE == kBwdRelu) {
+          pg[k] = t * __ldg(gv + c0 + k);
+          pb[k] = __ldg(bv + c0 + k);
+        }
       }
     }
     const size_t rows_per = (M + S - 1) / S;
@@ -128,7 +145,7 @@ __global__ void __launch_bounds__(kBlock) bn_reduce_nhwc(const float* __restrict
         for (int i = 0; i < 4; ++i) {
           const size_t off = (r + i * static_cast<size_t>(ty_n)) * C + c0;
           u[i] = __ldcs(reinterpret_cast<const float4*>(a + off));
-          if (MODE == kBwd) w[i] = __ldcs(reinterpret_cast<const float4*>(b + off));
+          if (MODE != kFwd) w[i] = __ldcs(reinterpret_cast<const float4*>(b + off));
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -141,8 +158,10 @@ __global__ void __launch_bounds__(kBlock) bn_reduce_nhwc(const float* __restrict
               s1[k] += dlt;
               s2[k] = fmaf(dlt, dlt, s2[k]);
             } else {
-              s1[k] += uu[k];
-              s2[k] = fmaf(uu[k], (ww[k] - p0[k]) * p1[k], s2[k]);
+              float d = uu[k];
+              if (MODE == kBwdRelu) d = fmaf(ww[k] - p0[k], pg[k], pb[k]) > 0.f ? d : 0.f;
+              s1[k] += d;
+              s2[k] = fmaf(d, (ww[k] - p0[k]) * p1[k], s2[k]);
             }
           }
         }
@@ -159,8 +178,10 @@ __global__ void __launch_bounds__(kBlock) bn_reduce_nhwc(const float* __restrict
           s2[k] = fmaf(dlt, dlt, s2[k]);
         } else {
           const float ww = __ldg(b + off + k);
-          s1[k] += uu;
-          s2[k] = fmaf(uu, (ww - p0[k]) * p1[k], s2[k]);
+          float d = uu;
+          if (MODE == kBwdRelu) d = fmaf(ww - p0[k], pg[k], pb[k]) > 0.f ? d : 0.f;
+          s1[k] += d;
+          s2[k] = fmaf(d, (ww - p0[k]) * p1[k], s2[k]);
         }
       }
     }
@@ -198,17 +219,24 @@ __global__ void __launch_bounds__(kBlock) bn_reduce_nchw(const float* __restrict
                                                          const float* __restrict__ b,
                                                          const float* __restrict__ p0v,
                                                          const float* __restrict__ p1v,
-                                                         int p1_is_gamma, float* __restrict__ ws,
+                                                         int p1_is_gamma,
+                                                         const float* __restrict__ gv,
+                                                         const float* __restrict__ bv,
+                                                         float* __restrict__ ws,
                                                          int C, int HW, size_t M, int S) {
   __shared__ float red[2][kBlock / 32];
   const int c = blockIdx.x;
-  float p0, p1 = 1.f;
+  float p0, p1 = 1.f, pg = 0.f, pb = 0.f;
   if (MODE == kFwd) {
     p0 = __ldg(a + static_cast<size_t>(c) * HW);
   } else {
     p0 = __ldg(p0v + c);
     float t = __ldg(p1v + c);
     p1 = p1_is_gamma ? 1.f / t : t;
+    if (MODE == kBwdRelu) {
+      pg = t * __ldg(gv + c);
+      pb = __ldg(bv + c);
+    }
   }
   const size_t per = (M + S - 1) / S;
   const size_t j0 = static_cast<size_t>(blockIdx.y) * per;
@@ -225,8 +253,10 @@ __global__ void __launch_bounds__(kBlock) bn_reduce_nchw(const float* __restrict
       s2 = fmaf(dlt, dlt, s2);
     } else {
       const float w = __ldg(b + off);
-      s1 += u;
-      s2 = fmaf(u, (w - p0) * p1, s2);
+      float d = u;
+      if (MODE == kBwdRelu) d = fmaf(w - p0, pg, pb) > 0.f ? d : 0.f;
+      s1 += d;
+      s2 = fmaf(d, (w - p0) * p1, s2);
     }
   }
   s1 = warp_sum(s1);
@@ -311,8 +341,11 @@ __global__ void __launch_bounds__(32 * kFinStripes) bn_finalize(
 }
 
 // ------------------------------------------------------------------- sweeps
-// MODE kFwd: out = (a - mean)*(invstd*gamma) + beta
-// MODE kBwd: out = (a - xhat*k2 - k1)*(invstd*gamma),  a = dy, xhat = (b-p0)*p1
+// MODE kFwd:     out = act((a - mean)*(invstd*gamma) + beta)
+// MODE kFwdRes:  out = act((a - mean)*(invstd*gamma) + beta + b),  b = residual
+// MODE kBwd:     out = (a - xhat*k2 - k1)*(invstd*gamma),  a = dy, xhat = (b-p0)*p1
+// MODE kBwdRelu: as kBwd with b = x, p0 = mean, p1 = invstd and a gated by
+//                fma(x-mean, invstd*gamma, beta) > 0
 struct SweepConst {
   const float* gamma;
   const float* beta;    // fwd
@@ -322,12 +355,14 @@ struct SweepConst {
   const float* p1v;     // bwd
   int p1_is_gamma;
   const float* k12;     // bwd: [2][C]
+  int relu;             // fwd modes: clamp the result at zero
 };
 
 template <int MODE>
 __device__ __forceinline__ void load_const(const SweepConst& k, int c, int C, float& q0, float& q1,
-                                           float& q2, float& q3, float& q4) {
-  if (MODE == kFwd) {
+                                           float& q2, float& q3, float& q4, float& q5) {
+  q5 = 0.f;
+  if (MODE == kFwd || MODE == kFwdRes) {
     q0 = __ldg(k.mean + c);
     q1 = __ldg(k.invstd + c) * __ldg(k.gamma + c);
     q2 = __ldg(k.beta + c);
@@ -339,13 +374,19 @@ __device__ __forceinline__ void load_const(const SweepConst& k, int c, int C, fl
     q2 = __ldg(k.k12 + c);      // S1/M
     q3 = __ldg(k.k12 + C + c);  // S2/M
     q4 = __ldg(k.invstd + c) * __ldg(k.gamma + c);
+    if (MODE == kBwdRelu) q5 = __ldg(k.beta + c);
   }
 }
 
 template <int MODE>
 __device__ __forceinline__ float sweep1(float a, float b, float q0, float q1, float q2, float q3,
-                                        float q4) {
-  if (MODE == kFwd) return fmaf(a - q0, q1, q2);
+                                        float q4, float q5, int relu) {
+  if (MODE == kFwd || MODE == kFwdRes) {
+    float z = fmaf(a - q0, q1, q2);
+    if (MODE == kFwdRes) z += b;
+    return relu ? (z > 0.f ? z : (z != z ? z : 0.f)) : z;   // NaN passes through, as in ReLU
+  }
+  if (MODE == kBwdRelu) a = fmaf(b - q0, q4, q5) > 0.f ? a : 0.f;
   const float xhat = (b - q0) * q1;
   return (a - xhat * q3 - q2) * q4;
 }
@@ -357,9 +398,10 @@ __global__ void __launch_bounds__(kBlock) bn_sweep_nhwc(const float* a, const fl
   const int tx = threadIdx.x % tx_n, ty = threadIdx.x / tx_n;
   const int c0 = (blockIdx.y * tx_n + tx) * VEC;
   if (c0 >= C) return;
-  float q0[VEC], q1[VEC], q2[VEC], q3[VEC], q4[VEC];
+  float q0[VEC], q1[VEC], q2[VEC], q3[VEC], q4[VEC], q5[VEC];
 #pragma unroll
-  for (int i = 0; i < VEC; ++i) load_const<MODE>(k, c0 + i, C, q0[i], q1[i], q2[i], q3[i], q4[i]);
+  for (int i = 0; i < VEC; ++i) load_const<MODE>(k, c0 + i, C, q0[i], q1[i], q2[i], q3[i], q4[i], q5[i]);
+  const int relu = k.relu;
   const size_t step = static_cast<size_t>(gridDim.x) * ty_n;
   size_t r = static_cast<size_t>(blockIdx.x) * ty_n + ty;
   if (VEC == 4) {
@@ -369,15 +411,15 @@ __global__ void __launch_bounds__(kBlock) bn_sweep_nhwc(const float* a, const fl
       for (int i = 0; i < 4; ++i) {
         const size_t off = (r + i * step) * C + c0;
         u[i] = *reinterpret_cast<const float4*>(a + off);
-        if (MODE == kBwd) w[i] = *reinterpret_cast<const float4*>(b + off);
+        if (MODE != kFwd) w[i] = *reinterpret_cast<const float4*>(b + off);
       }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         float4 o;
-        o.x = sweep1<MODE>(u[i].x, w[i].x, q0[0], q1[0], q2[0], q3[0], q4[0]);
-        o.y = sweep1<MODE>(u[i].y, w[i].y, q0[1], q1[1], q2[1], q3[1], q4[1]);
-        o.z = sweep1<MODE>(u[i].z, w[i].z, q0[2], q1[2], q2[2], q3[2], q4[2]);
-        o.w = sweep1<MODE>(u[i].w, w[i].w, q0[3], q1[3], q2[3], q3[3], q4[3]);
+        o.x = sweep1<MODE>(u[i].x, w[i].x, q0[0], q1[0], q2[0], q3[0], q4[0], q5[0], relu);
+        o.y = sweep1<MODE>(u[i].y, w[i].y, q0[1], q1[1], q2[1], q3[1], q4[1], q5[1], relu);
+        o.z = sweep1<MODE>(u[i].z, w[i].z, q0[2], q1[2], q2[2], q3[2], q4[2], q5[2], relu);
+        o.w = sweep1<MODE>(u[i].w, w[i].w, q0[3], q1[3], q2[3], q3[3], q4[3], q5[3], relu);
         *reinterpret_cast<float4*>(out + (r + i * step) * C + c0) = o;
       }
     }
@@ -387,8 +429,8 @@ __global__ void __launch_bounds__(kBlock) bn_sweep_nhwc(const float* a, const fl
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
       const float u = a[off + i];
-      const float w = MODE == kBwd ? b[off + i] : 0.f;
-      out[off + i] = sweep1<MODE>(u, w, q0[i], q1[i], q2[i], q3[i], q4[i]);
+      const float w = MODE != kFwd ? b[off + i] : 0.f;
+      out[off + i] = sweep1<MODE>(u, w, q0[i], q1[i], q2[i], q3[i], q4[i], q5[i], relu);
     }
   }
 }
@@ -398,13 +440,13 @@ template <int MODE>
 __global__ void __launch_bounds__(kBlock) bn_sweep_nchw(const float* a, const float* b, float* out,
                                                         SweepConst k, int C, int HW) {
   const int c = blockIdx.x % C;
-  float q0, q1, q2, q3, q4;
-  load_const<MODE>(k, c, C, q0, q1, q2, q3, q4);
+  float q0, q1, q2, q3, q4, q5;
+  load_const<MODE>(k, c, C, q0, q1, q2, q3, q4, q5);
   const size_t base = static_cast<size_t>(blockIdx.x) * HW;
   for (int i = blockIdx.y * kBlock + threadIdx.x; i < HW; i += gridDim.y * kBlock) {
     const float u = a[base + i];
-    const float w = MODE == kBwd ? b[base + i] : 0.f;
-    out[base + i] = sweep1<MODE>(u, w, q0, q1, q2, q3, q4);
+    const float w = MODE != kFwd ? b[base + i] : 0.f;
+    out[base + i] = sweep1<MODE>(u, w, q0, q1, q2, q3, q4, q5, k.relu);
   }
 }
 
@@ -420,17 +462,17 @@ int check(const char* who, const mb_bn_desc* d) {
 template <int MODE>
 int run_reduce(const char* who, const mb_bn_desc* d, const Geometry& g, const float* a,
                const float* b, const float* p0v, const float* p1v, int p1_is_gamma, float* ws,
-               cudaStream_t st) {
+               cudaStream_t st, const float* gv = nullptr, const float* bv = nullptr) {
   if (d->layout == MB_NHWC) {
     dim3 grid(g.S, g.slabs);
     const size_t smem = static_cast<size_t>(kBlock) * 2 * g.vec * sizeof(float);
     if (g.vec == 4)
-      bn_reduce_nhwc<MODE, 4><<<grid, kBlock, smem, st>>>(a, b, p0v, p1v, p1_is_gamma, ws, g.C, g.M, g.S, g.tx, g.ty);
+      bn_reduce_nhwc<MODE, 4><<<grid, kBlock, smem, st>>>(a, b, p0v, p1v, p1_is_gamma, gv, bv, ws, g.C, g.M, g.S, g.tx, g.ty);
     else
-      bn_reduce_nhwc<MODE, 1><<<grid, kBlock, smem, st>>>(a, b, p0v, p1v, p1_is_gamma, ws, g.C, g.M, g.S, g.tx, g.ty);
+      bn_reduce_nhwc<MODE, 1><<<grid, kBlock, smem, st>>>(a, b, p0v, p1v, p1_is_gamma, gv, bv, ws, g.C, g.M, g.S, g.tx, g.ty);
   } else {
     dim3 grid(g.C, g.S);
-    bn_reduce_nchw<MODE><<<grid, kBlock, 0, st>>>(a, b, p0v, p1v, p1_is_gamma, ws, g.C, g.HW, g.M, g.S);
+    bn_reduce_nchw<MODE><<<grid, kBlock, 0, st>>>(a, b, p0v, p1v, p1_is_gamma, gv, bv, ws, g.C, g.HW, g.M, g.S);
   }
   return after_launch(who);
 }
@@ -470,7 +512,7 @@ int check_alignment(const char* who, const mb_bn_desc* d, const void* p0, const 
 int bwd_common(const char* who, const float* dy, const float* v, const float* gamma,
                const float* p0v, const float* p1v, int p1_is_gamma, const float* invstd, float* dx,
                float* dgamma, float* dbeta, const mb_bn_desc* d, void* workspace,
-               size_t workspace_bytes, void* stream) {
+               size_t workspace_bytes, void* stream, const float* relu_beta = nullptr) {
   int rc = check(who, d);
   if (rc) return rc;
   if (!dy || !v || !gamma || !p0v || !p1v || !invstd || !dx || !dgamma || !dbeta)
@@ -484,13 +526,17 @@ int bwd_common(const char* who, const float* dy, const float* v, const float* ga
   float* ws = static_cast<float*>(workspace);
   float* ws_const = ws + 2 * static_cast<size_t>(g.S) * g.C;
   cudaStream_t st = as_stream(stream);
-  rc = run_reduce<kBwd>("bn_bwd_reduce", d, g, dy, v, p0v, p1v, p1_is_gamma, ws, st);
+  if (relu_beta)
+    rc = run_reduce<kBwdRelu>("bn_relu_bwd_reduce", d, g, dy, v, p0v, p1v, 0, ws, st, gamma, relu_beta);
+  else
+    rc = run_reduce<kBwd>("bn_bwd_reduce", d, g, dy, v, p0v, p1v, p1_is_gamma, ws, st);
   if (rc) return rc;
   bn_finalize<kBwd><<<(g.C + 31) / 32, 32 * kFinStripes, 0, st>>>(ws, ws_const, nullptr, 0, g.C, g.M, g.S, 0.f,
                                                     0.f, nullptr, nullptr, dgamma, dbeta);
   rc = after_launch("bn_bwd_finalize");
   if (rc) return rc;
-  SweepConst k{gamma, nullptr, nullptr, invstd, p0v, p1v, p1_is_gamma, ws_const};
+  SweepConst k{gamma, relu_beta, nullptr, invstd, p0v, p1v, p1_is_gamma, ws_const, 0};
+  if (relu_beta) return run_sweep<kBwdRelu>("bn_relu_bwd_sweep", d, g, dy, v, dx, k, st);
   return run_sweep<kBwd>("bn_bwd_sweep", d, g, dy, v, dx, k, st);
 }
 
@@ -506,15 +552,16 @@ size_t mb_bn_workspace_bytes(const mb_bn_desc* d) {
   return ws_floats(make_geometry(d)) * sizeof(float);
 }
 
-int mb_bn_fwd_train(const float* x, const float* gamma, const float* beta, float* running_mean,
-                    float* running_var, float* y, float* save_mean, float* save_invstd,
-                    const mb_bn_desc* d, void* workspace, size_t workspace_bytes, void* stream) {
-  const char* who = "mb_bn_fwd_train";
+static int fwd_train_impl(const char* who, const float* x, const float* residual, int relu,
+                          const float* gamma, const float* beta, float* running_mean,
+                          float* running_var, float* y, float* save_mean, float* save_invstd,
+                          const mb_bn_desc* d, void* workspace, size_t workspace_bytes,
+                          void* stream) {
   int rc = check(who, d);
   if (rc) return rc;
   if (!x || !gamma || !beta || !y || !save_mean || !save_invstd)
     return fail(MB_ERR_INVALID_ARGUMENT, "%s: null pointer", who);
-  rc = check_alignment(who, d, x, y, y);
+  rc = check_alignment(who, d, x, y, residual ? residual : y);
   if (rc) return rc;
   Geometry g = make_geometry(d);
   if (!workspace || workspace_bytes < ws_floats(g) * sizeof(float))
@@ -530,22 +577,60 @@ int mb_bn_fwd_train(const float* x, const float* gamma, const float* beta, float
                                                     running_var, save_mean, save_invstd);
   rc = after_launch("bn_fwd_finalize");
   if (rc) return rc;
-  SweepConst k{gamma, beta, save_mean, save_invstd, nullptr, nullptr, 0, nullptr};
+  SweepConst k{gamma, beta, save_mean, save_invstd, nullptr, nullptr, 0, nullptr, relu ? 1 : 0};
+  if (residual) return run_sweep<kFwdRes>("bn_act_fwd_sweep", d, g, x, residual, y, k, st);
   return run_sweep<kFwd>("bn_fwd_sweep", d, g, x, nullptr, y, k, st);
 }
 
-int mb_bn_fwd_apply(const float* x, const float* gamma, const float* beta, const float* mean,
-                    const float* invstd, float* y, const mb_bn_desc* d, void* stream) {
-  const char* who = "mb_bn_fwd_apply";
+static int fwd_apply_impl(const char* who, const float* x, const float* residual, int relu,
+                          const float* gamma, const float* beta, const float* mean,
+                          const float* invstd, float* y, const mb_bn_desc* d, void* stream) {
   int rc = check(who, d);
   if (rc) return rc;
   if (!x || !gamma || !beta || !mean || !invstd || !y)
     return fail(MB_ERR_INVALID_ARGUMENT, "%s: null pointer", who);
-  rc = check_alignment(who, d, x, y, y);
+  rc = check_alignment(who, d, x, y, residual ? residual : y);
   if (rc) return rc;
   Geometry g = make_geometry(d);
-  SweepConst k{gamma, beta, mean, invstd, nullptr, nullptr, 0, nullptr};
+  SweepConst k{gamma, beta, mean, invstd, nullptr, nullptr, 0, nullptr, relu ? 1 : 0};
+  if (residual) return run_sweep<kFwdRes>("bn_act_fwd_sweep", d, g, x, residual, y, k, as_stream(stream));
   return run_sweep<kFwd>("bn_fwd_sweep", d, g, x, nullptr, y, k, as_stream(stream));
+}
+
+int mb_bn_fwd_train(const float* x, const float* gamma, const float* beta, float* running_mean,
+                    float* running_var, float* y, float* save_mean, float* save_invstd,
+                    const mb_bn_desc* d, void* workspace, size_t workspace_bytes, void* stream) {
+  return fwd_train_impl("mb_bn_fwd_train", x, nullptr, 0, gamma, beta, running_mean, running_var, y,
+                        save_mean, save_invstd, d, workspace, workspace_bytes, stream);
+}
+
+int mb_bn_fwd_apply(const float* x, const float* gamma, const float* beta, const float* mean,
+                    const float* invstd, float* y, const mb_bn_desc* d, void* stream) {
+  return fwd_apply_impl("mb_bn_fwd_apply", x, nullptr, 0, gamma, beta, mean, invstd, y, d, stream);
+}
+
+int mb_bn_act_fwd_train(const float* x, const float* residual, int relu, const float* gamma,
+                        const float* beta, float* running_mean, float* running_var, float* y,
+                        float* save_mean, float* save_invstd, const mb_bn_desc* d, void* workspace,
+                        size_t workspace_bytes, void* stream) {
+  return fwd_train_impl("mb_bn_act_fwd_train", x, residual, relu, gamma, beta, running_mean,
+                        running_var, y, save_mean, save_invstd, d, workspace, workspace_bytes, stream);
+}
+
+int mb_bn_act_fwd_apply(const float* x, const float* residual, int relu, const float* gamma,
+                        const float* beta, const float* mean, const float* invstd, float* y,
+                        const mb_bn_desc* d, void* stream) {
+  return fwd_apply_impl("mb_bn_act_fwd_apply", x, residual, relu, gamma, beta, mean, invstd, y, d,
+                        stream);
+}
+
+int mb_bn_relu_bwd_from_input(const float* dy, const float* x, const float* gamma,
+                              const float* beta, const float* save_mean, const float* save_invstd,
+                              float* dx, float* dgamma, float* dbeta, const mb_bn_desc* d,
+                              void* workspace, size_t workspace_bytes, void* stream) {
+  if (!beta) return fail(MB_ERR_INVALID_ARGUMENT, "mb_bn_relu_bwd_from_input: null pointer");
+  return bwd_common("mb_bn_relu_bwd_from_input", dy, x, gamma, save_mean, save_invstd, 0,
+                    save_invstd, dx, dgamma, dbeta, d, workspace, workspace_bytes, stream, beta);
 }
 
 int mb_bn_bwd_from_output(const float* dy, const float* y, const float* gamma, const float* beta,

@@ -120,8 +120,11 @@ struct ReluBwdMask {
 
 // ------------------------------------ gated backward: ReLU-from-act, hardtanh
 // dx = (lo < act && act < hi) ? dy : 0;  ReLU uses lo = threshold, hi = +inf.
+// With dy2 != null the gradient is dy + dy2: a tensor read by two consumers gets its two
+// incoming gradients summed and gated in one pass (16 bytes per element instead of 12 + 12).
 struct GateBwd {
   const float* dy;
+  const float* dy2;   // may be null
   const float* act;
   float* dx;
   float lo, hi;
@@ -129,9 +132,17 @@ struct GateBwd {
 #pragma unroll
     for (int k = 0; k < 8; ++k) a.v[k] = (s.v[k] > lo && s.v[k] < hi) ? a.v[k] : 0.f;
   }
+  __device__ __forceinline__ void sum(f8& a, const f8& b) const {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) a.v[k] += b.v[k];
+  }
   __device__ __forceinline__ void vec(size_t g) const {
     f8 a = ld8(dy + g * 8);
     f8 s = ld8(act + g * 8);
+    if (dy2) {
+      f8 b = ld8(dy2 + g * 8);
+      sum(a, b);
+    }
     apply(a, s);
     st8(dx + g * 8, a);
   }
@@ -140,6 +151,12 @@ struct GateBwd {
     f8 s = ld8(act + g0 * 8);
     f8 c = ld8(dy + g1 * 8);
     f8 t = ld8(act + g1 * 8);
+    if (dy2) {
+      f8 b = ld8(dy2 + g0 * 8);
+      f8 d = ld8(dy2 + g1 * 8);
+      sum(a, b);
+      sum(c, d);
+    }
     apply(a, s);
     apply(c, t);
     st8(dx + g0 * 8, a);
@@ -149,6 +166,7 @@ struct GateBwd {
     for (int k = 0; k < count; ++k) {
       float s = act[g * 8 + k];
       float v = dy[g * 8 + k];
+      if (dy2) v += dy2[g * 8 + k];
       dx[g * 8 + k] = (s > lo && s < hi) ? v : 0.f;
     }
   }
@@ -190,6 +208,7 @@ struct AxpyFwd {
   const float* b;  // null: y = alpha * a
   float* y;
   float alpha;
+  int relu;        // y = relu(a + alpha*b)
   __device__ __forceinline__ void vec(size_t g) const {
     f8 u = ld8(a + g * 8);
     if (b) {
@@ -200,6 +219,10 @@ struct AxpyFwd {
 #pragma unroll
       for (int k = 0; k < 8; ++k) u.v[k] *= alpha;
     }
+    if (relu) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) u.v[k] = relu1(u.v[k]);
+    }
     st8(y + g * 8, u);
   }
   __device__ __forceinline__ void vec2(size_t g0, size_t g1) const {
@@ -209,7 +232,8 @@ struct AxpyFwd {
   __device__ __forceinline__ void scalar(size_t g, int count) const {
     for (int k = 0; k < count; ++k) {
       size_t i = g * 8 + k;
-      y[i] = b ? fmaf(alpha, b[i], a[i]) : alpha * a[i];
+      const float v = b ? fmaf(alpha, b[i], a[i]) : alpha * a[i];
+      y[i] = relu ? relu1(v) : v;
     }
   }
 };
@@ -356,7 +380,7 @@ int mb_relu_bwd_act(const float* dy, const float* act, float threshold, float* d
   if (n && (null_arg(dy) || null_arg(dx) || null_arg(act)))
     return fail(MB_ERR_INVALID_ARGUMENT, "mb_relu_bwd_act: null pointer");
   bool v = aligned(dy, 32) && aligned(dx, 32) && aligned(act, 32);
-  return launch_groups("relu_bwd_act", GateBwd{dy, act, dx, threshold, __builtin_huge_valf()}, n,
+  return launch_groups("relu_bwd_act", GateBwd{dy, nullptr, act, dx, threshold, __builtin_huge_valf()}, n,
                        v, stream);
 }
 
@@ -372,20 +396,36 @@ int mb_hardtanh_bwd(const float* dy, const float* act, float lo, float hi, float
   if (n && (null_arg(dy) || null_arg(dx) || null_arg(act)))
     return fail(MB_ERR_INVALID_ARGUMENT, "mb_hardtanh_bwd: null pointer");
   bool v = aligned(dy, 32) && aligned(dx, 32) && aligned(act, 32);
-  return launch_groups("hardtanh_bwd", GateBwd{dy, act, dx, lo, hi}, n, v, stream);
+  return launch_groups("hardtanh_bwd", GateBwd{dy, nullptr, act, dx, lo, hi}, n, v, stream);
 }
 
 int mb_add_fwd(const float* a, const float* b, float alpha, float* y, size_t n, void* stream) {
   if (n && (null_arg(a) || null_arg(b) || null_arg(y)))
     return fail(MB_ERR_INVALID_ARGUMENT, "mb_add_fwd: null pointer");
   bool v = aligned(a, 32) && aligned(b, 32) && aligned(y, 32);
-  return launch_groups("add_fwd", AxpyFwd{a, b, y, alpha}, n, v, stream);
+  return launch_groups("add_fwd", AxpyFwd{a, b, y, alpha, 0}, n, v, stream);
+}
+
+int mb_add_relu_fwd(const float* a, const float* b, float alpha, float* y, size_t n, void* stream) {
+  if (n && (null_arg(a) || null_arg(b) || null_arg(y)))
+    return fail(MB_ERR_INVALID_ARGUMENT, "mb_add_relu_fwd: null pointer");
+  bool v = aligned(a, 32) && aligned(b, 32) && aligned(y, 32);
+  return launch_groups("add_relu_fwd", AxpyFwd{a, b, y, alpha, 1}, n, v, stream);
+}
+
+int mb_relu_bwd_act2(const float* dy1, const float* dy2, const float* act, float threshold,
+                     float* dx, size_t n, void* stream) {
+  if (n && (null_arg(dy1) || null_arg(dy2) || null_arg(dx) || null_arg(act)))
+    return fail(MB_ERR_INVALID_ARGUMENT, "mb_relu_bwd_act2: null pointer");
+  bool v = aligned(dy1, 32) && aligned(dy2, 32) && aligned(dx, 32) && aligned(act, 32);
+  return launch_groups("relu_bwd_act2", GateBwd{dy1, dy2, act, dx, threshold, __builtin_huge_valf()},
+                       n, v, stream);
 }
 
 int mb_scale(const float* x, float alpha, float* y, size_t n, void* stream) {
   if (n && (null_arg(x) || null_arg(y))) return fail(MB_ERR_INVALID_ARGUMENT, "mb_scale: null pointer");
   bool v = aligned(x, 32) && aligned(y, 32);
-  return launch_groups("scale", AxpyFwd{x, nullptr, y, alpha}, n, v, stream);
+  return launch_groups("scale", AxpyFwd{x, nullptr, y, alpha, 0}, n, v, stream);
 }
 
 int mb_pack_bits(const uint8_t* in, uint8_t* out, size_t n, void* stream) {

@@ -106,6 +106,20 @@ def relu_bwd_act(dy: torch.Tensor, act: torch.Tensor, threshold: float = 0.0,
     return dx
 
 
+def relu_bwd_act2(dy1: torch.Tensor, dy2: torch.Tensor, act: torch.Tensor,
+                  threshold: float = 0.0) -> torch.Tensor:
+    """(dy1 + dy2) gated by act > threshold, written over dy1 (or a dense copy of it)."""
+    _need_cuda(dy1, dy2, act); _f32(dy1, "dy1"); _f32(dy2, "dy2"); _f32(act, "act")
+    a = dense(act)
+    d1 = like(a, dy1)
+    d2 = like(a, dy2)
+    if d1.shape != a.shape or d2.shape != a.shape:
+        raise RuntimeError("monet_b200: gradient and activation shapes differ")
+    check(lib().mb_relu_bwd_act2(d1.data_ptr(), d2.data_ptr(), a.data_ptr(), float(threshold),
+                                 d1.data_ptr(), d1.numel(), _stream()), "relu_bwd_act2")
+    return d1
+
+
 # ------------------------------------------------------------------------ packing
 
 def pack_bits(flags: torch.Tensor) -> torch.Tensor:
@@ -179,6 +193,19 @@ def add(a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0, inplace: bool = Fa
     y = ad if (inplace and ad is a) else torch.empty_like(ad)
     check(lib().mb_add_fwd(ad.data_ptr(), bd.data_ptr(), float(alpha), y.data_ptr(), ad.numel(),
                            _stream()), "add_fwd")
+    return y
+
+
+def add_relu(a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0, inplace: bool = False):
+    """relu(a + alpha * b) in one pass."""
+    _need_cuda(a, b); _f32(a, "a"); _f32(b, "b")
+    if a.shape != b.shape:
+        raise RuntimeError("monet_b200.add_relu: broadcasting is not supported")
+    ad = dense(a)
+    bd = like(ad, b)
+    y = ad if (inplace and ad is a) else torch.empty_like(ad)
+    check(lib().mb_add_relu_fwd(ad.data_ptr(), bd.data_ptr(), float(alpha), y.data_ptr(),
+                                ad.numel(), _stream()), "add_relu_fwd")
     return y
 
 
@@ -325,6 +352,69 @@ def bn_bwd_from_output(dy, y, gamma, beta, save_invstd, inplace=False):
 
 def bn_bwd_from_input(dy, x, gamma, save_mean, save_invstd, inplace=False):
     return _bn_bwd("mb_bn_bwd_from_input", dy, x, gamma, save_mean, save_invstd, inplace)
+
+
+def bn_act_fwd_train(x, residual, relu, gamma, beta, running_mean, running_var, momentum, eps,
+                     inplace=False):
+    """(y, save_mean, save_invstd) with y = act(bn(x) + residual); residual may be None."""
+    _need_cuda(x, gamma, beta, running_mean, running_var); _f32(x, "x")
+    xd = _bn_dense(x)
+    d = bn_desc(xd, eps, momentum)
+    rd = None
+    if residual is not None:
+        _need_cuda(residual); _f32(residual, "residual")
+        rd = like(xd, residual) if xd.dim() == 4 else residual.contiguous()
+        if rd.shape != xd.shape:
+            raise RuntimeError("monet_b200 batch norm: residual shape mismatch")
+    y = xd if (inplace and xd is x) else torch.empty_like(xd)
+    save_mean = torch.empty(d.C, dtype=torch.float32, device=x.device)
+    save_invstd = torch.empty(d.C, dtype=torch.float32, device=x.device)
+    ws = _bn_workspace(d, x.device)
+    check(lib().mb_bn_act_fwd_train(
+        xd.data_ptr(), rd.data_ptr() if rd is not None else None, 1 if relu else 0,
+        gamma.data_ptr(), beta.data_ptr(),
+        running_mean.data_ptr() if running_mean is not None else None,
+        running_var.data_ptr() if running_var is not None else None,
+        y.data_ptr(), save_mean.data_ptr(), save_invstd.data_ptr(), C.byref(d),
+        ws.data_ptr(), ws.numel(), _stream()), "bn_act_fwd_train")
+    return y, save_mean, save_invstd
+
+
+def bn_act_fwd_apply(x, residual, relu, gamma, beta, mean, invstd, inplace=False):
+    _need_cuda(x, gamma, beta, mean, invstd); _f32(x, "x")
+    xd = _bn_dense(x)
+    d = bn_desc(xd, 0.0, 0.0)
+    rd = None
+    if residual is not None:
+        _need_cuda(residual); _f32(residual, "residual")
+        rd = like(xd, residual) if xd.dim() == 4 else residual.contiguous()
+        if rd.shape != xd.shape:
+            raise RuntimeError("monet_b200 batch norm: residual shape mismatch")
+    y = xd if (inplace and xd is x) else torch.empty_like(xd)
+    check(lib().mb_bn_act_fwd_apply(
+        xd.data_ptr(), rd.data_ptr() if rd is not None else None, 1 if relu else 0,
+        gamma.data_ptr(), beta.data_ptr(), mean.data_ptr(), invstd.data_ptr(), y.data_ptr(),
+        C.byref(d), _stream()), "bn_act_fwd_apply")
+    return y
+
+
+def bn_relu_bwd_from_input(dy, x, gamma, beta, save_mean, save_invstd, inplace=False):
+    """(dx, dgamma, dbeta) through y = relu(bn(x)), gate re-evaluated from x."""
+    _need_cuda(dy, x, gamma, beta, save_mean, save_invstd); _f32(dy, "dy"); _f32(x, "x")
+    sd = _bn_dense(x)
+    dyd = like(sd, dy) if sd.dim() == 4 else dy.contiguous()
+    if dyd.shape != sd.shape:
+        raise RuntimeError("monet_b200 batch norm backward: gradient shape mismatch")
+    d = bn_desc(sd, 0.0, 0.0)
+    dx = dyd if (inplace and dyd is dy) else torch.empty_like(sd)
+    dgamma = torch.empty(d.C, dtype=torch.float32, device=dy.device)
+    dbeta = torch.empty(d.C, dtype=torch.float32, device=dy.device)
+    ws = _bn_workspace(d, dy.device)
+    check(lib().mb_bn_relu_bwd_from_input(
+        dyd.data_ptr(), sd.data_ptr(), gamma.data_ptr(), beta.data_ptr(), save_mean.data_ptr(),
+        save_invstd.data_ptr(), dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), C.byref(d),
+        ws.data_ptr(), ws.numel(), _stream()), "bn_relu_bwd_from_input")
+    return dx, dgamma, dbeta
 
 
 # ------------------------------------------------------------------------ softmax

@@ -18,6 +18,9 @@ then executes forward and backward through the operators' own protocol:
 
 Two ready-made policies: ``store_all`` (what stock PyTorch keeps) and ``low_memory``
 (in-place output-activated batch norm, ReLU recomputed from its input, 4-bit pooling indices).
+
+``fuse_graph`` optionally rewrites batch_norm -> relu, batch_norm -> add -> relu and
+add -> relu chains into the fused nodes of ``lm_ops/fused.py`` before execution.
 """
 from __future__ import annotations
 
@@ -143,6 +146,79 @@ def extract_graph(model: nn.Module) -> Tuple[List[Node], int]:
     return nodes, out_id
 
 
+def fuse_graph(nodes: List[Node], out_id: int) -> Tuple[List[Node], int]:
+    """Rewrites the element-wise tails of batch norm into fused nodes:
+
+    * ``batch_norm -> relu``                 => ``monet::batch_norm_relu`` (at the batch norm);
+    * ``batch_norm -> add(., r) -> relu``    => ``monet::batch_norm_add_relu`` with ``r`` appended
+      to the batch-norm arguments, placed where the add was (``r`` may be produced after the
+      batch norm, e.g. by a downsample branch);
+    * ``add -> relu`` (any other add)        => ``monet::add_relu``.
+
+    A link is fused only when the intermediate value has no other reader, the batch norm is
+    in training mode and the add has alpha == 1 and two distinct node operands."""
+    by_id = {n.id: n for n in nodes}
+    removed = set()
+    alias: Dict[int, int] = {}
+    relus = ('aten::relu', 'aten::relu_')
+    adds = ('aten::add', 'aten::add_')
+
+    def sole_user(n: Node) -> Optional[Node]:
+        return by_id[n.users[0]] if len(n.users) == 1 and n.id != out_id else None
+
+    def plain_add(u: Node) -> bool:
+        return (u.op in adds and u.args[2].value == 1 and u.args[0].kind == 'node'
+                and u.args[1].kind == 'node' and u.args[0].value != u.args[1].value)
+
+    for n in nodes:
+        if n.id in removed or n.op != 'aten::batch_norm' or not n.args[5].value:
+            continue
+        u = sole_user(n)
+        if u is None:
+            continue
+        if u.op in relus:
+            n.op = 'monet::batch_norm_relu'
+            removed.add(u.id)
+            alias[u.id] = n.id
+        elif plain_add(u):
+            r = sole_user(u)
+            if r is None or r.op not in relus:
+                continue
+            other = u.args[1] if u.args[0].value == n.id else u.args[0]
+            u.op = 'monet::batch_norm_add_relu'
+            u.args = list(n.args) + [other]
+            u.module = n.module
+            removed.add(n.id)
+            removed.add(r.id)
+            alias[r.id] = u.id
+    for n in nodes:
+        if n.id in removed or not plain_add(n):
+            continue
+        r = sole_user(n)
+        if r is not None and r.op in relus:
+            n.op = 'monet::add_relu'
+            removed.add(r.id)
+            alias[r.id] = n.id
+
+    kept = [n for n in nodes if n.id not in removed]
+    renumber = {n.id: i for i, n in enumerate(kept)}
+
+    def target(i: int) -> int:
+        while i in alias:
+            i = alias[i]
+        return renumber[i]
+
+    out: List[Node] = []
+    for n in kept:
+        args = [Arg('node', target(a.value)) if a.kind == 'node' else a for a in n.args]
+        out.append(Node(renumber[n.id], n.op, args, n.module))
+    for n in out:
+        for a in n.args:
+            if a.kind == 'node':
+                out[a.value].users.append(n.id)
+    return out, target(out_id)
+
+
 # ---------------------------------------------------------------------------- policy
 @dataclass
 class Choice:
@@ -177,6 +253,8 @@ def low_memory(nodes: List[Node], n: Node) -> Choice:
         return Choice(impl=0, inplace=False, recompute=True)
     if n.op == 'aten::max_pool2d':
         return Choice(impl=1)
+    if n.op == 'monet::batch_norm_relu':
+        return Choice(recompute=True)      # keeps x only; y = relu(bn(x)) is rebuilt from it
     return Choice()
 
 
@@ -198,9 +276,13 @@ class Runner:
     """Executes forward and backward of an extracted graph through ``lm_ops``."""
 
     def __init__(self, model: nn.Module, policy: Policy = store_all,
-                 mode: str = "conv_multiway_newnode", input_requires_grad: bool = False):
+                 mode: str = "conv_multiway_newnode", input_requires_grad: bool = False,
+                 fuse: bool = False):
         self.model = model
         self.nodes, self.out_id = extract_graph(model)
+        if fuse:
+            from .lm_ops import fused  # noqa: F401  (registers the monet:: nodes)
+            self.nodes, self.out_id = fuse_graph(self.nodes, self.out_id)
         self.mode = mode
         self.input_requires_grad = input_requires_grad
         self.choices = [policy(self.nodes, n) for n in self.nodes]
@@ -349,15 +431,36 @@ class Runner:
     def backward(self, grad_output: torch.Tensor) -> None:
         """Backpropagates `grad_output` from the output node; parameter gradients are left in
         ``self.param_grads`` (and accumulated into ``param.grad``)."""
-        grads: Dict[int, torch.Tensor] = {self.out_id: grad_output}
+        # node id -> gradients received so far.  They are summed as they arrive, except that an
+        # operator with ``accepts_grad_pair`` is handed two of them unsummed (it folds the sum
+        # into its own pass).
+        grads: Dict[int, List[torch.Tensor]] = {self.out_id: [grad_output]}
         self.param_grads = {}
+
+        def pending():
+            for lst in grads.values():
+                for o in lst:
+                    yield o
+
+        def private(g, own_entries=0):
+            """A gradient that may be overwritten: cloned when a pending gradient other than its
+            own `own_entries` entries lives in the same buffer."""
+            same = sum(1 for o in pending()
+                       if o.data_ptr() == g.data_ptr() and o.numel() == g.numel())
+            return g.clone() if same > own_entries else g
+
         with torch.no_grad():
             for n in reversed(self.nodes):
-                g = grads.pop(n.id, None)
-                if g is None:
+                gl = grads.pop(n.id, None)
+                if gl is None:
                     self._release(n.id)
                     continue
                 op = self._ops[n.id]
+                if len(gl) == 2:
+                    g = (private(gl[0]), gl[1])      # the second one is only read
+                else:
+                    g = private(gl[0])
+                del gl
                 stored: list = []
                 for d in _descriptors(op):
                     if isinstance(d, InputStorage):
@@ -378,10 +481,6 @@ class Runner:
                 if n.op in ('aten::_convolution', 'aten::addmm'):
                     variant = max(self.choices[n.id].algorithm, 0)
                     op.algorithm = 20 + variant          # weight and input gradients in one call
-                if any(o is g or (o.data_ptr() == g.data_ptr() and o.numel() == g.numel())
-                       for o in grads.values()):
-                    g = g.clone()     # another pending gradient shares this buffer; operators may
-                                      # work in place on the gradient they are given
                 if n.op == 'aten::cat':
                     outs = op.backward(g)
                 else:
@@ -397,10 +496,13 @@ class Runner:
                     if gi is None:
                         continue
                     if a.kind == 'node':
-                        if a.value in grads:
-                            grads[a.value] = F.add(grads[a.value], gi, 1.0, inplace=True)
+                        have = grads.get(a.value)
+                        if have is None:
+                            grads[a.value] = [gi]
+                        elif len(have) == 1 and getattr(self._ops[a.value], 'accepts_grad_pair', False):
+                            have.append(gi)
                         else:
-                            grads[a.value] = gi
+                            have[0] = F.add(private(have[0], own_entries=1), gi, 1.0, inplace=True)
                     elif a.kind == 'param':
                         p = self._tensors[a.value]
                         if not p.requires_grad:
@@ -413,8 +515,18 @@ class Runner:
         for name, gi in self.param_grads.items():
             p = self._tensors[name]
             gi = gi.reshape(p.shape) if gi.shape != p.shape else gi
+            if p.dim() != 4:
+                gi = gi.contiguous()
+            if gi.stride() != p.stride():
+                # same strides as the parameter, so that foreach optimisers keep their fused
+                # path: a 1x1 filter is the same memory either way, anything else is copied
+                if p.dim() == 4 and p.shape[2] == 1 and p.shape[3] == 1 and gi.is_contiguous(
+                        memory_format=torch.channels_last) and p.is_contiguous(memory_format=torch.channels_last):
+                    gi = gi.as_strided(p.shape, p.stride())
+                else:
+                    gi = torch.empty_like(p).copy_(gi)
             if p.grad is None:
-                p.grad = gi.contiguous() if p.dim() != 4 else gi
+                p.grad = gi
             else:
                 p.grad.add_(gi)
         self._vals = {}

@@ -202,6 +202,33 @@ def bn_backward_from_output(dy, y, gamma, beta, save_invstd):
     return dx.float(), (S2 / g).float(), S1.float()
 
 
+# ------------------------------------------ fused batch norm / add / ReLU forms
+# The reference has these only as chains of separate operators; the oracle is that chain.
+
+def bn_act_forward_train(x, residual, relu, gamma, beta, running_mean, running_var,
+                         momentum=0.1, eps=1e-5):
+    """bn.py forward, then funcs.py add of `residual` (may be None), then relu.py forward."""
+    y, mean, invstd, rm, rv = bn_forward_train(x, gamma, beta, running_mean, running_var,
+                                               momentum, eps)
+    if residual is not None:
+        y = y + residual.detach().cpu()
+    if relu:
+        y = relu_forward(y)
+    return y, mean, invstd, rm, rv
+
+
+def bn_relu_backward_from_input(dy, gate, x, gamma, eps=1e-5):
+    """relu.py backward with the given boolean gate (y > 0 of the forward), then batch-norm
+    backward from the input."""
+    dy = dy.detach().cpu() * gate.detach().cpu().to(dy.dtype)
+    return bn_backward_from_input(dy, x, gamma, eps)
+
+
+def relu_backward_sum2(dy1, dy2, saved):
+    """Two incoming gradients summed (schedule.py:296-301), then relu.py backward."""
+    return relu_backward(dy1.detach().cpu() + dy2.detach().cpu(), saved)
+
+
 # ------------------------------------------------------------------ softmax / CE
 
 def softmax_forward(x, dim, log=False):

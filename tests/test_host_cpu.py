@@ -80,6 +80,51 @@ def test_graph_extraction_and_policies():
         runner.Runner(model, lambda ns, n: runner.Choice(inplace=(n.op == "aten::_convolution")))
 
 
+def test_graph_fusion_rewrite():
+    """batch_norm -> relu and batch_norm -> add -> relu chains become fused nodes; the rewritten
+    graph stays in dependency order and its users lists are consistent."""
+    import torchvision
+    from monet_b200 import runner
+    for make, n_add in ((torchvision.models.resnet50, 16), (torchvision.models.resnet18, 8)):
+        nodes, out = runner.extract_graph(make())
+        n_relu = sum(n.op.startswith("aten::relu") for n in nodes)
+        fused, fout = runner.fuse_graph(nodes, out)
+        ops = [n.op for n in fused]
+        assert ops.count("monet::batch_norm_add_relu") == n_add
+        assert ops.count("monet::batch_norm_relu") == n_relu - n_add
+        assert not any(o in ("aten::relu", "aten::relu_", "aten::add", "aten::add_") for o in ops)
+        assert fused[fout].op == "aten::addmm"
+        users = {n.id: [] for n in fused}
+        for i, n in enumerate(fused):
+            assert n.id == i
+            for a in n.args:
+                if a.kind == "node":
+                    assert a.value < n.id          # producers come first
+                    users[a.value].append(n.id)
+        assert all(sorted(users[n.id]) == sorted(n.users) for n in fused)
+        far = [n for n in fused if n.op == "monet::batch_norm_add_relu"]
+        assert all(len(n.args) == 10 and n.args[9].kind == "node" for n in far)
+    # a batch norm whose output has a second reader is left alone
+    import torch.nn as nn
+
+    class TwoReaders(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.c = nn.Conv2d(4, 4, 1)
+            self.b = nn.BatchNorm2d(4)
+            self.r = nn.ReLU()
+
+        def forward(self, x):
+            z = self.b(self.c(x))
+            return self.r(z) + z
+
+    nodes, out = runner.extract_graph(TwoReaders())
+    fused, _ = runner.fuse_graph(nodes, out)
+    assert [n.op for n in fused] == [n.op for n in runner.extract_graph(TwoReaders())[0]]
+    r = runner.Runner(torchvision.models.resnet18(), runner.low_memory, fuse=True)
+    assert all(r.choices[n.id].recompute for n in r.nodes if n.op == "monet::batch_norm_relu")
+
+
 def test_oracle_maxpool_forms_agree():
     g = torch.Generator().manual_seed(0)
     x = torch.randn(2, 3, 9, 10, generator=g)
