@@ -389,15 +389,43 @@ def run_ours(args):
     dom_calls = len(fam_events[dominant]) / args.steps
 
     # ---- timed region 2: end to end from pinned host memory, loss read back every step
+    # Inputs are double-buffered: the batch of step i+1 crosses PCIe on a copy stream while
+    # step i computes; every step's batch is copied inside the timed region.
+    copy_stream = torch.cuda.Stream()
+    xb = [x_dev, torch.empty_like(x_dev)]
+    yb = [y_dev, torch.empty_like(y_dev)]
+    ready = [torch.cuda.Event(), torch.cuda.Event()]
+    free = [torch.cuda.Event(), torch.cuda.Event()]
+
+    def upload(i):
+        k = i % 2
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(free[k])          # the step that last read this buffer is done
+            xb[k].copy_(x_host, non_blocking=True)
+            yb[k].copy_(y_host, non_blocking=True)
+            ready[k].record(copy_stream)
+
+    def e2e_steps(n):
+        last = 0.0
+        for k in range(2):
+            free[k].record(stream)
+        upload(0)
+        for i in range(n):
+            k = i % 2
+            stream.wait_event(ready[k])
+            loss_t = step(xb[k], yb[k])
+            free[k].record(stream)
+            if i + 1 < n:
+                upload(i + 1)
+            last = float(loss_t)                     # device -> host read of the loss
+        return last
+
+    e2e_steps(2)                                     # untimed: first use of the copy stream
     barrier()
     w0 = time.perf_counter()
     e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
     e0.record()
-    last = 0.0
-    for _ in range(args.steps):
-        x_dev.copy_(x_host, non_blocking=True)
-        y_dev.copy_(y_host, non_blocking=True)
-        last = float(step(x_dev, y_dev))             # device -> host read of the loss
+    last = e2e_steps(args.steps)
     e1.record()
     barrier()
     ms_e2e = max(e0.elapsed_time(e1), (time.perf_counter() - w0) * 1e3) / args.steps
