@@ -73,6 +73,21 @@ int encode_act(const char* who, CUtensorMap* m, const float* base, int C, long l
   return encode_map(who, m, base, 4, dims, strides, box, swizzle);
 }
 
+// The same view with the channels split into chunks of 32: {32, Wv, Hv, Nv, C/32}, box
+// {32, bw, bh, bn, chunks}.  One copy lands `chunks` boxes of bw*bh*bn rows back to back in
+// shared memory, which is the operand layout of the backward-filter kernel.  C % 32 == 0.
+int encode_act_chunked(const char* who, CUtensorMap* m, const float* base, int C, long long Wv,
+                       long long Hv, long long Nv, long long sw_b, long long sh_b, long long sn_b,
+                       int bw, int bh, int bn, int chunks, CUtensorMapSwizzle swizzle) {
+  cuuint64_t dims[5] = {(cuuint64_t)kChunkK, (cuuint64_t)Wv, (cuuint64_t)Hv, (cuuint64_t)Nv,
+                        (cuuint64_t)(C / kChunkK)};
+  cuuint64_t strides[4] = {(cuuint64_t)sw_b, (cuuint64_t)sh_b, (cuuint64_t)sn_b,
+                           (cuuint64_t)kChunkK * 4};
+  cuuint32_t box[5] = {(cuuint32_t)kChunkK, (cuuint32_t)bw, (cuuint32_t)bh, (cuuint32_t)bn,
+                       (cuuint32_t)chunks};
+  return encode_map(who, m, base, 5, dims, strides, box, swizzle);
+}
+
 // Filter view {Cin, taps, Kout} of a [Kout][taps][Cin] array; box {32, 1, rows}.
 int encode_filter(const char* who, CUtensorMap* m, const float* base, int Cin, int taps, int Kout,
                   int rows) {
@@ -373,6 +388,7 @@ int wgrad_launch(const char* who, wg::Plan& pl, const CUtensorMap& mdy, const CU
   if (rc) return rc;
   static const int attr_rc = raise_smem_limit(who, conv_wgrad_tcgen05);
   if (attr_rc) return attr_rc;
+  p.prof = g_conv_prof;
   conv_wgrad_tcgen05<<<pl.grid, 192, pl.smem, st>>>(mdy, mx[0], mx[1], mx[2], mx[3], p);
   rc = after_launch("conv_wgrad_tcgen05");
   if (rc) return rc;
@@ -434,16 +450,22 @@ int wgrad_run(const char* who, const float* x, const float* dy, float* dw, float
   int rc;
   CUtensorMap mdy, mx[4];
   const long long K4 = static_cast<long long>(d->K) * 4, C4 = static_cast<long long>(d->C) * 4;
+  auto act = [&](CUtensorMap* m, const float* base, int Cn, long long Wv, long long Hv, long long Nv,
+                 long long sw_b, long long sh_b, long long sn_b, int chunks) {
+    if (p.chunked)
+      return encode_act_chunked(who, m, base, Cn, Wv, Hv, Nv, sw_b, sh_b, sn_b, p.bw, p.bh, p.bn,
+                                chunks, kWg);
+    return encode_act(who, m, base, Cn, Wv, Hv, Nv, sw_b, sh_b, sn_b, p.bw, p.bh, p.bn, kWg);
+  };
   if (pl.flat) {
     const long long pixels = static_cast<long long>(d->N) * d->P * d->Q;
-    rc = encode_act(who, &mdy, dy, d->K, pixels, 1, 1, K4, K4 * pixels, K4 * pixels, p.bw, 1, 1, kWg);
+    rc = act(&mdy, dy, d->K, pixels, 1, 1, K4, K4 * pixels, K4 * pixels, p.KA);
     if (rc) return rc;
-    rc = encode_act(who, &mx[0], x, d->C, pixels, 1, 1, C4, C4 * pixels, C4 * pixels, p.bw, 1, 1, kWg);
+    rc = act(&mx[0], x, d->C, pixels, 1, 1, C4, C4 * pixels, C4 * pixels, p.U);
     if (rc) return rc;
     mx[1] = mx[2] = mx[3] = mx[0];
   } else {
-    rc = encode_act(who, &mdy, dy, d->K, d->Q, d->P, d->N, K4, K4 * d->Q, K4 * d->Q * d->P, p.bw,
-                    p.bh, p.bn, kWg);
+    rc = act(&mdy, dy, d->K, d->Q, d->P, d->N, K4, K4 * d->Q, K4 * d->Q * d->P, p.KA);
     if (rc) return rc;
     int first = -1;
     for (int mi = 0; mi < d->stride_h * d->stride_w; ++mi) {
@@ -451,9 +473,8 @@ int wgrad_run(const char* who, const float* x, const float* dy, float* dw, float
       const int a = mi / d->stride_w, b = mi % d->stride_w;
       const long long Wv = (d->W - b + d->stride_w - 1) / d->stride_w;
       const long long Hv = (d->H - a + d->stride_h - 1) / d->stride_h;
-      rc = encode_act(who, &mx[mi], x + (static_cast<long long>(a) * d->W + b) * d->C, d->C, Wv, Hv,
-                      d->N, C4 * d->stride_w, C4 * d->W * d->stride_h, C4 * d->W * d->H, p.bw, p.bh,
-                      p.bn, kWg);
+      rc = act(&mx[mi], x + (static_cast<long long>(a) * d->W + b) * d->C, d->C, Wv, Hv, d->N,
+               C4 * d->stride_w, C4 * d->W * d->stride_h, C4 * d->W * d->H, p.U);
       if (rc) return rc;
       if (first < 0) first = mi;
     }

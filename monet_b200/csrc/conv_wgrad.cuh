@@ -46,6 +46,9 @@ struct WgradParams {
   int pix_tiles;            // total pixel tiles
   int stages;
   int use_atomics;
+  int chunked;              // 1: the maps are 5-d {32, w, h, n, chunk}: one copy brings all the
+                            //    32-channel boxes of an operand; units are ordered tap-major
+  long long* prof;          // optional: cycle counters written by CTA 0 (diagnostics), or null
   Taps taps;
 };
 
@@ -87,7 +90,8 @@ conv_wgrad_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_const
   const uint32_t box_bytes = static_cast<uint32_t>(p.rows) * 128u;
   const uint32_t a_bytes = static_cast<uint32_t>(p.KA) * box_bytes;     // fixed slot layout
   const uint32_t stage_bytes = a_bytes + static_cast<uint32_t>(p.U) * box_bytes;
-  const uint32_t tx_bytes = static_cast<uint32_t>(ka + nu) * box_bytes;
+  // a 5-d copy always delivers its whole box (chunks past the tensor arrive as zeros)
+  const uint32_t tx_bytes = static_cast<uint32_t>(p.chunked ? p.KA + p.U : ka + nu) * box_bytes;
   const uint32_t tmem_cols = 256u * (p.KA / 4) * NH;                     // 256 or 512
 
   if (threadIdx.x == 0) {
@@ -107,41 +111,88 @@ conv_wgrad_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const bool prof = p.prof != nullptr && blockIdx.x == 0;
 
   if (warp == 4) {
-    if (lane == 0 && n_iter > 0) {
-      prefetch_tensormap(&mapDy);
-      prefetch_tensormap(&mapX0);
+    // ------------------------------------------------------------ TMA producer
+    // One lane per box: lane j < ka loads dy box j, lane ka + u loads x box u, so the ka + nu
+    // (up to 20) copies of a stage are issued by one warp instruction instead of one after
+    // the other by a single thread.  Lane 0 owns the barriers.
+    if (n_iter > 0) {
+      if (lane == 0) {
+        prefetch_tensormap(&mapDy);
+        prefetch_tensormap(&mapX0);
+      }
+      bool is_a = lane < ka;
+      bool is_b = lane >= ka && lane < ka + nu;
+      const CUtensorMap* my_map = &mapDy;
+      int my_c = k0 + 32 * lane, my_dw = 0, my_dh = 0;
+      uint32_t my_off = static_cast<uint32_t>(lane) * box_bytes;
+      if (p.chunked) {
+        // lane 0: every dy box of the stage; lane 1: every x box (one tap, U consecutive chunks)
+        is_a = lane == 0;
+        is_b = lane == 1;
+        my_c = k0 / 32;
+        my_off = 0;
+        if (is_b) {
+          const int ti = u0 / p.cchunks;
+          const int mi = p.taps.map[ti];
+          my_map = mi == 0 ? &mapX0 : mi == 1 ? &mapX1 : mi == 2 ? &mapX2 : &mapX3;
+          my_c = u0 - ti * p.cchunks;
+          my_dw = p.taps.dw[ti];
+          my_dh = p.taps.dh[ti];
+          my_off = a_bytes;
+        }
+      } else if (is_b) {
+        const int u = lane - ka;
+        const int unit = u0 + u;
+        const int cc = unit / p.ntaps, ti = unit - cc * p.ntaps;
+        const int mi = p.taps.map[ti];
+        my_map = mi == 0 ? &mapX0 : mi == 1 ? &mapX1 : mi == 2 ? &mapX2 : &mapX3;
+        my_c = cc * 32;
+        my_dw = p.taps.dw[ti];
+        my_dh = p.taps.dh[ti];
+        my_off = a_bytes + static_cast<uint32_t>(u) * box_bytes;
+      }
       detail::Ring ring{0, 0u, p.stages};
       uint32_t armed[16];
       for (int s = 0; s < 16; ++s) armed[s] = 0;
       bool ok = true;
-      for (int t = t_begin; ok && t < t_end; ++t) {
-        const int wt = t % p.tiles_w;
-        int r = t / p.tiles_w;
-        const int ht = r % p.tiles_h;
-        const int nt = r / p.tiles_h;
+      long long w_empty = 0, w_issue = 0;
+      int wt = t_begin % p.tiles_w;
+      int rr = t_begin / p.tiles_w;
+      int ht = rr % p.tiles_h;
+      int nt = rr / p.tiles_h;
+      for (int t = t_begin; t < t_end; ++t) {
         const int q0 = wt * p.bw, p0 = ht * p.bh, n0 = nt * p.bn;
-        if (!mbar_wait(&empty[ring.stage], ring.phase ^ 1u, abort_flag)) {
-          ok = false;
-          break;
+        const long long tw0 = prof ? clock64() : 0;
+        if (lane == 0) {
+          ok = mbar_wait(&empty[ring.stage], ring.phase ^ 1u, abort_flag);
+          if (ok) {
+            mbar_arrive_expect_tx(&full[ring.stage], tx_bytes);
+            armed[ring.stage] = 1u + ring.phase;
+          }
         }
-        uint8_t* slot = slots_ptr + static_cast<size_t>(ring.stage) * stage_bytes;
-        mbar_arrive_expect_tx(&full[ring.stage], tx_bytes);
-        armed[ring.stage] = 1u + ring.phase;
-        for (int j = 0; j < ka; ++j)
-          tma_load_4d(&mapDy, slot + j * box_bytes, &full[ring.stage], k0 + 32 * j, q0, p0, n0);
-        for (int u = 0; u < nu; ++u) {
-          const int unit = u0 + u;
-          const int cc = unit / p.ntaps, ti = unit - cc * p.ntaps;
-          const int mi = p.taps.map[ti];
-          const CUtensorMap* mx = mi == 0 ? &mapX0 : mi == 1 ? &mapX1 : mi == 2 ? &mapX2 : &mapX3;
-          tma_load_4d(mx, slot + a_bytes + u * box_bytes, &full[ring.stage], cc * 32,
-                      q0 + p.taps.dw[ti], p0 + p.taps.dh[ti], n0);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
+        const long long tw1 = prof ? clock64() : 0;
+        w_empty += tw1 - tw0;
+        if (is_a || is_b) {
+          uint8_t* slot = slots_ptr + static_cast<size_t>(ring.stage) * stage_bytes;
+          if (p.chunked)
+            tma_load_5d(my_map, slot + my_off, &full[ring.stage], 0, q0 + my_dw, p0 + my_dh, n0, my_c);
+          else
+            tma_load_4d(my_map, slot + my_off, &full[ring.stage], my_c, q0 + my_dw, p0 + my_dh, n0);
         }
         ring.advance();
+        if (++wt == p.tiles_w) {
+          wt = 0;
+          if (++ht == p.tiles_h) { ht = 0; ++nt; }
+        }
+        if (prof) w_issue += clock64() - tw1;
       }
-      if (!ok) {
+      if (prof && lane == 0) { p.prof[1] = w_empty; p.prof[2] = w_issue; }
+      if (!ok && lane == 0) {
         *abort_flag = 1;
         atomicCAS(&g_conv_status, 0, 11);
         for (int s = 0; s < p.stages; ++s) {
@@ -157,11 +208,16 @@ conv_wgrad_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_const
       detail::Ring ring{0, 0u, p.stages};
       bool ok = true;
       const int ksteps = p.rows / 8;
+      long long w_full = 0, w_mma = 0;
+      const long long tk0 = prof ? clock64() : 0;
       for (int it = 0; it < n_iter; ++it) {
+        const long long tf0 = prof ? clock64() : 0;
         if (!mbar_wait(&full[ring.stage], ring.phase, abort_flag)) {
           ok = false;
           break;
         }
+        const long long tf1 = prof ? clock64() : 0;
+        w_full += tf1 - tf0;
         tc_fence_after();
         const uint32_t a_addr = slots0 + static_cast<uint32_t>(ring.stage) * stage_bytes;
         for (int mh = 0; mh < mh_n; ++mh) {
@@ -179,7 +235,9 @@ conv_wgrad_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_const
         }
         mma_commit(&empty[ring.stage]);
         ring.advance();
+        if (prof) w_mma += clock64() - tf1;
       }
+      if (prof) { p.prof[0] = clock64() - tk0; p.prof[3] = w_full; p.prof[4] = w_mma; p.prof[5] = n_iter; }
       if (ok) {
         mma_commit(&acc_full[0]);
       } else {
@@ -189,8 +247,10 @@ conv_wgrad_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_const
     }
   } else if (n_iter > 0 || !p.use_atomics) {
     // epilogue: thread = output channel row, 32 input channels per unit
+    const long long te0 = prof ? clock64() : 0;
     bool got = n_iter > 0 ? mbar_wait(&acc_full[0], 0, abort_flag) : true;
     got = __all_sync(0xffffffffu, got);
+    const long long te1 = prof ? clock64() : 0;
     if (got) {
       tc_fence_after();
       float* base = p.out + static_cast<long long>(split) * p.split_stride;
@@ -198,7 +258,14 @@ conv_wgrad_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_const
         const int k = k0 + mh * 128 + warp * 32 + lane;
         for (int u = 0; u < nu; ++u) {
           const int unit = u0 + u;
-          const int cc = unit / p.ntaps, ti = unit - cc * p.ntaps;
+          int cc, ti;
+          if (p.chunked) {
+            ti = unit / p.cchunks;
+            cc = unit - ti * p.cchunks;
+          } else {
+            cc = unit / p.ntaps;
+            ti = unit - cc * p.ntaps;
+          }
           float v[32];
           if (n_iter > 0) {
             tmem_ld32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) +
@@ -231,6 +298,7 @@ conv_wgrad_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_const
       *abort_flag = 1;
       atomicCAS(&g_conv_status, 0, 13);
     }
+    if (prof && threadIdx.x == 0) { p.prof[6] = te1 - te0; p.prof[7] = clock64() - te1; }
   }
 
   tc_fence_before();
@@ -270,6 +338,12 @@ __global__ void __launch_bounds__(256) bias_grad_kernel(const float* __restrict_
     for (int j = 1; j < 8; ++j) s += red[j][tx];
     atomicAdd(db + k, s);
   }
+}
+
+// experiment knob: integer from the environment, `dflt` when unset
+inline int tune_int(const char* name, int dflt) {
+  const char* v = getenv(name);
+  return v ? atoi(v) : dflt;
 }
 
 namespace wg {
@@ -335,10 +409,25 @@ inline bool make_plan(const mb_conv_desc* d, int variant, Plan* pl, bool smallc 
   p.groups = (p.units + u_max - 1) / u_max;
   p.U = (p.units + p.groups - 1) / p.groups;
   p.groups = (p.units + p.U - 1) / p.U;
+  // chunked form: whole 32-channel chunks on both operands, and every group of units is one
+  // tap with U consecutive chunks (units ordered tap-major), so that one 5-d copy per operand
+  // fills a stage
+  p.chunked = 0;
+  if (!smallc && d->C % 32 == 0 && d->K % 32 == 0 && tune_int("MB_WG_CHUNKED", 1)) {
+    int U = p.cchunks < u_max ? p.cchunks : u_max;
+    while (p.cchunks % U) --U;
+    if (U >= 2 || p.cchunks == 1) {
+      p.chunked = 1;
+      p.U = U;
+      p.groups = p.units / U;
+    }
+  }
   p.k_tiles = (d->K + 32 * p.KA - 1) / (32 * p.KA);
-  // pixel box: rows multiple of 8, slot = (KA + U) * rows * 128 bytes, at least 2 slots
+  // pixel box: rows multiple of 8, slot = (KA + U) * rows * 128 bytes; two slots of large
+  // boxes when every box is a copy of its own (the copy engine takes ~70 cycles per copy,
+  // whatever its size), three slots when one copy per operand fills a slot
   const int boxes = p.KA + p.U;
-  int max_rows = static_cast<int>((212 * 1024 / 2) / (boxes * 128)) / 8 * 8;
+  int max_rows = static_cast<int>((212 * 1024 / tune_int("MB_WG_SLOTS", p.chunked ? 3 : 2)) / (boxes * 128)) / 8 * 8;
   if (max_rows > 128) max_rows = 128;
   if (max_rows < 8) return false;
   if (flat) {

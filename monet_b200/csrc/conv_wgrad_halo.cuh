@@ -121,29 +121,38 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 4) {
-    if (lane == 0 && n_iter > 0) {
-      prefetch_tensormap(&mapDy);
-      prefetch_tensormap(&mapX);
+    // TMA producer: lanes 0..ka-1 copy the dy boxes, lane ka the x box, in one warp instruction;
+    // lane 0 owns the barriers
+    if (n_iter > 0) {
+      if (lane == 0) {
+        prefetch_tensormap(&mapDy);
+        prefetch_tensormap(&mapX);
+      }
       detail::Ring ring{0, 0u, p.stages};
       uint32_t armed[16];
       for (int s = 0; s < 16; ++s) armed[s] = 0;
       bool ok = true;
-      for (int t = t_begin; ok && t < t_end; ++t) {
-        const int ht = t % p.tiles_h, n0 = t / p.tiles_h;
+      int ht = t_begin % p.tiles_h, n0 = t_begin / p.tiles_h;
+      for (int t = t_begin; t < t_end; ++t) {
         const int p0 = ht * p.bh;
-        if (!mbar_wait(&empty[ring.stage], ring.phase ^ 1u, abort_flag)) {
-          ok = false;
-          break;
+        if (lane == 0) {
+          ok = mbar_wait(&empty[ring.stage], ring.phase ^ 1u, abort_flag);
+          if (ok) {
+            mbar_arrive_expect_tx(&full[ring.stage], tx_bytes);
+            armed[ring.stage] = 1u + ring.phase;
+          }
         }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
         uint8_t* slot = slots_ptr + static_cast<size_t>(ring.stage) * stage_bytes;
-        mbar_arrive_expect_tx(&full[ring.stage], tx_bytes);
-        armed[ring.stage] = 1u + ring.phase;
-        for (int j = 0; j < ka; ++j)
-          tma_load_4d(&mapDy, slot + j * a_box, &full[ring.stage], k0 + 32 * j, 0, p0, n0);
-        tma_load_4d(&mapX, slot + a_bytes, &full[ring.stage], cc * 32, p.org_w, p0 + p.org_h, n0);
+        if (lane < ka)
+          tma_load_4d(&mapDy, slot + lane * a_box, &full[ring.stage], k0 + 32 * lane, 0, p0, n0);
+        else if (lane == ka)
+          tma_load_4d(&mapX, slot + a_bytes, &full[ring.stage], cc * 32, p.org_w, p0 + p.org_h, n0);
         ring.advance();
+        if (++ht == p.tiles_h) { ht = 0; ++n0; }
       }
-      if (!ok) {
+      if (!ok && lane == 0) {
         *abort_flag = 1;
         atomicCAS(&g_conv_status, 0, 21);
         for (int s = 0; s < p.stages; ++s) {
@@ -300,7 +309,7 @@ inline bool plan_launch(int K, int C, int T, int N, int P, int Q, const Tap* tap
     sizes(bh, &ra, &raa, &rb, &rba);
     if (bh + halo_h > 256) continue;
     const size_t stage = static_cast<size_t>(4 * raa + rba) * 128;
-    if (stage <= 72 * 1024) { best_bh = bh; break; }
+    if (stage <= static_cast<size_t>(tune_int("MB_WGH_STAGE_KB", 108)) * 1024) { best_bh = bh; break; }
   }
   if (!best_bh) {
     int ra, raa, rb, rba;
@@ -343,11 +352,16 @@ struct Launches {
   int phase_a[4], phase_b[4];
 };
 
-// Stride 1 always; stride 2 only for large maps: a strided filter needs one launch per phase
-// and about twice the MMAs per pixel, which on small maps costs more than the per-tap boxes
-// of conv_wgrad.cuh (measured: 56->28 wins 2x, 28->14 and 14->7 lose 20 %).
+// The halo kernel saves shared-memory fill (x is fetched once instead of once per tap) but
+// its MMAs are only 32 * S columns wide, which is below the tensor pipe's floor of ~76 cycles
+// per instruction.  With 128 or more input channels the per-tap kernel of conv_wgrad.cuh
+// (256-column MMAs, one 5-d copy per operand and stage) is faster on every map size measured
+// (28x28: equal, 14x14 and 7x7: 1.3-1.8x, stride 2: 2x); with fewer channels it would be bound
+// by the 9-fold refetch of x, so those layers (64 channels on 56x56 maps) stay here.
 inline bool eligible(const mb_conv_desc* d) {
   if (d->groups != 1 || d->R * d->S <= 1 || d->R * d->S > 16) return false;
+  const bool per_tap_ok = d->C % 32 == 0 && d->K % 32 == 0 && d->C >= tune_int("MB_WGH_MAXC", 128);
+  if (per_tap_ok) return false;
   if (d->stride_h == 1 && d->stride_w == 1) return true;
   return d->stride_h <= 2 && d->stride_w <= 2 && d->Q >= 24 && d->P >= 24;
 }
