@@ -146,6 +146,8 @@ void pick_bn_stages(int kout, long long m_tiles, int* BN, int* stages, size_t* s
   *smem = 512 + 1024 + stage * st + staging;
 }
 
+long long* g_conv_prof = nullptr;   // diagnostics: device buffer for cycle counters (or null)
+
 struct GemmLaunch {
   CUtensorMap a[4];
   CUtensorMap b;
@@ -178,6 +180,7 @@ int launch_gemm(const char* who, GemmLaunch& L, cudaStream_t st) {
       L.out = L.b;
     }
   }
+  L.p.prof = g_conv_prof;
   conv_gemm_kmajor<<<L.grid, 192, L.smem, st>>>(L.a[0], L.a[1], L.a[2], L.a[3], L.b, L.out, L.p);
   return after_launch(who);
 }
@@ -190,7 +193,6 @@ int raise_smem_limit(const char* who, Kernel kernel) {
   return MB_OK;
 }
 
-long long* g_conv_prof = nullptr;   // diagnostics: device buffer for cycle counters (or null)
 
 // ----------------------------------------------------------- halo kernel (stride 1, many taps)
 struct HaloTap { int dh, dw, btap; };

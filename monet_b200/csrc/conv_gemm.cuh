@@ -53,6 +53,7 @@ struct GemmParams {
   int num_taps;
   int stages;
   int tma_store;                // epilogue stages tiles in shared memory and stores them with TMA
+  long long* prof;              // optional: cycle counters written by CTA 0 (diagnostics), or null
   Taps taps;
 };
 
@@ -143,9 +144,13 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
 
   if (warp == 4) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      prefetch_tensormap(&mapA0);
-      prefetch_tensormap(&mapB);
+    // Lane 0 owns the barriers and copies the activation tile, lane 1 copies the filter tile:
+    // the two copies of a stage leave in one warp instruction.
+    {
+      if (lane == 0) {
+        prefetch_tensormap(&mapA0);
+        prefetch_tensormap(&mapB);
+      }
       detail::Ring ring{0, 0u, p.stages};
       uint32_t armed[16];   // per slot: 0 = never armed, else 1 + parity of the last arming
       for (int s = 0; s < 16; ++s) armed[s] = 0;
@@ -158,20 +163,25 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
           const CUtensorMap* ma = mi == 0 ? &mapA0 : mi == 1 ? &mapA1 : mi == 2 ? &mapA2 : &mapA3;
           const int cw = q0 + p.taps.dw[t], ch = p0 + p.taps.dh[t], bt = p.taps.btap[t];
           for (int kc = 0; kc < p.kchunks; ++kc) {
-            if (!mbar_wait(&empty[ring.stage], ring.phase ^ 1u, abort_flag)) {
-              ok = false;
-              break;
+            if (lane == 0) {
+              ok = mbar_wait(&empty[ring.stage], ring.phase ^ 1u, abort_flag);
+              if (ok) {
+                mbar_arrive_expect_tx(&full[ring.stage], tx_bytes);
+                armed[ring.stage] = 1u + ring.phase;
+              }
             }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
             uint8_t* slot = slots_ptr + static_cast<size_t>(ring.stage) * stage_bytes;
-            mbar_arrive_expect_tx(&full[ring.stage], tx_bytes);
-            armed[ring.stage] = 1u + ring.phase;
-            tma_load_4d(ma, slot, &full[ring.stage], kc * kChunkK, cw, ch, n0);
-            tma_load_3d(&mapB, slot + kAStageBytes, &full[ring.stage], kc * kChunkK, bt, c0);
+            if (lane == 0)
+              tma_load_4d(ma, slot, &full[ring.stage], kc * kChunkK, cw, ch, n0);
+            else if (lane == 1)
+              tma_load_3d(&mapB, slot + kAStageBytes, &full[ring.stage], kc * kChunkK, bt, c0);
             ring.advance();
           }
         }
       }
-      if (!ok) {
+      if (!ok && lane == 0) {
         *abort_flag = 1;
         atomicCAS(&g_conv_status, 0, 1);
         // copies already issued still write this CTA's shared memory: give each armed
@@ -191,20 +201,27 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
       detail::Ring ring{0, 0u, p.stages};
       bool ok = true;
       int it = 0;
+      const bool prof = p.prof != nullptr && blockIdx.x == 0;
+      long long w_acc = 0, w_full = 0;
+      const long long tk0 = prof ? clock64() : 0;
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1u;
+        const long long ta0 = prof ? clock64() : 0;
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag)) {
           ok = false;
           break;
         }
+        if (prof) w_acc += clock64() - ta0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * p.BN);
         for (int kb = 0; kb < kblocks; ++kb) {
+          const long long tf0 = prof ? clock64() : 0;
           if (!mbar_wait(&full[ring.stage], ring.phase, abort_flag)) {
             ok = false;
             break;
           }
+          if (prof) w_full += clock64() - tf0;
           tc_fence_after();
           const uint32_t a_addr = slots0 + static_cast<uint32_t>(ring.stage) * stage_bytes;
           const uint64_t da = smem_desc_sw128(a_addr, 16, 1024);
@@ -217,6 +234,7 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
         }
         if (ok) mma_commit(&acc_full[acc]);
       }
+      if (prof) { p.prof[0] = clock64() - tk0; p.prof[1] = w_acc; p.prof[2] = w_full; p.prof[3] = it; }
       if (!ok) {
         *abort_flag = 1;
         atomicCAS(&g_conv_status, 0, 2);

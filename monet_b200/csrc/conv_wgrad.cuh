@@ -340,12 +340,6 @@ __global__ void __launch_bounds__(256) bias_grad_kernel(const float* __restrict_
   }
 }
 
-// experiment knob: integer from the environment, `dflt` when unset
-inline int tune_int(const char* name, int dflt) {
-  const char* v = getenv(name);
-  return v ? atoi(v) : dflt;
-}
-
 namespace wg {
 
 struct Plan {
@@ -413,7 +407,7 @@ inline bool make_plan(const mb_conv_desc* d, int variant, Plan* pl, bool smallc 
   // tap with U consecutive chunks (units ordered tap-major), so that one 5-d copy per operand
   // fills a stage
   p.chunked = 0;
-  if (!smallc && d->C % 32 == 0 && d->K % 32 == 0 && tune_int("MB_WG_CHUNKED", 1)) {
+  if (!smallc && d->C % 32 == 0 && d->K % 32 == 0) {
     int U = p.cchunks < u_max ? p.cchunks : u_max;
     while (p.cchunks % U) --U;
     if (U >= 2 || p.cchunks == 1) {
@@ -427,7 +421,7 @@ inline bool make_plan(const mb_conv_desc* d, int variant, Plan* pl, bool smallc 
   // boxes when every box is a copy of its own (the copy engine takes ~70 cycles per copy,
   // whatever its size), three slots when one copy per operand fills a slot
   const int boxes = p.KA + p.U;
-  int max_rows = static_cast<int>((212 * 1024 / tune_int("MB_WG_SLOTS", p.chunked ? 3 : 2)) / (boxes * 128)) / 8 * 8;
+  int max_rows = static_cast<int>((212 * 1024 / (p.chunked ? 3 : 2)) / (boxes * 128)) / 8 * 8;
   if (max_rows > 128) max_rows = 128;
   if (max_rows < 8) return false;
   if (flat) {

@@ -309,7 +309,8 @@ inline bool plan_launch(int K, int C, int T, int N, int P, int Q, const Tap* tap
     sizes(bh, &ra, &raa, &rb, &rba);
     if (bh + halo_h > 256) continue;
     const size_t stage = static_cast<size_t>(4 * raa + rba) * 128;
-    if (stage <= static_cast<size_t>(tune_int("MB_WGH_STAGE_KB", 108)) * 1024) { best_bh = bh; break; }
+    // two slots of up to 108 KiB: larger tiles beat a third, smaller slot (measured)
+    if (stage <= 108 * 1024) { best_bh = bh; break; }
   }
   if (!best_bh) {
     int ra, raa, rb, rba;
@@ -360,7 +361,7 @@ struct Launches {
 // by the 9-fold refetch of x, so those layers (64 channels on 56x56 maps) stay here.
 inline bool eligible(const mb_conv_desc* d) {
   if (d->groups != 1 || d->R * d->S <= 1 || d->R * d->S > 16) return false;
-  const bool per_tap_ok = d->C % 32 == 0 && d->K % 32 == 0 && d->C >= tune_int("MB_WGH_MAXC", 128);
+  const bool per_tap_ok = d->C % 32 == 0 && d->K % 32 == 0 && d->C >= 128;
   if (per_tap_ok) return false;
   if (d->stride_h == 1 && d->stride_w == 1) return true;
   return d->stride_h <= 2 && d->stride_w <= 2 && d->Q >= 24 && d->P >= 24;
