@@ -180,7 +180,7 @@ def test_fused_operator_classes(cuda):
     assert torch.equal(da.cpu(), oracle.relu_backward(dy, y.cpu())) and torch.equal(db_, da)
 
 
-@pytest.mark.parametrize("policy", ["store_all", "low_memory"])
+@pytest.mark.parametrize("policy", ["store_all", "low_memory", "budget_10gb"])
 def test_fused_network_equals_unfused(cuda, policy):
     """A residual network run with the fused nodes gives the logits of the unfused graph bit for
     bit and the same parameter gradients (up to the unordered atomic sums of the weight

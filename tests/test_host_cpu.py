@@ -123,6 +123,10 @@ def test_graph_fusion_rewrite():
     assert [n.op for n in fused] == [n.op for n in runner.extract_graph(TwoReaders())[0]]
     r = runner.Runner(torchvision.models.resnet18(), runner.low_memory, fuse=True)
     assert all(r.choices[n.id].recompute for n in r.nodes if n.op == "monet::batch_norm_relu")
+    # the 10 GB schedule drops every second block output, never two in a row
+    r = runner.Runner(torchvision.models.resnet50(), runner.budget_10gb, fuse=True)
+    flags = [r.choices[n.id].recompute for n in r.nodes if n.op == "monet::batch_norm_add_relu"]
+    assert flags == [False, True] * 8
 
 
 def test_oracle_maxpool_forms_agree():
