@@ -64,6 +64,7 @@ MICRO = {
     "relu_bwd": ("relu_bwd", 256, 56, 0, 0, 0, 0), "add": ("add", 256, 56, 0, 0, 0, 0),
     "bn_relu_fwd": ("bn_relu_fwd", 256, 56, 0, 0, 0, 0), "bn_add_relu_fwd": ("bn_add_relu_fwd", 256, 56, 0, 0, 0, 0),
     "bn_relu_bwd": ("bn_relu_bwd", 256, 56, 0, 0, 0, 0), "relu_bwd2": ("relu_bwd2", 256, 56, 0, 0, 0, 0),
+    "bn_add_relu_bwd": ("bn_add_relu_bwd", 256, 56, 0, 0, 0, 0),
     "maxpool_fwd": ("maxpool_fwd", 64, 112, 0, 0, 0, 0), "maxpool_bwd": ("maxpool_bwd", 64, 112, 0, 0, 0, 0),
 }
 
@@ -105,6 +106,10 @@ def run_micro(args):
         elif kind == "bn_relu_bwd":
             _, mu, iv = F.bn_fwd_train(x, g, b, None, None, 0.1, 1e-5)
             nbytes, fn = 20 * E, lambda: F.bn_relu_bwd_from_input(dy, x, g, b, mu, iv)
+        elif kind == "bn_add_relu_bwd":
+            yb, mu, iv = F.bn_act_fwd_train(x, dy, True, g, b, None, None, 0.1, 1e-5)
+            dy2 = torch.randn_like(x)
+            nbytes, fn = 32 * E, lambda: F.bn_add_relu_bwd(dy, dy2, yb, x, g, mu, iv)
         elif kind == "relu_bwd2":
             dy2 = torch.randn_like(x)
             nbytes, fn = 16 * E, lambda: F.relu_bwd_act2(dy, dy2, x)
@@ -209,7 +214,8 @@ def family_costs(runner_obj, batch_shape):
     conv pass: activations in + filter + activations out, 2*N*P*Q*K*C*R*S flops.
     bn train fwd 12 B/el (16 with a residual operand), bn cached-stat fwd 8, bn bwd 20 (also
     when it gates by the recomputed ReLU), relu fwd 8 (+1/8 with mask), relu bwd from a saved
-    activation 12 (16 when it also sums two gradients), add 12, max-pool 4*E_in + 4.5*E_out
+    activation 12 (16 when it also sums two gradients), bn+add+relu bwd 32 (28 with one
+    gradient), add 12, max-pool 4*E_in + 4.5*E_out
     each way."""
     import numpy as np
     cost = {}
@@ -246,9 +252,7 @@ def family_costs(runner_obj, batch_shape):
             add("mb_bn_act_fwd_train", 16 * e_out)
             if ch.recompute:
                 add("mb_bn_act_fwd_apply", 12 * e_out)
-            add("mb_relu_bwd_act2" if len(n.users) == 2 else "mb_relu_bwd_act",
-                (16 if len(n.users) == 2 else 12) * e_out)
-            add("mb_bn_bwd_from_input", 20 * e_out)
+            add("mb_bn_add_relu_bwd", (32 if len(n.users) == 2 else 28) * e_out)
         elif n.op in ('aten::relu', 'aten::relu_'):
             add("mb_relu_fwd", 8 * e_out * (2 if ch.recompute else 1))
             add("mb_relu_bwd_act", 12 * e_out)
@@ -268,6 +272,7 @@ TRAFFIC_RATIO = {
     "mb_conv2d_fprop": 679.8 / 738.7, "mb_conv2d_dgrad": 720.5 / 738.7, "mb_conv2d_wgrad": 742.9 / 738.7,
     "mb_bn_bwd_from_output": 1740.8 / 1772.0, "mb_bn_bwd_from_input": 1740.8 / 1772.0,
     "mb_bn_relu_bwd_from_input": (1188.5 + 1743.9) / (1182.0 + 1772.0),
+    "mb_bn_add_relu_bwd": (1188.5 + 1743.9) / (1182.0 + 1772.0),
     "mb_bn_fwd_train": 594.7 / 591.0, "mb_bn_act_fwd_train": (594.7 + 1136.9) / (591.0 + 1182.0),
     "mb_relu_fwd": 1136.5 / 1182.0, "mb_relu_bwd_act": 1744.0 / 1772.0, "mb_relu_bwd_act2": 2333.9 / 2363.0,
     "mb_add_fwd": 1743.8 / 1772.0, "mb_maxpool2d_bwd": 710.5 / 756.0,

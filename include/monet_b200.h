@@ -196,6 +196,17 @@ int mb_bn_relu_bwd_from_input(const float* dy, const float* x, const float* gamm
                               float* dx, float* dgamma, float* dbeta, const mb_bn_desc* d,
                               void* workspace, size_t workspace_bytes, void* stream);
 
+/* Backward through y = relu(bn(x) + r): the gated gradient
+ * d = (dy1 + dy2) * (y > 0) (dy2 may be NULL) is formed, written to `d` - it is
+ * the gradient of r - and summed per channel in ONE pass, then dx follows from
+ * d and x as in mb_bn_bwd_from_input.  Replaces relu.py's backward (plus the
+ * executor's gradient add, schedule.py:296-301) followed by cudnn_backward
+ * (lrbn.cpp:43-70): 32 instead of 36 bytes per element.  d may alias dy1.     */
+int mb_bn_add_relu_bwd(const float* dy1, const float* dy2, const float* y, const float* x,
+                       const float* gamma, const float* save_mean, const float* save_invstd,
+                       float* d, float* dx, float* dgamma, float* dbeta, const mb_bn_desc* desc,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- softmax / cross-entropy (replaces softmax.cpp:11-33, softmax.cu) --- */
 
 /* Softmax over `classes` for a [outer, classes, inner] contiguous tensor.   */

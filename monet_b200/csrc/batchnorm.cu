@@ -29,6 +29,9 @@
 //             re-evaluated from x with exactly the forward's expression
 //             z = fma(x - mean, invstd*gamma, beta), so no mask and no output is kept and
 //             dy is gated on the fly in both the reduce and the sweep.
+//   backward  through y = relu(bn(x) + r) from x and y: the reduce pass also forms the gated
+//             gradient d = (dy1 [+ dy2]) * (y > 0), writes it (it is the residual's gradient)
+//             and sums it, so the separate ReLU-backward pass disappears.
 #include "common.cuh"
 
 #include <mutex>
@@ -87,13 +90,15 @@ Geometry make_geometry(const mb_bn_desc* d) {
 // workspace: partials [2][S][C] floats, then constants [2][C] floats
 size_t ws_floats(const Geometry& g) { return (2 * static_cast<size_t>(g.S) + 2) * g.C; }
 
-enum { kFwd = 0, kBwd = 1, kBwdRelu = 2, kFwdRes = 3 };
+enum { kFwd = 0, kBwd = 1, kBwdRelu = 2, kFwdRes = 3, kBwdGate = 4 };
 
 // ------------------------------------------------------------- NHWC reduce
 // MODE kFwd: a = x;          accumulates (x-K), (x-K)^2
 // MODE kBwd: a = dy, b = v;  accumulates dy, dy*(v-p0)*p1
 // MODE kBwdRelu: a = dy, b = x, p0 = mean, p1 = invstd; dy is first gated by
 //                fma(x-mean, invstd*gamma, beta) > 0
+// MODE kBwdGate: a = dy1, a2 = dy2 or null, act = y, b = x, p0 = mean, p1 = invstd;
+//                d = (dy1 + dy2) * (y > 0) is written to dout (may alias a) and summed
 template <int MODE, int VEC>
 __global__ void __launch_bounds__(kBlock) bn_reduce_nhwc(const float* __restrict__ a,
                                                          const float* __restrict__ b,
@@ -104,7 +109,9 @@ __global__ void __launch_bounds__(kBlock) bn_reduce_nhwc(const float* __restrict
                                                          const float* __restrict__ bv,
                                                          float* __restrict__ ws,
                                                          int C, size_t M, int S, int tx_n,
-                                                         int ty_n) {
+                                                         int ty_n, const float* a2 = nullptr,
+                                                         const float* act = nullptr,
+                                                         float* dout = nullptr) {
   extern __shared__ float sm[];  // [ty_n][tx_n][2*VEC]
   const int tx = threadIdx.x % tx_n, ty = threadIdx.x / tx_n;
   const int c0 = (blockIdx.y * tx_n + tx) * VEC;
@@ -146,6 +153,18 @@ __global__ void __launch_bounds__(kBlock) bn_reduce_nhwc(const float* __restrict
           const size_t off = (r + i * static_cast<size_t>(ty_n)) * C + c0;
           u[i] = __ldcs(reinterpret_cast<const float4*>(a + off));
           if (MODE != kFwd) w[i] = __ldcs(reinterpret_cast<const float4*>(b + off));
+          if (MODE == kBwdGate) {
+            const float4 y4 = __ldcs(reinterpret_cast<const float4*>(act + off));
+            if (a2) {
+              const float4 v2 = __ldcs(reinterpret_cast<const float4*>(a2 + off));
+              u[i].x += v2.x; u[i].y += v2.y; u[i].z += v2.z; u[i].w += v2.w;
+            }
+            u[i].x = y4.x > 0.f ? u[i].x : 0.f;
+            u[i].y = y4.y > 0.f ? u[i].y : 0.f;
+            u[i].z = y4.z > 0.f ? u[i].z : 0.f;
+            u[i].w = y4.w > 0.f ? u[i].w : 0.f;
+            *reinterpret_cast<float4*>(dout + off) = u[i];
+          }
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -171,7 +190,12 @@ __global__ void __launch_bounds__(kBlock) bn_reduce_nhwc(const float* __restrict
       const size_t off = r * C + c0;
 #pragma unroll
       for (int k = 0; k < VEC; ++k) {
-        const float uu = __ldg(a + off + k);
+        float uu = __ldg(a + off + k);
+        if (MODE == kBwdGate) {
+          if (a2) uu += __ldg(a2 + off + k);
+          uu = __ldg(act + off + k) > 0.f ? uu : 0.f;
+          dout[off + k] = uu;
+        }
         if (MODE == kFwd) {
           const float dlt = uu - p0[k];
           s1[k] += dlt;
@@ -223,7 +247,10 @@ __global__ void __launch_bounds__(kBlock) bn_reduce_nchw(const float* __restrict
                                                          const float* __restrict__ gv,
                                                          const float* __restrict__ bv,
                                                          float* __restrict__ ws,
-                                                         int C, int HW, size_t M, int S) {
+                                                         int C, int HW, size_t M, int S,
+                                                         const float* a2 = nullptr,
+                                                         const float* act = nullptr,
+                                                         float* dout = nullptr) {
   __shared__ float red[2][kBlock / 32];
   const int c = blockIdx.x;
   float p0, p1 = 1.f, pg = 0.f, pb = 0.f;
@@ -246,7 +273,12 @@ __global__ void __launch_bounds__(kBlock) bn_reduce_nchw(const float* __restrict
   for (size_t j = j0 + threadIdx.x; j < j1; j += kBlock) {
     const size_t n = j / HW;
     const size_t off = (n * C + c) * HW + (j - n * HW);
-    const float u = __ldg(a + off);
+    float u = __ldg(a + off);
+    if (MODE == kBwdGate) {
+      if (a2) u += __ldg(a2 + off);
+      u = __ldg(act + off) > 0.f ? u : 0.f;
+      dout[off] = u;
+    }
     if (MODE == kFwd) {
       const float dlt = u - p0;
       s1 += dlt;
@@ -462,17 +494,18 @@ int check(const char* who, const mb_bn_desc* d) {
 template <int MODE>
 int run_reduce(const char* who, const mb_bn_desc* d, const Geometry& g, const float* a,
                const float* b, const float* p0v, const float* p1v, int p1_is_gamma, float* ws,
-               cudaStream_t st, const float* gv = nullptr, const float* bv = nullptr) {
+               cudaStream_t st, const float* gv = nullptr, const float* bv = nullptr,
+               const float* a2 = nullptr, const float* act = nullptr, float* dout = nullptr) {
   if (d->layout == MB_NHWC) {
     dim3 grid(g.S, g.slabs);
     const size_t smem = static_cast<size_t>(kBlock) * 2 * g.vec * sizeof(float);
     if (g.vec == 4)
-      bn_reduce_nhwc<MODE, 4><<<grid, kBlock, smem, st>>>(a, b, p0v, p1v, p1_is_gamma, gv, bv, ws, g.C, g.M, g.S, g.tx, g.ty);
+      bn_reduce_nhwc<MODE, 4><<<grid, kBlock, smem, st>>>(a, b, p0v, p1v, p1_is_gamma, gv, bv, ws, g.C, g.M, g.S, g.tx, g.ty, a2, act, dout);
     else
-      bn_reduce_nhwc<MODE, 1><<<grid, kBlock, smem, st>>>(a, b, p0v, p1v, p1_is_gamma, gv, bv, ws, g.C, g.M, g.S, g.tx, g.ty);
+      bn_reduce_nhwc<MODE, 1><<<grid, kBlock, smem, st>>>(a, b, p0v, p1v, p1_is_gamma, gv, bv, ws, g.C, g.M, g.S, g.tx, g.ty, a2, act, dout);
   } else {
     dim3 grid(g.C, g.S);
-    bn_reduce_nchw<MODE><<<grid, kBlock, 0, st>>>(a, b, p0v, p1v, p1_is_gamma, gv, bv, ws, g.C, g.HW, g.M, g.S);
+    bn_reduce_nchw<MODE><<<grid, kBlock, 0, st>>>(a, b, p0v, p1v, p1_is_gamma, gv, bv, ws, g.C, g.HW, g.M, g.S, a2, act, dout);
   }
   return after_launch(who);
 }
@@ -622,6 +655,36 @@ int mb_bn_act_fwd_apply(const float* x, const float* residual, int relu, const f
                         const mb_bn_desc* d, void* stream) {
   return fwd_apply_impl("mb_bn_act_fwd_apply", x, residual, relu, gamma, beta, mean, invstd, y, d,
                         stream);
+}
+
+int mb_bn_add_relu_bwd(const float* dy1, const float* dy2, const float* y, const float* x,
+                       const float* gamma, const float* save_mean, const float* save_invstd,
+                       float* d, float* dx, float* dgamma, float* dbeta, const mb_bn_desc* desc,
+                       void* workspace, size_t workspace_bytes, void* stream) {
+  const char* who = "mb_bn_add_relu_bwd";
+  int rc = check(who, desc);
+  if (rc) return rc;
+  if (!dy1 || !y || !x || !gamma || !save_mean || !save_invstd || !d || !dx || !dgamma || !dbeta)
+    return fail(MB_ERR_INVALID_ARGUMENT, "%s: null pointer", who);
+  rc = check_alignment(who, desc, dy1, y, x);
+  if (!rc) rc = check_alignment(who, desc, d, dx, dy2 ? dy2 : dy1);
+  if (rc) return rc;
+  Geometry g = make_geometry(desc);
+  if (!workspace || workspace_bytes < ws_floats(g) * sizeof(float))
+    return fail(MB_ERR_WORKSPACE, "%s: workspace of %zu bytes needed, %zu given", who,
+                ws_floats(g) * sizeof(float), workspace ? workspace_bytes : size_t(0));
+  float* ws = static_cast<float*>(workspace);
+  float* ws_const = ws + 2 * static_cast<size_t>(g.S) * g.C;
+  cudaStream_t st = as_stream(stream);
+  rc = run_reduce<kBwdGate>("bn_add_relu_bwd_reduce", desc, g, dy1, x, save_mean, save_invstd, 0, ws,
+                            st, nullptr, nullptr, dy2, y, d);
+  if (rc) return rc;
+  bn_finalize<kBwd><<<(g.C + 31) / 32, 32 * kFinStripes, 0, st>>>(ws, ws_const, nullptr, 0, g.C, g.M, g.S, 0.f,
+                                                    0.f, nullptr, nullptr, dgamma, dbeta);
+  rc = after_launch("bn_bwd_finalize");
+  if (rc) return rc;
+  SweepConst k{gamma, nullptr, nullptr, save_invstd, save_mean, save_invstd, 0, ws_const, 0};
+  return run_sweep<kBwd>("bn_bwd_sweep", desc, g, d, x, dx, k, st);
 }
 
 int mb_bn_relu_bwd_from_input(const float* dy, const float* x, const float* gamma,

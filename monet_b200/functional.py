@@ -425,6 +425,32 @@ def bn_relu_bwd_from_input(dy, x, gamma, beta, save_mean, save_invstd, inplace=F
     return dx, dgamma, dbeta
 
 
+def bn_add_relu_bwd(dy1, dy2, y, x, gamma, save_mean, save_invstd):
+    """(d, dx, dgamma, dbeta) through y = relu(bn(x) + r): d = (dy1 [+ dy2]) * (y > 0) is
+    written over dy1 (the gradient of r), dx is the gradient of x."""
+    _need_cuda(dy1, y, x, gamma, save_mean, save_invstd); _f32(dy1, "dy1"); _f32(x, "x")
+    xd = _bn_dense(x)
+    yd = like(xd, y) if xd.dim() == 4 else y.contiguous()
+    d1 = like(xd, dy1) if xd.dim() == 4 else dy1.contiguous()
+    d2 = None
+    if dy2 is not None:
+        _need_cuda(dy2); _f32(dy2, "dy2")
+        d2 = like(xd, dy2) if xd.dim() == 4 else dy2.contiguous()
+    if d1.shape != xd.shape or yd.shape != xd.shape or (d2 is not None and d2.shape != xd.shape):
+        raise RuntimeError("monet_b200 batch norm backward: shape mismatch")
+    desc = bn_desc(xd, 0.0, 0.0)
+    dx = torch.empty_like(xd)
+    dgamma = torch.empty(desc.C, dtype=torch.float32, device=x.device)
+    dbeta = torch.empty(desc.C, dtype=torch.float32, device=x.device)
+    ws = _bn_workspace(desc, x.device)
+    check(lib().mb_bn_add_relu_bwd(
+        d1.data_ptr(), d2.data_ptr() if d2 is not None else None, yd.data_ptr(), xd.data_ptr(),
+        gamma.data_ptr(), save_mean.data_ptr(), save_invstd.data_ptr(), d1.data_ptr(),
+        dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), C.byref(desc), ws.data_ptr(),
+        ws.numel(), _stream()), "bn_add_relu_bwd")
+    return d1, dx, dgamma, dbeta
+
+
 # ------------------------------------------------------------------------ softmax
 
 def _split_dim(x: torch.Tensor, dim: int):

@@ -79,7 +79,7 @@ class InputActBatchNormReLU(_FusedBatchNorm):
 class InputActBatchNormAddReLU(_FusedBatchNorm):
     """y = relu(bn(x) + residual).  Backward keeps x and y: the gated gradient
     d = dy * (y > 0) is what the residual branch receives, and batch norm backpropagates d
-    from x.  ``backward`` also accepts a pair ``(dy1, dy2)`` of gradients still to be summed
+    from x; d is formed inside the batch-norm backward's first pass.  ``backward`` also accepts a pair ``(dy1, dy2)`` of gradients still to be summed
     (y read by two consumers) and folds the sum into the gate."""
     backward_storage = [InputStorage(0, 1, 2, 3, 4), OutputStorage()]
     accepts_grad_pair = True
@@ -98,10 +98,10 @@ class InputActBatchNormAddReLU(_FusedBatchNorm):
             if not training:
                 raise NotImplementedError("batch-norm backward in eval mode")
             if isinstance(grad_output, (tuple, list)):
-                d = F.relu_bwd_act2(grad_output[0], grad_output[1], output)
+                g1, g2 = grad_output
             else:
-                d = F.relu_bwd_act(grad_output, output, 0.0, inplace=True)
-            dx, dw, db = F.bn_bwd_from_input(d, input_, weight, save_mean, save_invstd)
+                g1, g2 = grad_output, None
+            d, dx, dw, db = F.bn_add_relu_bwd(g1, g2, output, input_, weight, save_mean, save_invstd)
             if not nodel:
                 del stored[5], stored[4], stored[3], stored[2], stored[1], stored[0]
             return dx, dw, db, None, None, d

@@ -90,6 +90,35 @@ def test_bn_relu_backward(cuda, shape, nhwc):
     assert dx3.data_ptr() == dyc.data_ptr() and torch.equal(dx3, dx)
 
 
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("nhwc", [False, True])
+@pytest.mark.parametrize("pair", [False, True])
+def test_bn_add_relu_backward(cuda, shape, nhwc, pair):
+    """Backward through y = relu(bn(x) + r) with the gate folded into the batch-norm reduce."""
+    from monet_b200 import functional as F
+    x, gamma, beta, rm, rv, res, dy = _data(shape, seed=2)
+    xg, rg = _fmt(x.to(cuda), nhwc), _fmt(res.to(cuda), nhwc)
+    gg, bg = gamma.to(cuda), beta.to(cuda)
+    y, mean, invstd = F.bn_act_fwd_train(xg, rg, True, gg, bg, None, None, 0.1, 1e-5)
+    g1, g2 = (dy * 0.3, dy * 0.7) if pair else (dy, None)
+    d_ref = oracle.relu_backward_sum2(g1, g2, y.cpu()) if pair else oracle.relu_backward(dy, y.cpu())
+    ref_dx, ref_dg, ref_db = oracle.bn_backward_from_input(d_ref, x, gamma, 1e-5)
+    scale = max(1.0, float(ref_dx.abs().max()))
+    g1g = _fmt(g1.to(cuda), nhwc)
+    g2g = _fmt(g2.to(cuda), nhwc) if pair else None
+    # the unfused chain on the GPU, for bit equality
+    dd = F.relu_bwd_act2(g1g.clone(memory_format=torch.preserve_format), g2g, y) if pair else \
+        F.relu_bwd_act(g1g, y, 0.0, inplace=False)
+    dx2, dg2, db2 = F.bn_bwd_from_input(dd, xg, gg, mean, invstd)
+    d, dx, dg, db = F.bn_add_relu_bwd(g1g, g2g, y, xg, gg, mean, invstd)
+    assert d.data_ptr() == g1g.data_ptr()                   # written over the first gradient
+    assert torch.equal(d.cpu(), d_ref)
+    assert torch.allclose(dx.cpu(), ref_dx, rtol=RTOL, atol=1e-5 * scale)
+    assert torch.allclose(dg.cpu(), ref_dg, rtol=1e-4, atol=1e-4)
+    assert torch.allclose(db.cpu(), ref_db, rtol=1e-4, atol=1e-4)
+    assert torch.equal(dx, dx2) and torch.equal(dg, dg2) and torch.equal(db, db2)
+
+
 @pytest.mark.parametrize("n", [0, 1, 7, 8, 9, 1000, 4097, 1 << 20, (1 << 20) + 3])
 def test_relu_backward_two_gradients_and_add_relu(cuda, n):
     from monet_b200 import functional as F
