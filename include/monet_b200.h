@@ -278,8 +278,10 @@ size_t mb_conv_workspace_bytes(int pass, int variant, const mb_conv_desc* d);
 int mb_conv2d_fprop(const float* x, const float* w, const float* bias, float* y,
                     const mb_conv_desc* d, int variant, void* workspace, size_t workspace_bytes,
                     void* stream);
-/* dx = backward-data.  Variant 0: implicit GEMM over dy with the filter
- * transposed to [C][R][S][K] in the workspace (K*R*S*C*4 bytes).             */
+/* dx = backward-data.  Variant 0: implicit GEMM over dy.  When C is a multiple of
+ * 32 the filter is read in place (MN-major tiles of w) and no workspace is needed;
+ * otherwise it is first transposed to [C][R][S][K] in the workspace
+ * (mb_conv_workspace_bytes = K*R*S*C*4 bytes).                                  */
 int mb_conv2d_dgrad(const float* dy, const float* w, float* dx, const mb_conv_desc* d, int variant,
                     void* workspace, size_t workspace_bytes, void* stream);
 /* dw = backward-filter, dbias[K] = sum of dy when non-NULL (conv.py:313-314).

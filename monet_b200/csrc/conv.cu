@@ -97,6 +97,16 @@ int encode_filter(const char* who, CUtensorMap* m, const float* base, int Cin, i
   return encode_map(who, m, base, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
+// The filter of a backward-data pass read in place: w is [K][taps][C] and the GEMM reduces over
+// K, so a tile of `cols` output columns (input channels of the convolution) x 32 k is MN-major:
+// view {32, K, taps, C/32}, box {32, 32, 1, cols/32} = cols/32 boxes of [32 k rows][32 columns].
+int encode_filter_mn(const char* who, CUtensorMap* m, const float* w, int K, int taps, int C, int cols) {
+  cuuint64_t dims[4] = {(cuuint64_t)kChunkK, (cuuint64_t)K, (cuuint64_t)taps, (cuuint64_t)(C / kChunkK)};
+  cuuint64_t strides[3] = {(cuuint64_t)taps * C * 4, (cuuint64_t)C * 4, (cuuint64_t)kChunkK * 4};
+  cuuint32_t box[4] = {(cuuint32_t)kChunkK, (cuuint32_t)kChunkK, 1, (cuuint32_t)(cols / kChunkK)};
+  return encode_map(who, m, w, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+}
+
 // ------------------------------------------------------------------- tiling
 struct TileShape { int bw, bh, bn; };
 
@@ -202,7 +212,7 @@ struct HaloTap { int dh, dw, btap; };
 // geometry does not fit, so that the caller can fall back to the per-tap kernel.
 int run_halo(const char* who, const float* in, int Cin, int Win, int Hin, const float* filt, int T,
              float* out, int Kout, int Qo, int Po, int N, const HaloTap* taps, int ntaps,
-             const float* bias, cudaStream_t st) {
+             const float* bias, cudaStream_t st, bool filter_mn = false) {
   if (ntaps < 2 || ntaps > kMaxTaps) return MB_ERR_UNSUPPORTED;
   int min_dh = taps[0].dh, max_dh = taps[0].dh, min_dw = taps[0].dw, max_dw = taps[0].dw;
   for (int t = 1; t < ntaps; ++t) {
@@ -274,7 +284,9 @@ int run_halo(const char* who, const float* in, int Cin, int Win, int Hin, const 
   const long long C4 = static_cast<long long>(Cin) * 4, K4 = static_cast<long long>(Kout) * 4;
   int rc = encode_act(who, &ma, in, Cin, Win, Hin, N, C4, C4 * Win, C4 * Win * Hin, p.Wh, p.Hb, p.bn);
   if (rc) return rc;
-  rc = encode_filter(who, &mb_, filt, Cin, T, Kout, p.BN);
+  p.b_mn = filter_mn ? 1 : 0;
+  rc = filter_mn ? encode_filter_mn(who, &mb_, filt, Cin, T, Kout, p.BN)
+                 : encode_filter(who, &mb_, filt, Cin, T, Kout, p.BN);
   if (rc) return rc;
   rc = encode_act(who, &mo, out, Kout, Qo, Po, N, K4, K4 * Qo, K4 * Qo * Po, p.Wh, p.Hout, p.bn);
   if (rc) return rc;
@@ -558,7 +570,8 @@ int mb_conv_num_variants(int pass) {
 
 size_t mb_conv_workspace_bytes(int pass, int variant, const mb_conv_desc* d) {
   if (!d || variant < 0 || variant >= mb_conv_num_variants(pass)) return 0;
-  if (pass == MB_CONV_DGRAD) return static_cast<size_t>(d->K) * d->R * d->S * d->C * sizeof(float);
+  if (pass == MB_CONV_DGRAD)   // the filter is read in place when its tiles are whole 32-channel groups
+    return d->C % 32 == 0 ? 0 : static_cast<size_t>(d->K) * d->R * d->S * d->C * sizeof(float);
   if (pass == MB_CONV_WGRAD) return wgrad_workspace_bytes(d, variant);
   return 0;
 }
@@ -686,17 +699,22 @@ int mb_conv2d_dgrad(const float* dy, const float* w, float* dx, const mb_conv_de
   if (!aligned(dy, 16) || !aligned(w, 16) || !aligned(dx, 16))
     return fail(MB_ERR_INVALID_ARGUMENT, "%s: pointers must be 16-byte aligned", who);
   const size_t need = mb_conv_workspace_bytes(MB_CONV_DGRAD, variant, d);
-  if (!workspace || workspace_bytes < need || !aligned(workspace, 16))
+  if (need && (!workspace || workspace_bytes < need || !aligned(workspace, 16)))
     return fail(MB_ERR_WORKSPACE, "%s: workspace of %zu bytes needed, %zu given", who, need,
                 workspace ? workspace_bytes : size_t(0));
   cudaStream_t st = as_stream(stream);
   const int T = d->R * d->S;
-  float* wt = static_cast<float*>(workspace);   // [C][R*S][K]
-  {
+  // The GEMM reduces over K.  With whole 32-channel groups of C the filter tile is taken MN-major
+  // straight from w = [K][R*S][C]; otherwise w is first transposed to [C][R*S][K] in the workspace.
+  const bool filter_mn = need == 0;
+  const float* wt = w;
+  if (!filter_mn) {
+    float* t = static_cast<float*>(workspace);
     const size_t total = static_cast<size_t>(d->K) * T * d->C;
-    transpose_filter<<<grid_for(total, 256, 8), 256, 0, st>>>(w, wt, d->K, T, d->C);
+    transpose_filter<<<grid_for(total, 256, 8), 256, 0, st>>>(w, t, d->K, T, d->C);
     rc = after_launch("conv_transpose_filter");
     if (rc) return rc;
+    wt = t;
   }
   if (d->stride_h == 1 && d->stride_w == 1 && T > 1) {
     HaloTap taps[kMaxTaps];
@@ -704,7 +722,8 @@ int mb_conv2d_dgrad(const float* dy, const float* w, float* dx, const mb_conv_de
     for (int r = 0; r < d->R; ++r)
       for (int s = 0; s < d->S; ++s)
         taps[nt++] = HaloTap{d->pad_h - r * d->dil_h, d->pad_w - s * d->dil_w, r * d->S + s};
-    rc = run_halo(who, dy, d->K, d->Q, d->P, wt, T, dx, d->C, d->W, d->H, d->N, taps, nt, nullptr, st);
+    rc = run_halo(who, dy, d->K, d->Q, d->P, wt, T, dx, d->C, d->W, d->H, d->N, taps, nt, nullptr, st,
+                  filter_mn);
     if (rc != MB_ERR_UNSUPPORTED) return rc;
   }
   const long long K4 = static_cast<long long>(d->K) * 4;
@@ -780,7 +799,9 @@ int mb_conv2d_dgrad(const float* dy, const float* w, float* dx, const mb_conv_de
       const long long tiles = m_tiles * p.tiles_c;
       if (tiles > 0x7fffffffLL) return fail(MB_ERR_UNSUPPORTED, "%s: too many tiles", who);
       p.num_tiles = static_cast<int>(tiles);
-      rc = encode_filter(who, &L.b, wt, d->K, T, d->C, p.BN);
+      p.b_mn = filter_mn ? 1 : 0;
+      rc = filter_mn ? encode_filter_mn(who, &L.b, wt, d->K, T, d->C, p.BN)
+                     : encode_filter(who, &L.b, wt, d->K, T, d->C, p.BN);
       if (rc) return rc;
       L.grid = p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs;
       rc = launch_gemm("conv_dgrad_tcgen05", L, st);

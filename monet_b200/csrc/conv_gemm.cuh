@@ -53,6 +53,8 @@ struct GemmParams {
   int num_taps;
   int stages;
   int tma_store;                // epilogue stages tiles in shared memory and stores them with TMA
+  int b_mn;                     // 1: the filter tile is MN-major, [32-column group][32 k rows][32 columns]
+                                //    straight from a [k][tap][n] filter (backward-data without a transpose)
   long long* prof;              // optional: cycle counters written by CTA 0 (diagnostics), or null
   Taps taps;
 };
@@ -176,7 +178,12 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
             if (lane == 0)
               tma_load_4d(ma, slot, &full[ring.stage], kc * kChunkK, cw, ch, n0);
             else if (lane == 1)
-              tma_load_3d(&mapB, slot + kAStageBytes, &full[ring.stage], kc * kChunkK, bt, c0);
+{
+              if (p.b_mn)
+                tma_load_4d(&mapB, slot + kAStageBytes, &full[ring.stage], 0, kc * kChunkK, bt, c0 / 32);
+              else
+                tma_load_3d(&mapB, slot + kAStageBytes, &full[ring.stage], kc * kChunkK, bt, c0);
+            }
             ring.advance();
           }
         }
@@ -197,7 +204,8 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
   } else if (warp == 5) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = idesc_tf32(kTileM, p.BN, 0, 0);
+      const uint32_t idesc = idesc_tf32(kTileM, p.BN, 0, p.b_mn);
+      const uint32_t b_step = p.b_mn ? 64u : 2u;   // 8 k: 8 rows of 128 bytes, or 32 bytes along a row
       detail::Ring ring{0, 0u, p.stages};
       bool ok = true;
       int it = 0;
@@ -225,10 +233,11 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
           tc_fence_after();
           const uint32_t a_addr = slots0 + static_cast<uint32_t>(ring.stage) * stage_bytes;
           const uint64_t da = smem_desc_sw128(a_addr, 16, 1024);
-          const uint64_t db = smem_desc_sw128(a_addr + kAStageBytes, 16, 1024);
+          const uint64_t db = p.b_mn ? smem_desc(a_addr + kAStageBytes, 4096, 512, kSwizzle128BBase32B)
+                                     : smem_desc_sw128(a_addr + kAStageBytes, 16, 1024);
 #pragma unroll
           for (int k = 0; k < 4; ++k)   // 4 x K=8 per 32-channel chunk, 32 bytes apart
-            mma_tf32(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            mma_tf32(d_tmem, da + 2u * k, db + b_step * k, idesc, (kb | k) != 0 ? 1u : 0u);
           mma_commit(&empty[ring.stage]);
           ring.advance();
         }

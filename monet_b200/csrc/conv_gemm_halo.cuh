@@ -37,6 +37,7 @@ struct HaloParams {
   int org_w, org_h;          // input coordinates of the box origin relative to the output pixel
   int a_stages, b_stages;
   int acc_bufs;              // 1 or 2 accumulator sets in tensor memory
+  int b_mn;                  // 1: MN-major filter tiles (see GemmParams)
   long long* prof;           // optional: 16 cycle counters written by CTA 0 (diagnostics), or null
   short tap_off[kMaxTaps];   // operand row offset of each tap
   unsigned char btap[kMaxTaps];
@@ -127,8 +128,11 @@ conv_gemm_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             if (!timed_wait(&b_empty[rb.stage], rb.phase ^ 1u, w_be)) { ok = false; break; }
             mbar_arrive_expect_tx(&b_full[rb.stage], b_slot_bytes);
             armed_b[rb.stage] = 1u + rb.phase;
-            tma_load_3d(&mapB, base_ptr + a_region + static_cast<size_t>(rb.stage) * b_slot_bytes,
-                        &b_full[rb.stage], kc * kChunkK, p.btap[t], c0);
+            uint8_t* b_dst = base_ptr + a_region + static_cast<size_t>(rb.stage) * b_slot_bytes;
+            if (p.b_mn)
+              tma_load_4d(&mapB, b_dst, &b_full[rb.stage], 0, kc * kChunkK, p.btap[t], c0 / 32);
+            else
+              tma_load_3d(&mapB, b_dst, &b_full[rb.stage], kc * kChunkK, p.btap[t], c0);
             rb.advance();
           }
         }
@@ -154,7 +158,8 @@ conv_gemm_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
   } else if (warp == 5) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = idesc_tf32(kTileM, p.BN, 0, 0);
+      const uint32_t idesc = idesc_tf32(kTileM, p.BN, 0, p.b_mn);
+      const uint32_t b_step = p.b_mn ? 64u : 2u;
       detail::Ring ra{0, 0u, p.a_stages}, rb{0, 0u, p.b_stages};
       bool ok = true;
       int it = 0;
@@ -172,7 +177,9 @@ conv_gemm_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
           for (int t = 0; t < p.num_taps; ++t) {
             if (!timed_wait(&b_full[rb.stage], rb.phase, w_bf)) { ok = false; break; }
             tc_fence_after();
-            const uint64_t db = smem_desc_sw128(base0 + a_region + static_cast<uint32_t>(rb.stage) * b_slot_bytes, 16, 1024);
+            const uint32_t b_addr = base0 + a_region + static_cast<uint32_t>(rb.stage) * b_slot_bytes;
+            const uint64_t db = p.b_mn ? smem_desc(b_addr, 4096, 512, kSwizzle128BBase32B)
+                                       : smem_desc_sw128(b_addr, 16, 1024);
             const uint32_t first = (kc | t) == 0 ? 0u : 1u;
             for (int mt = 0; mt < p.MT; ++mt) {
               // operand rows of this tap: (mt*128 + off) rows into the halo box
@@ -180,7 +187,7 @@ conv_gemm_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
               const uint32_t d_tmem = d_base + static_cast<uint32_t>(mt * p.BN);
 #pragma unroll
               for (int k = 0; k < 4; ++k)
-                mma_tf32(d_tmem, da + 2u * k, db + 2u * k, idesc, (first | k) != 0 ? 1u : 0u);
+                mma_tf32(d_tmem, da + 2u * k, db + b_step * k, idesc, (first | k) != 0 ? 1u : 0u);
             }
             mma_commit(&b_empty[rb.stage]);
             rb.advance();
