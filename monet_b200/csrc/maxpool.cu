@@ -23,11 +23,15 @@ __device__ __forceinline__ bool better(float v, float best) { return v > best ||
 // One thread = one output pixel x 8 channels: per tap two 128-bit loads, then a
 // 256-bit value store and one 32-bit nibble store.  Consecutive threads walk the
 // channel groups first, so a warp reads contiguous runs of C floats.
+// KH/KW > 0 fix the window at compile time (dilation 1) so that the tap loops unroll.
+template <int KH, int KW>
 __global__ void __launch_bounds__(256) maxpool_fwd_nhwc8(const float* __restrict__ x,
                                                          float* __restrict__ y,
                                                          uint32_t* __restrict__ nib, PoolP p,
                                                          size_t total) {
   const int cg = p.C / 8;
+  const int kh = KH ? KH : p.kh, kw = KW ? KW : p.kw;
+  const int dh = KH ? 1 : p.dh, dw = KW ? 1 : p.dw;
   for (size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
        t += static_cast<size_t>(gridDim.x) * blockDim.x) {
     const int g = static_cast<int>(t % cg);
@@ -46,13 +50,15 @@ __global__ void __launch_bounds__(256) maxpool_fwd_nhwc8(const float* __restrict
       idx[k] = 0;
     }
     const float* xn = x + static_cast<size_t>(n) * p.H * p.W * p.C + g * 8;
-    for (int i = 0; i < p.kh; ++i) {
-      const int h = h0 + i * p.dh;
+#pragma unroll
+    for (int i = 0; i < kh; ++i) {
+      const int h = h0 + i * dh;
       if (h < 0 || h >= p.H) continue;
-      for (int j = 0; j < p.kw; ++j) {
-        const int w = w0 + j * p.dw;
+#pragma unroll
+      for (int j = 0; j < kw; ++j) {
+        const int w = w0 + j * dw;
         if (w < 0 || w >= p.W) continue;
-        const uint32_t local = i * p.kw + j;
+        const uint32_t local = i * kw + j;
         const float4* src =
             reinterpret_cast<const float4*>(xn + (static_cast<size_t>(h) * p.W + w) * p.C);
         const float4 a = __ldg(src), b = __ldg(src + 1);
@@ -84,11 +90,17 @@ __global__ void __launch_bounds__(256) maxpool_fwd_nhwc8(const float* __restrict
 
 // ---------------------------------------------------------------- NHWC bwd
 // One thread = one INPUT pixel x 8 channels; loops over the windows covering it.
+// KH/KW/SH/SW > 0 fix the window and stride at compile time (dilation 1): the tap loops
+// unroll and the divisions by the stride become shifts; 0 takes them from `p`.
+template <int KH, int KW, int SH, int SW>
 __global__ void __launch_bounds__(256) maxpool_bwd_nhwc8(const float* __restrict__ dy,
                                                          const uint32_t* __restrict__ nib,
                                                          float* __restrict__ dx, PoolP p,
                                                          size_t total) {
   const int cg = p.C / 8;
+  const int kh = KH ? KH : p.kh, kw = KW ? KW : p.kw;
+  const int sh = SH ? SH : p.sh, sw = SW ? SW : p.sw;
+  const int dh = KH ? 1 : p.dh, dw = KW ? 1 : p.dw;
   for (size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
        t += static_cast<size_t>(gridDim.x) * blockDim.x) {
     const int g = static_cast<int>(t % cg);
@@ -101,17 +113,19 @@ __global__ void __launch_bounds__(256) maxpool_bwd_nhwc8(const float* __restrict
 #pragma unroll
     for (int k = 0; k < 8; ++k) acc[k] = 0.f;
     // windows pp with pp*sh - ph + i*dh == h for some tap i in [0, kh)
-    for (int i = 0; i < p.kh; ++i) {
-      const int hn = h + p.ph - i * p.dh;
-      if (hn < 0 || hn % p.sh) continue;
-      const int pp = hn / p.sh;
+#pragma unroll
+    for (int i = 0; i < kh; ++i) {
+      const int hn = h + p.ph - i * dh;
+      if (hn < 0 || hn % sh) continue;
+      const int pp = hn / sh;
       if (pp >= p.P) continue;
-      for (int j = 0; j < p.kw; ++j) {
-        const int wn = w + p.pw - j * p.dw;
-        if (wn < 0 || wn % p.sw) continue;
-        const int q = wn / p.sw;
+#pragma unroll
+      for (int j = 0; j < kw; ++j) {
+        const int wn = w + p.pw - j * dw;
+        if (wn < 0 || wn % sw) continue;
+        const int q = wn / sw;
         if (q >= p.Q) continue;
-        const uint32_t local = i * p.kw + j;
+        const uint32_t local = i * kw + j;
         const size_t o = ((static_cast<size_t>(n) * p.P + pp) * p.Q + q) * cg + g;
         const uint32_t r = __ldg(nib + o);
         const float4* src = reinterpret_cast<const float4*>(dy + o * 8);
@@ -271,8 +285,15 @@ int mb_maxpool2d_fwd(const float* x, float* y, uint8_t* nibbles, const mb_pool_d
   if (d->layout == MB_NHWC && p.C % 8 == 0 && aligned(x, 16) && aligned(y, 32) &&
       aligned(nibbles, 4)) {
     const size_t total = total_out / 8;
-    maxpool_fwd_nhwc8<<<grid_for(total, 256, 8), 256, 0, as_stream(stream)>>>(
-        x, y, reinterpret_cast<uint32_t*>(nibbles), p, total);
+    uint32_t* nw = reinterpret_cast<uint32_t*>(nibbles);
+    const int grid = grid_for(total, 256, 8);
+    const bool unit_dil = p.dh == 1 && p.dw == 1;
+    if (unit_dil && p.kh == 3 && p.kw == 3)
+      maxpool_fwd_nhwc8<3, 3><<<grid, 256, 0, as_stream(stream)>>>(x, y, nw, p, total);
+    else if (unit_dil && p.kh == 2 && p.kw == 2)
+      maxpool_fwd_nhwc8<2, 2><<<grid, 256, 0, as_stream(stream)>>>(x, y, nw, p, total);
+    else
+      maxpool_fwd_nhwc8<0, 0><<<grid, 256, 0, as_stream(stream)>>>(x, y, nw, p, total);
     return after_launch("maxpool_fwd_nhwc8");
   }
   const size_t pairs = (total_out + 1) / 2;
@@ -294,8 +315,15 @@ int mb_maxpool2d_bwd(const float* dy, const uint8_t* nibbles, float* dx, const m
   if (d->layout == MB_NHWC && p.C % 8 == 0 && aligned(dy, 16) && aligned(dx, 32) &&
       aligned(nibbles, 4)) {
     const size_t total = total_in / 8;
-    maxpool_bwd_nhwc8<<<grid_for(total, 256, 8), 256, 0, as_stream(stream)>>>(
-        dy, reinterpret_cast<const uint32_t*>(nibbles), dx, p, total);
+    const uint32_t* nw = reinterpret_cast<const uint32_t*>(nibbles);
+    const int grid = grid_for(total, 256, 8);
+    const bool unit_dil = p.dh == 1 && p.dw == 1;
+    if (unit_dil && p.kh == 3 && p.kw == 3 && p.sh == 2 && p.sw == 2)
+      maxpool_bwd_nhwc8<3, 3, 2, 2><<<grid, 256, 0, as_stream(stream)>>>(dy, nw, dx, p, total);
+    else if (unit_dil && p.kh == 2 && p.kw == 2 && p.sh == 2 && p.sw == 2)
+      maxpool_bwd_nhwc8<2, 2, 2, 2><<<grid, 256, 0, as_stream(stream)>>>(dy, nw, dx, p, total);
+    else
+      maxpool_bwd_nhwc8<0, 0, 0, 0><<<grid, 256, 0, as_stream(stream)>>>(dy, nw, dx, p, total);
     return after_launch("maxpool_bwd_nhwc8");
   }
   if (d->layout == MB_NHWC)
