@@ -177,7 +177,8 @@ int mb_bn_bwd_from_input(const float* dy, const float* x, const float* gamma,
 /* Fused forms.  The reference runs batch norm, the residual add and ReLU as
  * three operators (bn.py, funcs.py add, relu.py), i.e. three passes over the
  * activation; these do the same arithmetic in the batch-norm sweep.
- *   y = act(bn(x) + residual),  residual may be null, act = ReLU when relu != 0.
+ *   y = act(bn(x) + residual),  residual may be null; `relu` is the activation
+ *   code: 0 none, 1 ReLU, 2 ReLU6 (hardtanh.py's clamp to [0, 6]).
  * Same statistics, workspace and aliasing rules as mb_bn_fwd_train / _apply
  * (y may alias x or residual).                                                */
 int mb_bn_act_fwd_train(const float* x, const float* residual, int relu, const float* gamma,
@@ -191,6 +192,12 @@ int mb_bn_act_fwd_apply(const float* x, const float* residual, int relu, const f
  * (dy gated by y > 0) followed by cudnn_backward (lrbn.cpp:43-70) in one reduce
  * and one sweep.  The gate is re-evaluated from x with the forward's own
  * expression, so neither y nor a mask has to be kept.  dx may alias dy.       */
+/* The same with the activation code of the forward (1 ReLU, 2 ReLU6: the gate
+ * is 0 < z < 6, hardtanh.py's backward).                                       */
+int mb_bn_act_bwd_from_input(const float* dy, const float* x, const float* gamma, const float* beta,
+                             const float* save_mean, const float* save_invstd, int act, float* dx,
+                             float* dgamma, float* dbeta, const mb_bn_desc* d, void* workspace,
+                             size_t workspace_bytes, void* stream);
 int mb_bn_relu_bwd_from_input(const float* dy, const float* x, const float* gamma,
                               const float* beta, const float* save_mean, const float* save_invstd,
                               float* dx, float* dgamma, float* dbeta, const mb_bn_desc* d,

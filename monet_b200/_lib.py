@@ -71,6 +71,7 @@ PROTOTYPES = {
     "mb_bn_act_fwd_train": (C.c_int, [c_f, c_f, C.c_int] + [c_f] * 7 + [C.POINTER(BnDesc), c_f, c_sz, c_f]),
     "mb_bn_act_fwd_apply": (C.c_int, [c_f, c_f, C.c_int] + [c_f] * 5 + [C.POINTER(BnDesc), c_f]),
     "mb_bn_add_relu_bwd": (C.c_int, [c_f] * 11 + [C.POINTER(BnDesc), c_f, c_sz, c_f]),
+    "mb_bn_act_bwd_from_input": (C.c_int, [c_f] * 6 + [C.c_int] + [c_f] * 3 + [C.POINTER(BnDesc), c_f, c_sz, c_f]),
     "mb_bn_relu_bwd_from_input": (C.c_int, [c_f] * 9 + [C.POINTER(BnDesc), c_f, c_sz, c_f]),
     "mb_softmax_fwd": (C.c_int, [c_f, c_f, c_sz, C.c_int, c_sz, C.c_int, c_f]),
     "mb_softmax_bwd": (C.c_int, [c_f, c_f, c_f, c_sz, C.c_int, c_sz, C.c_int, c_f]),

@@ -111,7 +111,8 @@ __global__ void __launch_bounds__(kBlock) bn_reduce_nhwc(const float* __restrict
                                                          int C, size_t M, int S, int tx_n,
                                                          int ty_n, const float* a2 = nullptr,
                                                          const float* act = nullptr,
-                                                         float* dout = nullptr) {
+                                                         float* dout = nullptr,
+                                                         float act_hi = __builtin_huge_valf()) {
   extern __shared__ float sm[];  // [ty_n][tx_n][2*VEC]
   const int tx = threadIdx.x % tx_n, ty = threadIdx.x / tx_n;
   const int c0 = (blockIdx.y * tx_n + tx) * VEC;
@@ -178,7 +179,10 @@ __global__ void __launch_bounds__(kBlock) bn_reduce_nhwc(const float* __restrict
               s2[k] = fmaf(dlt, dlt, s2[k]);
             } else {
               float d = uu[k];
-              if (MODE == kBwdRelu) d = fmaf(ww[k] - p0[k], pg[k], pb[k]) > 0.f ? d : 0.f;
+              if (MODE == kBwdRelu) {
+                const float z = fmaf(ww[k] - p0[k], pg[k], pb[k]);
+                d = (z > 0.f && z < act_hi) ? d : 0.f;
+              }
               s1[k] += d;
               s2[k] = fmaf(d, (ww[k] - p0[k]) * p1[k], s2[k]);
             }
@@ -203,7 +207,10 @@ __global__ void __launch_bounds__(kBlock) bn_reduce_nhwc(const float* __restrict
         } else {
           const float ww = __ldg(b + off + k);
           float d = uu;
-          if (MODE == kBwdRelu) d = fmaf(ww - p0[k], pg[k], pb[k]) > 0.f ? d : 0.f;
+          if (MODE == kBwdRelu) {
+            const float z = fmaf(ww - p0[k], pg[k], pb[k]);
+            d = (z > 0.f && z < act_hi) ? d : 0.f;
+          }
           s1[k] += d;
           s2[k] = fmaf(d, (ww - p0[k]) * p1[k], s2[k]);
         }
@@ -250,7 +257,8 @@ __global__ void __launch_bounds__(kBlock) bn_reduce_nchw(const float* __restrict
                                                          int C, int HW, size_t M, int S,
                                                          const float* a2 = nullptr,
                                                          const float* act = nullptr,
-                                                         float* dout = nullptr) {
+                                                         float* dout = nullptr,
+                                                         float act_hi = __builtin_huge_valf()) {
   __shared__ float red[2][kBlock / 32];
   const int c = blockIdx.x;
   float p0, p1 = 1.f, pg = 0.f, pb = 0.f;
@@ -286,7 +294,10 @@ __global__ void __launch_bounds__(kBlock) bn_reduce_nchw(const float* __restrict
     } else {
       const float w = __ldg(b + off);
       float d = u;
-      if (MODE == kBwdRelu) d = fmaf(w - p0, pg, pb) > 0.f ? d : 0.f;
+      if (MODE == kBwdRelu) {
+        const float z = fmaf(w - p0, pg, pb);
+        d = (z > 0.f && z < act_hi) ? d : 0.f;
+      }
       s1 += d;
       s2 = fmaf(d, (w - p0) * p1, s2);
     }
@@ -388,6 +399,7 @@ struct SweepConst {
   int p1_is_gamma;
   const float* k12;     // bwd: [2][C]
   int relu;             // fwd modes: clamp the result at zero
+  float act_hi;         // upper clamp of the activation (+inf: ReLU, 6: ReLU6)
 };
 
 template <int MODE>
@@ -412,13 +424,16 @@ __device__ __forceinline__ void load_const(const SweepConst& k, int c, int C, fl
 
 template <int MODE>
 __device__ __forceinline__ float sweep1(float a, float b, float q0, float q1, float q2, float q3,
-                                        float q4, float q5, int relu) {
+                                        float q4, float q5, int relu, float hi) {
   if (MODE == kFwd || MODE == kFwdRes) {
     float z = fmaf(a - q0, q1, q2);
     if (MODE == kFwdRes) z += b;
-    return relu ? (z > 0.f ? z : (z != z ? z : 0.f)) : z;   // NaN passes through, as in ReLU
+    return relu ? (z > 0.f ? fminf(z, hi) : (z != z ? z : 0.f)) : z;   // NaN passes through, as in ReLU
   }
-  if (MODE == kBwdRelu) a = fmaf(b - q0, q4, q5) > 0.f ? a : 0.f;
+  if (MODE == kBwdRelu) {
+    const float z = fmaf(b - q0, q4, q5);
+    a = (z > 0.f && z < hi) ? a : 0.f;
+  }
   const float xhat = (b - q0) * q1;
   return (a - xhat * q3 - q2) * q4;
 }
@@ -434,6 +449,7 @@ __global__ void __launch_bounds__(kBlock) bn_sweep_nhwc(const float* a, const fl
 #pragma unroll
   for (int i = 0; i < VEC; ++i) load_const<MODE>(k, c0 + i, C, q0[i], q1[i], q2[i], q3[i], q4[i], q5[i]);
   const int relu = k.relu;
+  const float hi = k.act_hi;
   const size_t step = static_cast<size_t>(gridDim.x) * ty_n;
   size_t r = static_cast<size_t>(blockIdx.x) * ty_n + ty;
   if (VEC == 4) {
@@ -448,10 +464,10 @@ __global__ void __launch_bounds__(kBlock) bn_sweep_nhwc(const float* a, const fl
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         float4 o;
-        o.x = sweep1<MODE>(u[i].x, w[i].x, q0[0], q1[0], q2[0], q3[0], q4[0], q5[0], relu);
-        o.y = sweep1<MODE>(u[i].y, w[i].y, q0[1], q1[1], q2[1], q3[1], q4[1], q5[1], relu);
-        o.z = sweep1<MODE>(u[i].z, w[i].z, q0[2], q1[2], q2[2], q3[2], q4[2], q5[2], relu);
-        o.w = sweep1<MODE>(u[i].w, w[i].w, q0[3], q1[3], q2[3], q3[3], q4[3], q5[3], relu);
+        o.x = sweep1<MODE>(u[i].x, w[i].x, q0[0], q1[0], q2[0], q3[0], q4[0], q5[0], relu, hi);
+        o.y = sweep1<MODE>(u[i].y, w[i].y, q0[1], q1[1], q2[1], q3[1], q4[1], q5[1], relu, hi);
+        o.z = sweep1<MODE>(u[i].z, w[i].z, q0[2], q1[2], q2[2], q3[2], q4[2], q5[2], relu, hi);
+        o.w = sweep1<MODE>(u[i].w, w[i].w, q0[3], q1[3], q2[3], q3[3], q4[3], q5[3], relu, hi);
         *reinterpret_cast<float4*>(out + (r + i * step) * C + c0) = o;
       }
     }
@@ -462,7 +478,7 @@ __global__ void __launch_bounds__(kBlock) bn_sweep_nhwc(const float* a, const fl
     for (int i = 0; i < VEC; ++i) {
       const float u = a[off + i];
       const float w = MODE != kFwd ? b[off + i] : 0.f;
-      out[off + i] = sweep1<MODE>(u, w, q0[i], q1[i], q2[i], q3[i], q4[i], q5[i], relu);
+      out[off + i] = sweep1<MODE>(u, w, q0[i], q1[i], q2[i], q3[i], q4[i], q5[i], relu, hi);
     }
   }
 }
@@ -478,9 +494,12 @@ __global__ void __launch_bounds__(kBlock) bn_sweep_nchw(const float* a, const fl
   for (int i = blockIdx.y * kBlock + threadIdx.x; i < HW; i += gridDim.y * kBlock) {
     const float u = a[base + i];
     const float w = MODE != kFwd ? b[base + i] : 0.f;
-    out[base + i] = sweep1<MODE>(u, w, q0, q1, q2, q3, q4, q5, k.relu);
+    out[base + i] = sweep1<MODE>(u, w, q0, q1, q2, q3, q4, q5, k.relu, k.act_hi);
   }
 }
+
+// activation code of the fused entries: 0 none, 1 ReLU, 2 ReLU6
+float act_upper(int act) { return act == 2 ? 6.f : __builtin_huge_valf(); }
 
 int check(const char* who, const mb_bn_desc* d) {
   if (!d) return fail(MB_ERR_INVALID_ARGUMENT, "%s: null descriptor", who);
@@ -495,17 +514,18 @@ template <int MODE>
 int run_reduce(const char* who, const mb_bn_desc* d, const Geometry& g, const float* a,
                const float* b, const float* p0v, const float* p1v, int p1_is_gamma, float* ws,
                cudaStream_t st, const float* gv = nullptr, const float* bv = nullptr,
-               const float* a2 = nullptr, const float* act = nullptr, float* dout = nullptr) {
+               const float* a2 = nullptr, const float* act = nullptr, float* dout = nullptr,
+               float act_hi = __builtin_huge_valf()) {
   if (d->layout == MB_NHWC) {
     dim3 grid(g.S, g.slabs);
     const size_t smem = static_cast<size_t>(kBlock) * 2 * g.vec * sizeof(float);
     if (g.vec == 4)
-      bn_reduce_nhwc<MODE, 4><<<grid, kBlock, smem, st>>>(a, b, p0v, p1v, p1_is_gamma, gv, bv, ws, g.C, g.M, g.S, g.tx, g.ty, a2, act, dout);
+      bn_reduce_nhwc<MODE, 4><<<grid, kBlock, smem, st>>>(a, b, p0v, p1v, p1_is_gamma, gv, bv, ws, g.C, g.M, g.S, g.tx, g.ty, a2, act, dout, act_hi);
     else
-      bn_reduce_nhwc<MODE, 1><<<grid, kBlock, smem, st>>>(a, b, p0v, p1v, p1_is_gamma, gv, bv, ws, g.C, g.M, g.S, g.tx, g.ty, a2, act, dout);
+      bn_reduce_nhwc<MODE, 1><<<grid, kBlock, smem, st>>>(a, b, p0v, p1v, p1_is_gamma, gv, bv, ws, g.C, g.M, g.S, g.tx, g.ty, a2, act, dout, act_hi);
   } else {
     dim3 grid(g.C, g.S);
-    bn_reduce_nchw<MODE><<<grid, kBlock, 0, st>>>(a, b, p0v, p1v, p1_is_gamma, gv, bv, ws, g.C, g.HW, g.M, g.S, a2, act, dout);
+    bn_reduce_nchw<MODE><<<grid, kBlock, 0, st>>>(a, b, p0v, p1v, p1_is_gamma, gv, bv, ws, g.C, g.HW, g.M, g.S, a2, act, dout, act_hi);
   }
   return after_launch(who);
 }
@@ -545,7 +565,8 @@ int check_alignment(const char* who, const mb_bn_desc* d, const void* p0, const 
 int bwd_common(const char* who, const float* dy, const float* v, const float* gamma,
                const float* p0v, const float* p1v, int p1_is_gamma, const float* invstd, float* dx,
                float* dgamma, float* dbeta, const mb_bn_desc* d, void* workspace,
-               size_t workspace_bytes, void* stream, const float* relu_beta = nullptr) {
+               size_t workspace_bytes, void* stream, const float* relu_beta = nullptr,
+               float act_hi = __builtin_huge_valf()) {
   int rc = check(who, d);
   if (rc) return rc;
   if (!dy || !v || !gamma || !p0v || !p1v || !invstd || !dx || !dgamma || !dbeta)
@@ -560,7 +581,8 @@ int bwd_common(const char* who, const float* dy, const float* v, const float* ga
   float* ws_const = ws + 2 * static_cast<size_t>(g.S) * g.C;
   cudaStream_t st = as_stream(stream);
   if (relu_beta)
-    rc = run_reduce<kBwdRelu>("bn_relu_bwd_reduce", d, g, dy, v, p0v, p1v, 0, ws, st, gamma, relu_beta);
+    rc = run_reduce<kBwdRelu>("bn_relu_bwd_reduce", d, g, dy, v, p0v, p1v, 0, ws, st, gamma, relu_beta,
+                              nullptr, nullptr, nullptr, act_hi);
   else
     rc = run_reduce<kBwd>("bn_bwd_reduce", d, g, dy, v, p0v, p1v, p1_is_gamma, ws, st);
   if (rc) return rc;
@@ -568,7 +590,7 @@ int bwd_common(const char* who, const float* dy, const float* v, const float* ga
                                                     0.f, nullptr, nullptr, dgamma, dbeta);
   rc = after_launch("bn_bwd_finalize");
   if (rc) return rc;
-  SweepConst k{gamma, relu_beta, nullptr, invstd, p0v, p1v, p1_is_gamma, ws_const, 0};
+  SweepConst k{gamma, relu_beta, nullptr, invstd, p0v, p1v, p1_is_gamma, ws_const, 0, act_hi};
   if (relu_beta) return run_sweep<kBwdRelu>("bn_relu_bwd_sweep", d, g, dy, v, dx, k, st);
   return run_sweep<kBwd>("bn_bwd_sweep", d, g, dy, v, dx, k, st);
 }
@@ -610,7 +632,7 @@ static int fwd_train_impl(const char* who, const float* x, const float* residual
                                                     running_var, save_mean, save_invstd);
   rc = after_launch("bn_fwd_finalize");
   if (rc) return rc;
-  SweepConst k{gamma, beta, save_mean, save_invstd, nullptr, nullptr, 0, nullptr, relu ? 1 : 0};
+  SweepConst k{gamma, beta, save_mean, save_invstd, nullptr, nullptr, 0, nullptr, relu ? 1 : 0, act_upper(relu)};
   if (residual) return run_sweep<kFwdRes>("bn_act_fwd_sweep", d, g, x, residual, y, k, st);
   return run_sweep<kFwd>("bn_fwd_sweep", d, g, x, nullptr, y, k, st);
 }
@@ -625,7 +647,7 @@ static int fwd_apply_impl(const char* who, const float* x, const float* residual
   rc = check_alignment(who, d, x, y, residual ? residual : y);
   if (rc) return rc;
   Geometry g = make_geometry(d);
-  SweepConst k{gamma, beta, mean, invstd, nullptr, nullptr, 0, nullptr, relu ? 1 : 0};
+  SweepConst k{gamma, beta, mean, invstd, nullptr, nullptr, 0, nullptr, relu ? 1 : 0, act_upper(relu)};
   if (residual) return run_sweep<kFwdRes>("bn_act_fwd_sweep", d, g, x, residual, y, k, as_stream(stream));
   return run_sweep<kFwd>("bn_fwd_sweep", d, g, x, nullptr, y, k, as_stream(stream));
 }
@@ -683,8 +705,19 @@ int mb_bn_add_relu_bwd(const float* dy1, const float* dy2, const float* y, const
                                                     0.f, nullptr, nullptr, dgamma, dbeta);
   rc = after_launch("bn_bwd_finalize");
   if (rc) return rc;
-  SweepConst k{gamma, nullptr, nullptr, save_invstd, save_mean, save_invstd, 0, ws_const, 0};
+  SweepConst k{gamma, nullptr, nullptr, save_invstd, save_mean, save_invstd, 0, ws_const, 0, __builtin_huge_valf()};
   return run_sweep<kBwd>("bn_bwd_sweep", desc, g, d, x, dx, k, st);
+}
+
+int mb_bn_act_bwd_from_input(const float* dy, const float* x, const float* gamma, const float* beta,
+                             const float* save_mean, const float* save_invstd, int act, float* dx,
+                             float* dgamma, float* dbeta, const mb_bn_desc* d, void* workspace,
+                             size_t workspace_bytes, void* stream) {
+  if (act != 1 && act != 2)
+    return fail(MB_ERR_INVALID_ARGUMENT, "mb_bn_act_bwd_from_input: activation must be 1 (ReLU) or 2 (ReLU6)");
+  if (!beta) return fail(MB_ERR_INVALID_ARGUMENT, "mb_bn_act_bwd_from_input: null pointer");
+  return bwd_common("mb_bn_act_bwd_from_input", dy, x, gamma, save_mean, save_invstd, 0, save_invstd,
+                    dx, dgamma, dbeta, d, workspace, workspace_bytes, stream, beta, act_upper(act));
 }
 
 int mb_bn_relu_bwd_from_input(const float* dy, const float* x, const float* gamma,

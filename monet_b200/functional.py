@@ -379,7 +379,7 @@ def bn_act_fwd_train(x, residual, relu, gamma, beta, running_mean, running_var, 
     save_invstd = torch.empty(d.C, dtype=torch.float32, device=x.device)
     ws = _bn_workspace(d, x.device)
     check(lib().mb_bn_act_fwd_train(
-        xd.data_ptr(), rd.data_ptr() if rd is not None else None, 1 if relu else 0,
+        xd.data_ptr(), rd.data_ptr() if rd is not None else None, int(relu),
         gamma.data_ptr(), beta.data_ptr(),
         running_mean.data_ptr() if running_mean is not None else None,
         running_var.data_ptr() if running_var is not None else None,
@@ -400,14 +400,15 @@ def bn_act_fwd_apply(x, residual, relu, gamma, beta, mean, invstd, inplace=False
             raise RuntimeError("monet_b200 batch norm: residual shape mismatch")
     y = xd if (inplace and xd is x) else torch.empty_like(xd)
     check(lib().mb_bn_act_fwd_apply(
-        xd.data_ptr(), rd.data_ptr() if rd is not None else None, 1 if relu else 0,
+        xd.data_ptr(), rd.data_ptr() if rd is not None else None, int(relu),
         gamma.data_ptr(), beta.data_ptr(), mean.data_ptr(), invstd.data_ptr(), y.data_ptr(),
         C.byref(d), _stream()), "bn_act_fwd_apply")
     return y
 
 
-def bn_relu_bwd_from_input(dy, x, gamma, beta, save_mean, save_invstd, inplace=False):
-    """(dx, dgamma, dbeta) through y = relu(bn(x)), gate re-evaluated from x."""
+def bn_relu_bwd_from_input(dy, x, gamma, beta, save_mean, save_invstd, inplace=False, act: int = 1):
+    """(dx, dgamma, dbeta) through y = act(bn(x)), gate re-evaluated from x; act 1 = ReLU,
+    2 = ReLU6."""
     _need_cuda(dy, x, gamma, beta, save_mean, save_invstd); _f32(dy, "dy"); _f32(x, "x")
     sd = _bn_dense(x)
     dyd = like(sd, dy) if sd.dim() == 4 else dy.contiguous()
@@ -418,10 +419,10 @@ def bn_relu_bwd_from_input(dy, x, gamma, beta, save_mean, save_invstd, inplace=F
     dgamma = torch.empty(d.C, dtype=torch.float32, device=dy.device)
     dbeta = torch.empty(d.C, dtype=torch.float32, device=dy.device)
     ws = _bn_workspace(d, dy.device)
-    check(lib().mb_bn_relu_bwd_from_input(
+    check(lib().mb_bn_act_bwd_from_input(
         dyd.data_ptr(), sd.data_ptr(), gamma.data_ptr(), beta.data_ptr(), save_mean.data_ptr(),
-        save_invstd.data_ptr(), dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), C.byref(d),
-        ws.data_ptr(), ws.numel(), _stream()), "bn_relu_bwd_from_input")
+        save_invstd.data_ptr(), int(act), dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(),
+        C.byref(d), ws.data_ptr(), ws.numel(), _stream()), "bn_act_bwd_from_input")
     return dx, dgamma, dbeta
 
 

@@ -5,8 +5,8 @@ The reference has no such operators: its graph runs ``aten::batch_norm``, ``aten
 over the activation.  On a B200 those passes are pure HBM traffic, so the element-wise tail
 is folded into the batch-norm sweep.  They follow the same protocol (``backward_storage``,
 ``params`` carried to later instances of the node, ``inplace``) and register under node
-names of their own, ``monet::batch_norm_relu``, ``monet::batch_norm_add_relu`` and
-``monet::add_relu``, so the slot order of the reference's names is untouched; a graph
+names of their own, ``monet::batch_norm_relu`` (and ``_relu6``),
+``monet::batch_norm_add_relu`` and ``monet::add_relu``, so the slot order of the reference's names is untouched; a graph
 rewriter (``runner.fuse_graph``) produces those nodes from the unfused pattern.
 
 Argument order = the batch-norm node's arguments, then the residual:
@@ -69,10 +69,17 @@ class InputActBatchNormReLU(_FusedBatchNorm):
             if not training:
                 raise NotImplementedError("batch-norm backward in eval mode")
             dx, dw, db = F.bn_relu_bwd_from_input(grad_output, input_, weight, bias, save_mean,
-                                                  save_invstd, inplace=True)
+                                                  save_invstd, inplace=True, act=int(self.relu))
             if not nodel:
                 del stored[4], stored[3], stored[2], stored[1], stored[0]
             return dx, dw, db, None, None
+
+
+@implements(['monet::batch_norm_relu6'], COMMON_MODES)
+class InputActBatchNormReLU6(InputActBatchNormReLU):
+    """y = clamp(bn(x), 0, 6) (MobileNetV2's batch norm + ReLU6); the gate 0 < z < 6 is
+    re-evaluated from x in the backward."""
+    relu = 2
 
 
 @implements(['monet::batch_norm_add_relu'], COMMON_MODES)

@@ -150,6 +150,7 @@ def fuse_graph(nodes: List[Node], out_id: int) -> Tuple[List[Node], int]:
     """Rewrites the element-wise tails of batch norm into fused nodes:
 
     * ``batch_norm -> relu``                 => ``monet::batch_norm_relu`` (at the batch norm);
+    * ``batch_norm -> hardtanh(0, 6)``       => ``monet::batch_norm_relu6``;
     * ``batch_norm -> add(., r) -> relu``    => ``monet::batch_norm_add_relu`` with ``r`` appended
       to the batch-norm arguments, placed where the add was (``r`` may be produced after the
       batch norm, e.g. by a downsample branch);
@@ -178,6 +179,11 @@ def fuse_graph(nodes: List[Node], out_id: int) -> Tuple[List[Node], int]:
             continue
         if u.op in relus:
             n.op = 'monet::batch_norm_relu'
+            removed.add(u.id)
+            alias[u.id] = n.id
+        elif (u.op in ('aten::hardtanh', 'aten::hardtanh_') and float(u.args[1].value) == 0.0
+              and float(u.args[2].value) == 6.0):
+            n.op = 'monet::batch_norm_relu6'
             removed.add(u.id)
             alias[u.id] = n.id
         elif plain_add(u):
@@ -253,7 +259,7 @@ def low_memory(nodes: List[Node], n: Node) -> Choice:
         return Choice(impl=0, inplace=False, recompute=True)
     if n.op == 'aten::max_pool2d':
         return Choice(impl=1)
-    if n.op == 'monet::batch_norm_relu':
+    if n.op in ('monet::batch_norm_relu', 'monet::batch_norm_relu6'):
         return Choice(recompute=True)      # keeps x only; y = relu(bn(x)) is rebuilt from it
     return Choice()
 

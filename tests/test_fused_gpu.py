@@ -92,6 +92,37 @@ def test_bn_relu_backward(cuda, shape, nhwc):
 
 @pytest.mark.parametrize("shape", SHAPES)
 @pytest.mark.parametrize("nhwc", [False, True])
+def test_bn_relu6(cuda, shape, nhwc):
+    """Batch norm + ReLU6 (activation code 2): forward = bn.py then hardtanh.py's clamp to [0, 6],
+    backward gate 0 < z < 6 re-evaluated from x; bit-identical to the separate operators."""
+    from monet_b200 import functional as F
+    x, gamma, beta, rm, rv, _, dy = _data(shape, seed=4)
+    gamma = gamma * 4.0                                    # so that a good part exceeds 6
+    xg, dyg = _fmt(x.to(cuda), nhwc), _fmt(dy.to(cuda), nhwc)
+    gg, bg = gamma.to(cuda), beta.to(cuda)
+    ref_y, ref_mean, ref_invstd, _, _ = oracle.bn_forward_train(x, gamma, beta, rm, rv, 0.1, 1e-5)
+    ref_y = ref_y.clamp(0.0, 6.0)
+    y, mean, invstd = F.bn_act_fwd_train(xg, None, 2, gg, bg, None, None, 0.1, 1e-5)
+    assert torch.allclose(y.cpu(), ref_y, rtol=RTOL, atol=1e-5)
+    if y.numel() >= 1000:                                  # both clamps are exercised
+        assert float((y == 6).float().mean()) > 0.01 and float((y == 0).float().mean()) > 0.01
+    z, _, _ = F.bn_fwd_train(xg, gg, bg, None, None, 0.1, 1e-5)
+    assert torch.equal(y, F.hardtanh(z, 0.0, 6.0))
+    assert torch.equal(F.bn_act_fwd_apply(xg, None, 2, gg, bg, mean, invstd), y)
+    gate = ((y > 0) & (y < 6)).cpu()
+    ref_dx, ref_dg, ref_db = oracle.bn_relu_backward_from_input(dy, gate, x, gamma, 1e-5)
+    scale = max(1.0, float(ref_dx.abs().max()))
+    dx, dg, db = F.bn_relu_bwd_from_input(dyg, xg, gg, bg, mean, invstd, act=2)
+    assert torch.allclose(dx.cpu(), ref_dx, rtol=RTOL, atol=1e-5 * scale)
+    assert torch.allclose(dg.cpu(), ref_dg, rtol=1e-4, atol=1e-4 * max(1.0, float(ref_dg.abs().max())))
+    assert torch.allclose(db.cpu(), ref_db, rtol=1e-4, atol=1e-4)
+    d = F.hardtanh_bwd(dyg, z, 0.0, 6.0)
+    dx2, dg2, db2 = F.bn_bwd_from_input(d, xg, gg, mean, invstd)
+    assert torch.equal(dx, dx2) and torch.equal(dg, dg2) and torch.equal(db, db2)
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("nhwc", [False, True])
 @pytest.mark.parametrize("pair", [False, True])
 def test_bn_add_relu_backward(cuda, shape, nhwc, pair):
     """Backward through y = relu(bn(x) + r) with the gate folded into the batch-norm reduce."""
@@ -240,6 +271,35 @@ def test_fused_network_equals_unfused(cuda, policy):
     assert torch.equal(o0, o1)
     for k in s0:
         assert torch.equal(s0[k], s1[k]), k
+    for k in g0:
+        scale = float(g0[k].abs().max()) + 1e-12
+        assert float((g0[k] - g1[k]).abs().max()) <= 1e-4 * scale, k
+
+
+def test_mobilenet_fused_equals_unfused(cuda):
+    """MobileNetV2 (depthwise convolutions, ReLU6): the graph with batch_norm_relu6 nodes gives
+    the logits of the unfused graph bit for bit."""
+    import torchvision
+    from monet_b200 import runner
+    torch.manual_seed(0)
+    model = torchvision.models.mobilenet_v2(num_classes=10).to(cuda).to(memory_format=torch.channels_last)
+    model.train()
+    x = torch.randn(4, 3, 64, 64, device=cuda)
+    gout = torch.randn(4, 10, device=cuda)
+    state = {k: v.clone() for k, v in model.state_dict().items()}
+    results = []
+    for fuse in (False, True):
+        model.load_state_dict(state)
+        for p in model.parameters():
+            p.grad = None
+        run = runner.Runner(model, runner.low_memory, fuse=fuse)
+        if fuse:
+            assert sum(n.op == 'monet::batch_norm_relu6' for n in run.nodes) == 35
+        out = run.forward(x)
+        run.backward(gout.clone())
+        results.append((out.clone(), {k: p.grad.clone() for k, p in model.named_parameters()}))
+    (o0, g0), (o1, g1) = results
+    assert torch.equal(o0, o1)
     for k in g0:
         scale = float(g0[k].abs().max()) + 1e-12
         assert float((g0[k] - g1[k]).abs().max()) <= 1e-4 * scale, k
