@@ -54,6 +54,7 @@ def parse():
 MICRO = {
     "fprop3x3_c64": ("fprop", 64, 56, 64, 3, 1, 1), "dgrad3x3_c64": ("dgrad", 64, 56, 64, 3, 1, 1),
     "wgrad3x3_c64": ("wgrad", 64, 56, 64, 3, 1, 1), "wgrad3x3_c128": ("wgrad", 128, 28, 128, 3, 1, 1),
+    "fprop3x3_c128": ("fprop", 128, 28, 128, 3, 1, 1), "dgrad3x3_c128": ("dgrad", 128, 28, 128, 3, 1, 1),
     "fprop3x3_c256": ("fprop", 256, 14, 256, 3, 1, 1), "wgrad3x3_c256": ("wgrad", 256, 14, 256, 3, 1, 1),
     "fprop1x1_c64_k256": ("fprop", 64, 56, 256, 1, 1, 0), "dgrad1x1_c64_k256": ("dgrad", 64, 56, 256, 1, 1, 0),
     "wgrad1x1_c64_k256": ("wgrad", 64, 56, 256, 1, 1, 0), "fprop1x1_c1024_k256": ("fprop", 1024, 14, 256, 1, 1, 0),
