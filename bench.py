@@ -270,10 +270,10 @@ def family_costs(runner_obj, batch_shape):
 # capture under ncu, and every one of these kernels streams its operands once, so the traffic
 # of a step's launches is taken to grow in proportion to their algorithmic bytes.
 TRAFFIC_RATIO = {
-    "mb_conv2d_fprop": 679.8 / 738.7, "mb_conv2d_dgrad": 720.5 / 738.7, "mb_conv2d_wgrad": 742.9 / 738.7,
+    "mb_conv2d_fprop": 679.8 / 738.7, "mb_conv2d_dgrad": 719.8 / 738.7, "mb_conv2d_wgrad": 742.9 / 738.7,
     "mb_bn_bwd_from_output": 1740.8 / 1772.0, "mb_bn_bwd_from_input": 1740.8 / 1772.0,
     "mb_bn_relu_bwd_from_input": (1188.5 + 1743.9) / (1182.0 + 1772.0),
-    "mb_bn_add_relu_bwd": (1188.5 + 1743.9) / (1182.0 + 1772.0),
+    "mb_bn_add_relu_bwd": (2903.3 + 1743.9) / (2954.0 + 1772.0),
     "mb_bn_fwd_train": 594.7 / 591.0, "mb_bn_act_fwd_train": (594.7 + 1136.9) / (591.0 + 1182.0),
     "mb_relu_fwd": 1136.5 / 1182.0, "mb_relu_bwd_act": 1744.0 / 1772.0, "mb_relu_bwd_act2": 2333.9 / 2363.0,
     "mb_add_fwd": 1743.8 / 1772.0, "mb_maxpool2d_bwd": 710.5 / 756.0,
