@@ -82,10 +82,114 @@ __global__ void __launch_bounds__(256) dw_dgrad(const float* __restrict__ dy, co
   }
 }
 
+
+// ---------------------------------------------------------------- 3x3 specialisations
+// MobileNetV2's depthwise layers are all 3x3, dilation 1, stride 1 or 2.  With the filter
+// shape and the stride fixed at compile time the tap loops unroll, the divisions by the
+// stride disappear, and one thread produces kTw consecutive output pixels of a row: the
+// 3 x ((kTw-1)*STRIDE + 3) input columns it needs are loaded once and shared by its outputs
+// (4.5 instead of 9 loads per output at stride 1).  A warp still walks the channel groups
+// first, so every load instruction covers contiguous runs of 4*32 channels.
+constexpr int kTw = 4;
+
+__device__ __forceinline__ void fma4(float4& acc, const float4& a, const float4& f) {
+  acc.x = fmaf(a.x, f.x, acc.x); acc.y = fmaf(a.y, f.y, acc.y);
+  acc.z = fmaf(a.z, f.z, acc.z); acc.w = fmaf(a.w, f.w, acc.w);
+}
+
+// y[n][pp][q] = sum_{r,s} x[n][pp*STRIDE - ph + r][q*STRIDE - pw + s] * f[r][s]   (FLIP: f[2-r][2-s])
+// `p.H, p.W` are the extents of the tensor read, `p.P, p.Q` of the tensor written, so the same
+// kernel is the stride-1 backward-data pass when it reads dy with the flipped filter and the
+// padding 2 - pad.
+template <int STRIDE, bool FLIP>
+__global__ void __launch_bounds__(256) dw3x3_tiled(const float* __restrict__ x, const float* __restrict__ w,
+                                                   const float* __restrict__ bias, float* __restrict__ y,
+                                                   DwP p, int qtiles, size_t total) {
+  constexpr int kCols = (kTw - 1) * STRIDE + 3;
+  const int cg = p.C / 4;
+  for (size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
+       t += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const int g = static_cast<int>(t % cg);
+    size_t rest = t / cg;
+    const int qt = static_cast<int>(rest % qtiles);
+    rest /= qtiles;
+    const int pp = static_cast<int>(rest % p.P);
+    const int n = static_cast<int>(rest / p.P);
+    const int q0 = qt * kTw;
+    float4 f[9];
+#pragma unroll
+    for (int i = 0; i < 9; ++i)
+      f[i] = __ldg(reinterpret_cast<const float4*>(w + static_cast<size_t>(FLIP ? 8 - i : i) * p.C) + g);
+    float4 acc[kTw];
+    const float4 b0 = bias ? __ldg(reinterpret_cast<const float4*>(bias) + g) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int j = 0; j < kTw; ++j) acc[j] = b0;
+    const float* xn = x + static_cast<size_t>(n) * p.H * p.W * p.C + g * 4;
+    const int w0 = q0 * STRIDE - p.pw;
+#pragma unroll
+    for (int r = 0; r < 3; ++r) {
+      const int h = pp * STRIDE - p.ph + r;
+      if (h < 0 || h >= p.H) continue;
+      const float* xr = xn + static_cast<size_t>(h) * p.W * p.C;
+      float4 col[kCols];
+#pragma unroll
+      for (int c = 0; c < kCols; ++c) {
+        const int ww = w0 + c;
+        col[c] = (ww >= 0 && ww < p.W) ? __ldg(reinterpret_cast<const float4*>(xr + static_cast<size_t>(ww) * p.C))
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < kTw; ++j)
+#pragma unroll
+        for (int sidx = 0; sidx < 3; ++sidx) fma4(acc[j], col[j * STRIDE + sidx], f[r * 3 + sidx]);
+    }
+    float4* yo = reinterpret_cast<float4*>(y + ((static_cast<size_t>(n) * p.P + pp) * p.Q + q0) * p.C) + g;
+#pragma unroll
+    for (int j = 0; j < kTw; ++j)
+      if (q0 + j < p.Q) yo[static_cast<size_t>(j) * cg] = acc[j];
+  }
+}
+
+// Stride-2 backward-data, 3x3: thread = input pixel x 4 channels; only the taps whose parity
+// matches reach an output pixel (2.25 of 9 on average), selected without divisions.
+__global__ void __launch_bounds__(256) dw3x3s2_dgrad(const float* __restrict__ dy, const float* __restrict__ w,
+                                                     float* __restrict__ dx, DwP p, size_t total) {
+  const int cg = p.C / 4;
+  for (size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
+       t += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const int g = static_cast<int>(t % cg);
+    size_t pix = t / cg;
+    const int ww = static_cast<int>(pix % p.W);
+    pix /= p.W;
+    const int h = static_cast<int>(pix % p.H);
+    const int n = static_cast<int>(pix / p.H);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float* dn = dy + static_cast<size_t>(n) * p.P * p.Q * p.C + g * 4;
+#pragma unroll
+    for (int r = 0; r < 3; ++r) {
+      const int hn = h + p.ph - r;
+      if (hn < 0 || (hn & 1)) continue;
+      const int pp = hn >> 1;
+      if (pp >= p.P) continue;
+#pragma unroll
+      for (int sidx = 0; sidx < 3; ++sidx) {
+        const int wn = ww + p.pw - sidx;
+        if (wn < 0 || (wn & 1)) continue;
+        const int q = wn >> 1;
+        if (q >= p.Q) continue;
+        const float4 a = __ldg(reinterpret_cast<const float4*>(dn + (static_cast<size_t>(pp) * p.Q + q) * p.C));
+        const float4 f = __ldg(reinterpret_cast<const float4*>(w + static_cast<size_t>(r * 3 + sidx) * p.C) + g);
+        fma4(acc, a, f);
+      }
+    }
+    reinterpret_cast<float4*>(dx)[t] = acc;
+  }
+}
+
 // block = (tx channel groups of 4) x (ty row lanes); grid = (row chunks, channel slabs).
 // A "row" is one output pixel.  TAPS = R*S is a template parameter so that the per-tap
 // accumulators live in registers.
-template <int TAPS>
+template <int TAPS, int SW>
 __global__ void __launch_bounds__(256) dw_wgrad(const float* __restrict__ x, const float* __restrict__ dy,
                                                 float* __restrict__ dwt, float* __restrict__ db, DwP p,
                                                 size_t pixels, int chunks, int tx_n, int ty_n) {
@@ -111,7 +215,7 @@ __global__ void __launch_bounds__(256) dw_wgrad(const float* __restrict__ x, con
       const float* xn = x + static_cast<size_t>(n) * p.H * p.W * p.C + g * 4;
 #pragma unroll
       for (int t = 0; t < TAPS; ++t) {
-        const int r = t / p.S, s = t - r * p.S;
+        const int r = t / SW, s = t - r * SW;        // SW = filter width, compile time
         const int h = pp * p.sh - p.ph + r * p.dh, ww = q * p.sw - p.pw + s * p.dw;
         if (h < 0 || h >= p.H || ww < 0 || ww >= p.W) continue;
         const float4 a = __ldg(reinterpret_cast<const float4*>(xn + (static_cast<size_t>(h) * p.W + ww) * p.C));
@@ -120,8 +224,10 @@ __global__ void __launch_bounds__(256) dw_wgrad(const float* __restrict__ x, con
       }
     }
   }
-  // combine the row lanes of each channel group, one tap at a time
+  // combine the row lanes of each channel group, one tap at a time (unrolled: a dynamic index
+  // would push the accumulators out of registers into local memory)
   float4* mine = reinterpret_cast<float4*>(sm) + ty * tx_n + tx;
+#pragma unroll
   for (int t = 0; t <= TAPS; ++t) {
     *mine = t < TAPS ? acc[t] : accb;
     __syncthreads();
@@ -133,6 +239,82 @@ __global__ void __launch_bounds__(256) dw_wgrad(const float* __restrict__ x, con
       }
       float* dst = t < TAPS ? dwt + static_cast<size_t>(t) * p.C + g * 4 : db + g * 4;
       atomicAdd(dst + 0, s.x); atomicAdd(dst + 1, s.y); atomicAdd(dst + 2, s.z); atomicAdd(dst + 3, s.w);
+    }
+    __syncthreads();
+  }
+}
+
+
+// 3x3 backward-filter with the same row tiling: a lane takes kTw consecutive output pixels of a
+// row, loads their dy values and the 3 x ((kTw-1)*STRIDE + 3) input columns once, and updates the
+// nine per-tap accumulators for all of them (5.5 instead of 10 loads per pixel at stride 1).
+template <int STRIDE>
+__global__ void __launch_bounds__(256) dw3x3_wgrad(const float* __restrict__ x, const float* __restrict__ dy,
+                                                   float* __restrict__ dwt, float* __restrict__ db, DwP p,
+                                                   int qtiles, size_t tiles, int chunks, int tx_n, int ty_n) {
+  constexpr int kCols = (kTw - 1) * STRIDE + 3;
+  extern __shared__ float sm[];   // [ty_n][tx_n][4]
+  const int tx = threadIdx.x % tx_n, ty = threadIdx.x / tx_n;
+  const int g = blockIdx.y * tx_n + tx;
+  const bool live = g * 4 < p.C;
+  float4 acc[9];
+  float4 accb = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int t = 0; t < 9; ++t) acc[t] = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (live) {
+    const size_t per = (tiles + chunks - 1) / chunks;
+    const size_t t0 = static_cast<size_t>(blockIdx.x) * per;
+    const size_t t1 = (t0 + per) < tiles ? (t0 + per) : tiles;
+    for (size_t tile = t0 + ty; tile < t1; tile += ty_n) {
+      const int qt = static_cast<int>(tile % qtiles);
+      size_t rest = tile / qtiles;
+      const int pp = static_cast<int>(rest % p.P);
+      const int n = static_cast<int>(rest / p.P);
+      const int q0 = qt * kTw;
+      float4 d[kTw];
+      const float4* dr = reinterpret_cast<const float4*>(dy + ((static_cast<size_t>(n) * p.P + pp) * p.Q + q0) * p.C) + g;
+      const int cgs = p.C / 4;
+#pragma unroll
+      for (int j = 0; j < kTw; ++j) {
+        d[j] = (q0 + j < p.Q) ? __ldg(dr + static_cast<size_t>(j) * cgs) : make_float4(0.f, 0.f, 0.f, 0.f);
+        accb.x += d[j].x; accb.y += d[j].y; accb.z += d[j].z; accb.w += d[j].w;
+      }
+      const float* xn = x + static_cast<size_t>(n) * p.H * p.W * p.C + g * 4;
+      const int w0 = q0 * STRIDE - p.pw;
+#pragma unroll
+      for (int r = 0; r < 3; ++r) {
+        const int h = pp * STRIDE - p.ph + r;
+        if (h < 0 || h >= p.H) continue;
+        const float* xr = xn + static_cast<size_t>(h) * p.W * p.C;
+        float4 col[kCols];
+#pragma unroll
+        for (int c = 0; c < kCols; ++c) {
+          const int ww = w0 + c;
+          col[c] = (ww >= 0 && ww < p.W) ? __ldg(reinterpret_cast<const float4*>(xr + static_cast<size_t>(ww) * p.C))
+                                         : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < kTw; ++j)
+#pragma unroll
+          for (int sidx = 0; sidx < 3; ++sidx) fma4(acc[r * 3 + sidx], col[j * STRIDE + sidx], d[j]);
+      }
+    }
+  }
+  // combine the row lanes of each channel group, one tap at a time (unrolled: a dynamic index
+  // would push the accumulators out of registers into local memory)
+  float4* mine = reinterpret_cast<float4*>(sm) + ty * tx_n + tx;
+#pragma unroll
+  for (int t = 0; t <= 9; ++t) {
+    *mine = t < 9 ? acc[t] : accb;
+    __syncthreads();
+    if (ty == 0 && live && (t < 9 || db)) {
+      float4 sum = *mine;
+      for (int j = 1; j < ty_n; ++j) {
+        const float4 o = reinterpret_cast<float4*>(sm)[j * tx_n + tx];
+        sum.x += o.x; sum.y += o.y; sum.z += o.z; sum.w += o.w;
+      }
+      float* dst = t < 9 ? dwt + static_cast<size_t>(t) * p.C + g * 4 : db + g * 4;
+      atomicAdd(dst + 0, sum.x); atomicAdd(dst + 1, sum.y); atomicAdd(dst + 2, sum.z); atomicAdd(dst + 3, sum.w);
     }
     __syncthreads();
   }
@@ -167,6 +349,16 @@ int mb_depthwise_fprop(const float* x, const float* w_tc, const float* bias, flo
   if (rc) return rc;
   if (!x || !w_tc || !y || !aligned(x, 16) || !aligned(w_tc, 16) || !aligned(y, 16) || !aligned(bias, 16))
     return fail(MB_ERR_INVALID_ARGUMENT, "mb_depthwise_fprop: null or misaligned pointer");
+  if (p.R == 3 && p.S == 3 && p.dh == 1 && p.dw == 1 && p.sh == p.sw && (p.sh == 1 || p.sh == 2)) {
+    const int qtiles = (p.Q + kTw - 1) / kTw;
+    const size_t total = static_cast<size_t>(p.N) * p.P * qtiles * (p.C / 4);
+    const int grid = grid_for(total, 256, 8);
+    if (p.sh == 1)
+      dw3x3_tiled<1, false><<<grid, 256, 0, as_stream(stream)>>>(x, w_tc, bias, y, p, qtiles, total);
+    else
+      dw3x3_tiled<2, false><<<grid, 256, 0, as_stream(stream)>>>(x, w_tc, bias, y, p, qtiles, total);
+    return after_launch("depthwise_fprop_3x3");
+  }
   const size_t total = static_cast<size_t>(p.N) * p.P * p.Q * (p.C / 4);
   dw_fprop<<<grid_for(total, 256, 8), 256, 0, as_stream(stream)>>>(x, w_tc, bias, y, p, total);
   return after_launch("depthwise_fprop");
@@ -179,7 +371,22 @@ int mb_depthwise_dgrad(const float* dy, const float* w_tc, float* dx, const mb_c
   if (rc) return rc;
   if (!dy || !w_tc || !dx || !aligned(dy, 16) || !aligned(w_tc, 16) || !aligned(dx, 16))
     return fail(MB_ERR_INVALID_ARGUMENT, "mb_depthwise_dgrad: null or misaligned pointer");
+  if (p.R == 3 && p.S == 3 && p.dh == 1 && p.dw == 1 && p.sh == 1 && p.sw == 1 && p.ph <= 2 && p.pw <= 2) {
+    // stride 1: a forward pass over dy with the flipped filter and padding 2 - pad
+    DwP b = p;
+    b.H = p.P; b.W = p.Q; b.P = p.H; b.Q = p.W;
+    b.ph = 2 - p.ph; b.pw = 2 - p.pw;
+    const int qtiles = (b.Q + kTw - 1) / kTw;
+    const size_t total = static_cast<size_t>(b.N) * b.P * qtiles * (b.C / 4);
+    dw3x3_tiled<1, true><<<grid_for(total, 256, 8), 256, 0, as_stream(stream)>>>(dy, w_tc, nullptr, dx, b,
+                                                                                 qtiles, total);
+    return after_launch("depthwise_dgrad_3x3");
+  }
   const size_t total = static_cast<size_t>(p.N) * p.H * p.W * (p.C / 4);
+  if (p.R == 3 && p.S == 3 && p.dh == 1 && p.dw == 1 && p.sh == 2 && p.sw == 2) {
+    dw3x3s2_dgrad<<<grid_for(total, 256, 8), 256, 0, as_stream(stream)>>>(dy, w_tc, dx, p, total);
+    return after_launch("depthwise_dgrad_3x3s2");
+  }
   dw_dgrad<<<grid_for(total, 256, 8), 256, 0, as_stream(stream)>>>(dy, w_tc, dx, p, total);
   return after_launch("depthwise_dgrad");
 }
@@ -194,6 +401,7 @@ int mb_depthwise_wgrad(const float* x, const float* dy, float* dw_tc, float* dbi
     return fail(MB_ERR_INVALID_ARGUMENT, "%s: null or misaligned pointer", who);
   cudaStream_t st = as_stream(stream);
   const int taps = p.R * p.S;
+  if (p.R != p.S) return fail(MB_ERR_UNSUPPORTED, "%s: square filters only", who);
   if (cudaMemsetAsync(dw_tc, 0, static_cast<size_t>(taps) * p.C * sizeof(float), st) != cudaSuccess ||
       (dbias && cudaMemsetAsync(dbias, 0, static_cast<size_t>(p.C) * sizeof(float), st) != cudaSuccess))
     return fail(MB_ERR_LAUNCH, "%s: memset failed", who);
@@ -207,12 +415,25 @@ int mb_depthwise_wgrad(const float* x, const float* dy, float* dw_tc, float* dbi
   const int cap = kNumSMs * 4 / slabs > 0 ? kNumSMs * 4 / slabs : 1;
   if (chunks > cap) chunks = cap;
   if (chunks < 1) chunks = 1;
-  dim3 grid(chunks, slabs);
   const size_t smem = 256 * sizeof(float4);
+  if (taps == 9 && p.dh == 1 && p.dw == 1 && p.sh == p.sw && (p.sh == 1 || p.sh == 2)) {
+    const int qtiles = (p.Q + kTw - 1) / kTw;
+    const size_t tiles = static_cast<size_t>(p.N) * p.P * qtiles;
+    int tchunks = static_cast<int>((tiles + ty * 2 - 1) / (static_cast<size_t>(ty) * 2));
+    if (tchunks > cap) tchunks = cap;
+    if (tchunks < 1) tchunks = 1;
+    dim3 tgrid(tchunks, slabs);
+    if (p.sh == 1)
+      dw3x3_wgrad<1><<<tgrid, 256, smem, st>>>(x, dy, dw_tc, dbias, p, qtiles, tiles, tchunks, tx, ty);
+    else
+      dw3x3_wgrad<2><<<tgrid, 256, smem, st>>>(x, dy, dw_tc, dbias, p, qtiles, tiles, tchunks, tx, ty);
+    return after_launch("depthwise_wgrad_3x3");
+  }
+  dim3 grid(chunks, slabs);
   switch (taps) {
-    case 1: dw_wgrad<1><<<grid, 256, smem, st>>>(x, dy, dw_tc, dbias, p, pixels, chunks, tx, ty); break;
-    case 9: dw_wgrad<9><<<grid, 256, smem, st>>>(x, dy, dw_tc, dbias, p, pixels, chunks, tx, ty); break;
-    case 25: dw_wgrad<25><<<grid, 256, smem, st>>>(x, dy, dw_tc, dbias, p, pixels, chunks, tx, ty); break;
+    case 1: dw_wgrad<1, 1><<<grid, 256, smem, st>>>(x, dy, dw_tc, dbias, p, pixels, chunks, tx, ty); break;
+    case 9: dw_wgrad<9, 3><<<grid, 256, smem, st>>>(x, dy, dw_tc, dbias, p, pixels, chunks, tx, ty); break;
+    case 25: dw_wgrad<25, 5><<<grid, 256, smem, st>>>(x, dy, dw_tc, dbias, p, pixels, chunks, tx, ty); break;
     default: return fail(MB_ERR_UNSUPPORTED, "%s: %dx%d filters (1x1, 3x3 and 5x5 are built)", who, p.R, p.S);
   }
   return after_launch("depthwise_wgrad");
