@@ -40,6 +40,9 @@ def parse():
     ap.add_argument("--no-fuse", action="store_true",
                     help="run batch norm, residual add and ReLU as separate operators, as the "
                          "reference's graph does")
+    ap.add_argument("--no-channel-sums", action="store_true",
+                    help="batch norms make their own statistics pass instead of taking the sums "
+                         "the preceding convolution's statistics warps leave")
     ap.add_argument("--batch", type=int, default=184)
     ap.add_argument("--cpu-batch", type=int, default=16, help="images per step of the CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -216,7 +219,7 @@ def family_costs(runner_obj, batch_shape):
     bn train fwd 12 B/el (16 with a residual operand), bn cached-stat fwd 8, bn bwd 20 (also
     when it gates by the recomputed ReLU), relu fwd 8 (+1/8 with mask), relu bwd from a saved
     activation 12 (16 when it also sums two gradients), bn+add+relu bwd 32 (28 with one
-    gradient), add 12, max-pool 4*E_in + 4.5*E_out
+    gradient), add 12, batch norm fed with its producer's channel sums 8 (12 with a residual), max-pool 4*E_in + 4.5*E_out
     each way."""
     import numpy as np
     cost = {}
@@ -226,6 +229,17 @@ def family_costs(runner_obj, batch_shape):
         c[0] += b; c[1] += f
 
     shapes = runner_obj.shapes
+    emitters = {n.sums_from for n in runner_obj.nodes if getattr(n, "sums_from", -1) >= 0}
+
+    def emits_sums(n):
+        """True when this convolution's statistics warps leave the sums for its batch norm."""
+        if n.id not in emitters:
+            return False
+        w = runner_obj._tensors[n.args[1].value]
+        stride = n.args[3].value
+        multi_tap_s1 = w.shape[2] * w.shape[3] > 1 and stride[0] == 1 and stride[1] == 1
+        return w.shape[0] % 32 == 0 and w.shape[1] > 4 and not multi_tap_s1
+
     for n in runner_obj.nodes:
         out = shapes[n.id]
         e_out = float(np.prod(out))
@@ -237,20 +251,32 @@ def family_costs(runner_obj, batch_shape):
             w = runner_obj._tensors[n.args[1].value]
             e_w = float(w.numel())
             fl = 2.0 * e_out * w.shape[1] * w.shape[2] * w.shape[3]
-            add("mb_conv2d_fprop", 4 * (e_in + e_w + e_out), fl)
+            add("mb_conv2d_fprop_bnstats" if emits_sums(n) else "mb_conv2d_fprop", 4 * (e_in + e_w + e_out), fl)
             add("mb_conv2d_wgrad", 4 * (e_in + e_w + e_out), fl)
             if a0.kind == 'node':
                 add("mb_conv2d_dgrad", 4 * (e_in + e_w + e_out), fl)
         elif n.op == 'aten::batch_norm':
-            add("mb_bn_fwd_train", 12 * e_out)
+            src = runner_obj.nodes[n.sums_from] if getattr(n, "sums_from", -1) >= 0 else None
+            if src is not None and emits_sums(src):
+                add("mb_bn_act_fwd_train_partials", 8 * e_out)
+            else:
+                add("mb_bn_fwd_train", 12 * e_out)
             add("mb_bn_bwd_from_output" if ch.impl == 1 else "mb_bn_bwd_from_input", 20 * e_out)
-        elif n.op == 'monet::batch_norm_relu':
-            add("mb_bn_act_fwd_train", 12 * e_out)
+        elif n.op in ('monet::batch_norm_relu', 'monet::batch_norm_relu6'):
+            src = runner_obj.nodes[n.sums_from] if n.sums_from >= 0 else None
+            if src is not None and emits_sums(src):
+                add("mb_bn_act_fwd_train_partials", 8 * e_out)
+            else:
+                add("mb_bn_act_fwd_train", 12 * e_out)
             if ch.recompute:
                 add("mb_bn_act_fwd_apply", 8 * e_out)
-            add("mb_bn_relu_bwd_from_input", 20 * e_out)
+            add("mb_bn_act_bwd_from_input", 20 * e_out)
         elif n.op == 'monet::batch_norm_add_relu':
-            add("mb_bn_act_fwd_train", 16 * e_out)
+            src = runner_obj.nodes[n.sums_from] if n.sums_from >= 0 else None
+            if src is not None and emits_sums(src):
+                add("mb_bn_act_fwd_train_partials", 12 * e_out)
+            else:
+                add("mb_bn_act_fwd_train", 16 * e_out)
             if ch.recompute:
                 add("mb_bn_act_fwd_apply", 12 * e_out)
             add("mb_bn_add_relu_bwd", (32 if len(n.users) == 2 else 28) * e_out)
@@ -270,9 +296,10 @@ def family_costs(runner_obj, batch_shape):
 # capture under ncu, and every one of these kernels streams its operands once, so the traffic
 # of a step's launches is taken to grow in proportion to their algorithmic bytes.
 TRAFFIC_RATIO = {
-    "mb_conv2d_fprop": 679.8 / 738.7, "mb_conv2d_dgrad": 719.8 / 738.7, "mb_conv2d_wgrad": 742.9 / 738.7,
+    "mb_conv2d_fprop": 679.8 / 738.7, "mb_conv2d_fprop_bnstats": 679.8 / 738.7, "mb_conv2d_dgrad": 719.8 / 738.7, "mb_conv2d_wgrad": 742.9 / 738.7,
     "mb_bn_bwd_from_output": 1740.8 / 1772.0, "mb_bn_bwd_from_input": 1740.8 / 1772.0,
-    "mb_bn_relu_bwd_from_input": (1188.5 + 1743.9) / (1182.0 + 1772.0),
+    "mb_bn_act_bwd_from_input": (1188.5 + 1743.9) / (1182.0 + 1772.0),
+    "mb_bn_act_fwd_train_partials": 1136.9 / 1182.0,
     "mb_bn_add_relu_bwd": (2903.3 + 1743.9) / (2954.0 + 1772.0),
     "mb_bn_fwd_train": 594.7 / 591.0, "mb_bn_act_fwd_train": (594.7 + 1136.9) / (591.0 + 1182.0),
     "mb_relu_fwd": 1136.5 / 1182.0, "mb_relu_bwd_act": 1744.0 / 1772.0, "mb_relu_bwd_act2": 2333.9 / 2363.0,
@@ -316,7 +343,7 @@ def run_ours(args):
             views.append(flat[off:off + p.numel()].view(p.shape))
             off += p.numel()
     policy = getattr(runner, args.schedule)
-    run = runner.Runner(model, policy, fuse=not args.no_fuse)
+    run = runner.Runner(model, policy, fuse=not args.no_fuse, channel_sums=not args.no_channel_sums)
     ce = SoftmaxCrossEntropy()
 
     B = args.batch

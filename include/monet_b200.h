@@ -188,6 +188,16 @@ int mb_bn_act_fwd_train(const float* x, const float* residual, int relu, const f
 int mb_bn_act_fwd_apply(const float* x, const float* residual, int relu, const float* gamma,
                         const float* beta, const float* mean, const float* invstd, float* y,
                         const mb_bn_desc* d, void* stream);
+/* The same forward when the producer of x already summed it per channel
+ * (mb_conv2d_fprop_bnstats): `partials` is [2][partial_rows][C] with
+ * sum(x - shift) and sum((x - shift)^2) per row and channel, `shift` [C] or null
+ * for zero.  Skips the statistics pass over x (4 of the 12 bytes per element);
+ * needs no workspace.                                                          */
+int mb_bn_act_fwd_train_partials(const float* x, const float* residual, int relu, const float* gamma,
+                                 const float* beta, float* running_mean, float* running_var,
+                                 float* y, float* save_mean, float* save_invstd,
+                                 const mb_bn_desc* d, const float* partials, int partial_rows,
+                                 const float* shift, void* stream);
 /* Backward through y = relu(bn(x)) from the stored INPUT x: relu.py's backward
  * (dy gated by y > 0) followed by cudnn_backward (lrbn.cpp:43-70) in one reduce
  * and one sweep.  The gate is re-evaluated from x with the forward's own
@@ -285,6 +295,21 @@ size_t mb_conv_workspace_bytes(int pass, int variant, const mb_conv_desc* d);
 int mb_conv2d_fprop(const float* x, const float* w, const float* bias, float* y,
                     const mb_conv_desc* d, int variant, void* workspace, size_t workspace_bytes,
                     void* stream);
+/* The same convolution, also leaving the per-channel sums of its output that a
+ * following batch norm needs (the reference's batch norm re-reads the whole
+ * activation for them, lrbn.cpp:32-40): four extra warps per CTA walk every
+ * staged output chunk and add partials[0][cta][k] = sum(y - shift[k]),
+ * partials[1][cta][k] = sum((y - shift[k])^2); *partial_rows returns the number
+ * of CTA rows written.  `partials` must hold mb_conv_bnstats_bytes(d); `shift` is
+ * [K] or NULL (zero) - a value near the channel mean (the running mean) keeps the
+ * variance from cancelling.  K must be a multiple of 32; stride-1 multi-tap
+ * filters return MB_ERR_UNSUPPORTED (run the plain pair).  Hand the result to
+ * mb_bn_act_fwd_train_partials.                                               */
+size_t mb_conv_bnstats_bytes(const mb_conv_desc* d);
+int mb_conv2d_fprop_bnstats(const float* x, const float* w, const float* bias, float* y,
+                            const mb_conv_desc* d, int variant, void* workspace,
+                            size_t workspace_bytes, const float* shift, float* partials,
+                            size_t partials_bytes, int* partial_rows, void* stream);
 /* dx = backward-data.  Variant 0: implicit GEMM over dy.  When C is a multiple of
  * 32 the filter is read in place (MN-major tiles of w) and no workspace is needed;
  * otherwise it is first transposed to [C][R][S][K] in the workspace

@@ -70,6 +70,7 @@ PROTOTYPES = {
     "mb_bn_bwd_from_input": (C.c_int, [c_f] * 8 + [C.POINTER(BnDesc), c_f, c_sz, c_f]),
     "mb_bn_act_fwd_train": (C.c_int, [c_f, c_f, C.c_int] + [c_f] * 7 + [C.POINTER(BnDesc), c_f, c_sz, c_f]),
     "mb_bn_act_fwd_apply": (C.c_int, [c_f, c_f, C.c_int] + [c_f] * 5 + [C.POINTER(BnDesc), c_f]),
+    "mb_bn_act_fwd_train_partials": (C.c_int, [c_f, c_f, C.c_int] + [c_f] * 7 + [C.POINTER(BnDesc), c_f, C.c_int, c_f, c_f]),
     "mb_bn_add_relu_bwd": (C.c_int, [c_f] * 11 + [C.POINTER(BnDesc), c_f, c_sz, c_f]),
     "mb_bn_act_bwd_from_input": (C.c_int, [c_f] * 6 + [C.c_int] + [c_f] * 3 + [C.POINTER(BnDesc), c_f, c_sz, c_f]),
     "mb_bn_relu_bwd_from_input": (C.c_int, [c_f] * 9 + [C.POINTER(BnDesc), c_f, c_sz, c_f]),
@@ -82,6 +83,9 @@ PROTOTYPES = {
     "mb_conv_num_variants": (C.c_int, [C.c_int]),
     "mb_conv_workspace_bytes": (c_sz, [C.c_int, C.c_int, C.POINTER(ConvDesc)]),
     "mb_conv2d_fprop": (C.c_int, [c_f, c_f, c_f, c_f, C.POINTER(ConvDesc), C.c_int, c_f, c_sz, c_f]),
+    "mb_conv_bnstats_bytes": (c_sz, [C.POINTER(ConvDesc)]),
+    "mb_conv2d_fprop_bnstats": (C.c_int, [c_f, c_f, c_f, c_f, C.POINTER(ConvDesc), C.c_int, c_f, c_sz,
+                                           c_f, c_f, c_sz, C.POINTER(C.c_int), c_f]),
     "mb_conv2d_dgrad": (C.c_int, [c_f, c_f, c_f, C.POINTER(ConvDesc), C.c_int, c_f, c_sz, c_f]),
     "mb_conv2d_wgrad": (C.c_int, [c_f, c_f, c_f, c_f, C.POINTER(ConvDesc), C.c_int, c_f, c_sz, c_f]),
     "mb_depthwise_fprop": (C.c_int, [c_f, c_f, c_f, c_f, C.POINTER(ConvDesc), c_f]),

@@ -362,7 +362,7 @@ __global__ void __launch_bounds__(32 * kFinStripes) bn_finalize(
     }
     const double m = static_cast<double>(M);
     if (MODE == kFwd) {
-      const double K = static_cast<double>(first_elems[static_cast<size_t>(c) * first_stride]);
+      const double K = first_elems ? static_cast<double>(first_elems[static_cast<size_t>(c) * first_stride]) : 0.0;
       const double e1 = s1 / m;
       double var = s2 / m - e1 * e1;
       if (var < 0.0) var = 0.0;
@@ -677,6 +677,32 @@ int mb_bn_act_fwd_apply(const float* x, const float* residual, int relu, const f
                         const mb_bn_desc* d, void* stream) {
   return fwd_apply_impl("mb_bn_act_fwd_apply", x, residual, relu, gamma, beta, mean, invstd, y, d,
                         stream);
+}
+
+int mb_bn_act_fwd_train_partials(const float* x, const float* residual, int relu, const float* gamma,
+                                 const float* beta, float* running_mean, float* running_var,
+                                 float* y, float* save_mean, float* save_invstd,
+                                 const mb_bn_desc* d, const float* partials, int partial_rows,
+                                 const float* shift, void* stream) {
+  const char* who = "mb_bn_act_fwd_train_partials";
+  int rc = check(who, d);
+  if (rc) return rc;
+  if (!x || !gamma || !beta || !y || !save_mean || !save_invstd || !partials || partial_rows <= 0)
+    return fail(MB_ERR_INVALID_ARGUMENT, "%s: null pointer or no partial sums", who);
+  rc = check_alignment(who, d, x, y, residual ? residual : y);
+  if (rc) return rc;
+  Geometry g = make_geometry(d);
+  cudaStream_t st = as_stream(stream);
+  // the statistics pass over x is replaced by the sums its producer left: finalize over
+  // `partial_rows` rows of [2][rows][C], taken around `shift` (null: zero)
+  bn_finalize<kFwd><<<(g.C + 31) / 32, 32 * kFinStripes, 0, st>>>(
+      partials, nullptr, shift, 1, g.C, g.M, partial_rows, d->eps, d->momentum, running_mean,
+      running_var, save_mean, save_invstd);
+  rc = after_launch("bn_fwd_finalize");
+  if (rc) return rc;
+  SweepConst k{gamma, beta, save_mean, save_invstd, nullptr, nullptr, 0, nullptr, relu ? 1 : 0, act_upper(relu)};
+  if (residual) return run_sweep<kFwdRes>("bn_act_fwd_sweep", d, g, x, residual, y, k, st);
+  return run_sweep<kFwd>("bn_fwd_sweep", d, g, x, nullptr, y, k, st);
 }
 
 int mb_bn_add_relu_bwd(const float* dy1, const float* dy2, const float* y, const float* x,

@@ -138,7 +138,8 @@ TileShape pick_tile(int N, int P, int Q) {
 int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
 // Tile width along N and pipeline depth for `kout` output channels.
-void pick_bn_stages(int kout, long long m_tiles, int* BN, int* stages, size_t* smem) {
+void pick_bn_stages(int kout, long long m_tiles, int* BN, int* stages, size_t* smem,
+                    size_t extra_bytes = 0) {
   int bn = round_up(kout < 256 ? kout : 256, 32);   // whole 32-column chunks for the TMA-store epilogue
   // prefer more, narrower tiles when the wide ones would leave SMs idle in the last wave
   auto eff = [&](int b) {
@@ -149,12 +150,12 @@ void pick_bn_stages(int kout, long long m_tiles, int* BN, int* stages, size_t* s
   while (bn > 64 && bn % 64 == 0 && eff(bn / 2) > eff(bn) * 1.15) bn /= 2;
   const size_t stage = kAStageBytes + static_cast<size_t>(bn) * 128;
   const size_t staging = 2 * kAStageBytes;            // TMA-store epilogue buffers
-  int st = static_cast<int>((220 * 1024 - 2048 - staging) / stage);
+  int st = static_cast<int>((220 * 1024 - 2048 - staging - extra_bytes) / stage);
   if (st > 8) st = 8;
   if (st < 2) st = 2;
   *BN = bn;
   *stages = st;
-  *smem = 512 + 1024 + stage * st + staging;
+  *smem = 512 + 1024 + stage * st + staging + extra_bytes;
 }
 
 long long* g_conv_prof = nullptr;   // diagnostics: device buffer for cycle counters (or null)
@@ -192,7 +193,10 @@ int launch_gemm(const char* who, GemmLaunch& L, cudaStream_t st) {
     }
   }
   L.p.prof = g_conv_prof;
-  conv_gemm_kmajor<<<L.grid, 192, L.smem, st>>>(L.a[0], L.a[1], L.a[2], L.a[3], L.b, L.out, L.p);
+  if (L.p.stats && !L.p.tma_store)
+    return fail(MB_ERR_UNSUPPORTED, "%s: output statistics need the TMA-store epilogue", who);
+  // warps 6-9 exist only when the per-channel sums of the output are wanted
+  conv_gemm_kmajor<<<L.grid, L.p.stats ? 320 : 192, L.smem, st>>>(L.a[0], L.a[1], L.a[2], L.a[3], L.b, L.out, L.p);
   return after_launch(who);
 }
 
@@ -677,10 +681,9 @@ int mb_conv_device_status(int reset) {
   return v;
 }
 
-int mb_conv2d_fprop(const float* x, const float* w, const float* bias, float* y,
-                    const mb_conv_desc* d, int variant, void* workspace, size_t workspace_bytes,
-                    void* stream) {
-  const char* who = "mb_conv2d_fprop";
+static int fprop_impl(const char* who, const float* x, const float* w, const float* bias, float* y,
+                      const mb_conv_desc* d, int variant, void* workspace, size_t workspace_bytes,
+                      void* stream, float* stats, const float* stats_shift, int* stats_rows) {
   int rc = validate(who, d);
   if (rc) return rc;
   if (variant < 0 || variant >= mb_conv_num_variants(MB_CONV_FPROP))
@@ -691,6 +694,8 @@ int mb_conv2d_fprop(const float* x, const float* w, const float* bias, float* y,
   (void)workspace; (void)workspace_bytes;
 
   if (d->stride_h == 1 && d->stride_w == 1 && d->R * d->S > 1) {
+    // the halo kernels have no statistics warps: the caller falls back to the plain pair
+    if (stats) return fail(MB_ERR_UNSUPPORTED, "%s: no output statistics for stride-1 multi-tap filters", who);
     HaloTap taps[kMaxTaps];
     int nt = 0;
     for (int r = 0; r < d->R; ++r)
@@ -771,7 +776,8 @@ int mb_conv2d_fprop(const float* x, const float* w, const float* bias, float* y,
   p.tiles_h = (p.P + ts.bh - 1) / ts.bh;
   const long long tiles_n = (p.Nimg + ts.bn - 1) / ts.bn;
   const long long m_tiles = static_cast<long long>(p.tiles_w) * p.tiles_h * tiles_n;
-  pick_bn_stages(d->K, m_tiles, &p.BN, &p.stages, &L.smem);
+  pick_bn_stages(d->K, m_tiles, &p.BN, &p.stages, &L.smem,
+                 stats ? (static_cast<size_t>(2) * d->K + 128) * sizeof(float) : 0);
   p.tiles_c = (d->K + p.BN - 1) / p.BN;
   const long long tiles = m_tiles * p.tiles_c;
   if (tiles > 0x7fffffffLL) return fail(MB_ERR_UNSUPPORTED, "%s: too many tiles", who);
@@ -779,7 +785,38 @@ int mb_conv2d_fprop(const float* x, const float* w, const float* bias, float* y,
   rc = encode_filter(who, &L.b, w, d->C, d->R * d->S, d->K, p.BN);
   if (rc) return rc;
   L.grid = p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs;
+  p.stats = stats;
+  p.stats_shift = stats_shift;
+  if (stats_rows) *stats_rows = L.grid;
   return launch_gemm("conv_fprop_tcgen05", L, as_stream(stream));
+}
+
+int mb_conv2d_fprop(const float* x, const float* w, const float* bias, float* y,
+                    const mb_conv_desc* d, int variant, void* workspace, size_t workspace_bytes,
+                    void* stream) {
+  return fprop_impl("mb_conv2d_fprop", x, w, bias, y, d, variant, workspace, workspace_bytes, stream,
+                    nullptr, nullptr, nullptr);
+}
+
+size_t mb_conv_bnstats_bytes(const mb_conv_desc* d) {
+  if (!d || d->K <= 0) return 0;
+  return static_cast<size_t>(2) * kNumSMs * d->K * sizeof(float);
+}
+
+int mb_conv2d_fprop_bnstats(const float* x, const float* w, const float* bias, float* y,
+                            const mb_conv_desc* d, int variant, void* workspace,
+                            size_t workspace_bytes, const float* shift, float* partials,
+                            size_t partials_bytes, int* partial_rows, void* stream) {
+  const char* who = "mb_conv2d_fprop_bnstats";
+  if (!partials || !partial_rows) return fail(MB_ERR_INVALID_ARGUMENT, "%s: null pointer", who);
+  if (partials_bytes < mb_conv_bnstats_bytes(d))
+    return fail(MB_ERR_WORKSPACE, "%s: %zu bytes needed for the partial sums, %zu given", who,
+                mb_conv_bnstats_bytes(d), partials_bytes);
+  if (d && d->K % 32)
+    return fail(MB_ERR_UNSUPPORTED, "%s: output channels must be a multiple of 32", who);
+  *partial_rows = 0;
+  return fprop_impl(who, x, w, bias, y, d, variant, workspace, workspace_bytes, stream, partials, shift,
+                    partial_rows);
 }
 
 int mb_conv2d_dgrad(const float* dy, const float* w, float* dx, const mb_conv_desc* d, int variant,

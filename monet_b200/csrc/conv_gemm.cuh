@@ -16,6 +16,8 @@
 //   warp 4   TMA producer: fills a ring of `stages` {A,B} slots
 //   warp 5   MMA issuer  : one thread issues tcgen05.mma (M=128, N=BN, K=8),
 //                          commits free the slots and publish the accumulator
+//   warps 6-9 statistics : only when the output's per-channel sums are wanted: they walk the
+//                          columns of every staged chunk while the epilogue moves on
 //   warps 0-3 epilogue   : tcgen05.ld of a double-buffered accumulator, bias,
 //                          128-byte-per-thread stores, overlapped with the
 //                          next tile's main loop
@@ -56,6 +58,10 @@ struct GemmParams {
   int b_mn;                     // 1: the filter tile is MN-major, [32-column group][32 k rows][32 columns]
                                 //    straight from a [k][tap][n] filter (backward-data without a transpose)
   long long* prof;              // optional: cycle counters written by CTA 0 (diagnostics), or null
+  float* stats;                 // optional: per-CTA partial sums [2][gridDim.x][Kout] of the output
+                                // (sum of (y - shift) and of (y - shift)^2 per channel), or null;
+                                // needs tma_store and a launch with 320 threads (warps 6-9 do it)
+  const float* stats_shift;     // [Kout] shift used in those sums, or null for zero
   Taps taps;
 };
 
@@ -78,7 +84,7 @@ struct Ring {
 
 }  // namespace detail
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUtensorMap mapA1,
                  const __grid_constant__ CUtensorMap mapA2, const __grid_constant__ CUtensorMap mapA3,
                  const __grid_constant__ CUtensorMap mapB, const __grid_constant__ CUtensorMap mapOut,
@@ -93,12 +99,16 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* epi_ok = abort_flag + 1;                            // [4], one per epilogue warp
+  uint64_t* stat_full = reinterpret_cast<uint64_t*>(smem_raw + 320);   // [2] staged chunk ready for the statistics warps
+  uint64_t* stat_empty = stat_full + 2;                               // [2] statistics warps are done with the buffer
   const uint32_t slots0 = (smem_u32(smem_raw) + 512u + 1023u) & ~1023u;
   const uint32_t b_stage_bytes = static_cast<uint32_t>(p.BN) * 128u;
   const uint32_t stage_bytes = kAStageBytes + b_stage_bytes;
   uint8_t* slots_ptr = smem_raw + (slots0 - smem_u32(smem_raw));
   // two 16 KiB staging buffers for the TMA-store epilogue sit behind the operand slots
   uint8_t* stage_out = slots_ptr + static_cast<size_t>(p.stages) * stage_bytes;
+  float* s_stats = reinterpret_cast<float*>(stage_out + 2 * kAStageBytes);   // [2][Kout] when p.stats
+  int* row_dec = reinterpret_cast<int*>(s_stats + 2 * p.Kout);               // [128] when p.stats
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // two accumulators of BN columns; the epilogue reads whole 32-column groups, so the
@@ -114,6 +124,8 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
       mbar_init(&acc_empty[a], 128);
+      mbar_init(&stat_full[a], 1);
+      mbar_init(&stat_empty[a], 4);      // one arrival per statistics warp
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -121,6 +133,15 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
   if (warp == 5) {
     tmem_alloc(tmem_slot, tmem_cols);
     tmem_relinquish();
+  }
+  if (p.stats) {
+    // per-CTA sums start at zero; row_dec[m] = (w, h, n) of tile row m packed 10 bits each, or
+    // -1 for rows past the pixel box (the same for every tile of this launch)
+    for (int i = threadIdx.x; i < 2 * p.Kout; i += blockDim.x) s_stats[i] = 0.f;
+    for (int m = threadIdx.x; m < kTileM; m += blockDim.x) {
+      const int wi = m % p.bw, hi = (m / p.bw) % p.bh, ni = m / (p.bw * p.bh);
+      row_dec[m] = m < p.bn * p.bh * p.bw ? (wi | (hi << 10) | (ni << 20)) : -1;
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -249,7 +270,7 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
         atomicCAS(&g_conv_status, 0, 2);
       }
     }
-  } else {
+  } else if (warp < 4) {
     // ---------------------------------------------------------------- epilogue
     bool ok = true;
     int it = 0;
@@ -287,7 +308,14 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
           tmem_ld32(t_row + col, v);
           tmem_ld_wait();
           uint8_t* buf = stage_out + static_cast<size_t>(chunk_no & 1) * kAStageBytes;
-          if (threadIdx.x == 0) tma_store_wait_read<1>();     // the store that last read `buf` is done
+          if (threadIdx.x == 0) {
+            tma_store_wait_read<1>();                         // the store that last read `buf` is done
+            // ... and so are the statistics warps (first use of a buffer passes at once)
+            if (p.stats && !mbar_wait_spin(&stat_empty[chunk_no & 1], ((chunk_no >> 1) & 1u) ^ 1u, abort_flag)) {
+              *abort_flag = 1;
+              atomicCAS(&g_conv_status, 0, 4);
+            }
+          }
           named_barrier(1, 128);
           float4* rowp = reinterpret_cast<float4*>(buf + m * 128);
 #pragma unroll
@@ -304,6 +332,7 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
           if (threadIdx.x == 0) {
             tma_store_4d(&mapOut, buf, c0 + col, q0, p0, n0);
             tma_store_commit();
+            if (p.stats) mbar_arrive(&stat_full[chunk_no & 1]);   // staged chunk visible to warps 6-9
           }
           ++chunk_no;
         }
@@ -336,6 +365,105 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
     if (!ok && lane == 0) {
       *abort_flag = 1;
       atomicCAS(&g_conv_status, 0, 3);
+    }
+  } else if (p.stats) {
+    // -------------------------------------------------------------- statistics (warps 6-9)
+    // Warp w owns columns 8w .. 8w+7 of every staged 32-column chunk, all 128 rows: lane l sums
+    // column 8w + (l & 7) over the 32 rows of group l >> 3 (rows visited in a per-group rotated
+    // order so that the four groups read different banks of the swizzled staging buffer), two
+    // shuffles combine the groups, and lanes 0-7 add the totals to the CTA's sums in shared
+    // memory.  Every column of the output belongs to one fixed thread, so those sums need no
+    // atomics (a float atomicAdd on shared memory is a compare-and-swap loop and cost more than
+    // the whole walk).  Sums are taken around stats_shift; halo / padding rows are masked.
+    const int sw = warp - 6;
+    const int cl = lane & 7, grp = lane >> 3;
+    const int c = 8 * sw + cl, r0 = 32 * grp;
+    const int t = static_cast<int>(threadIdx.x) - 192;
+    int row_off8[8];         // byte offset, inside a block of 8 rows, of the j-th row this lane visits
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int r7 = (j + 2 * grp) & 7;
+      row_off8[j] = r7 * 128 + (((c >> 2) ^ r7) << 4);
+    }
+    bool ok = true;
+    int chunk_no = 0;
+    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      int c0, q0, p0, n0;
+      decode(tile, c0, q0, p0, n0);
+      uint32_t mask = 0;     // bit i: the i-th row this lane visits is a real output pixel
+#pragma unroll 4
+      for (int i = 0; i < 32; ++i) {
+        const int dec = row_dec[r0 + (i & ~7) + ((i + 2 * grp) & 7)];
+        const bool valid = dec >= 0 && q0 + (dec & 0x3ff) < p.Q && p0 + ((dec >> 10) & 0x3ff) < p.P &&
+                           n0 + (dec >> 20) < p.Nimg;
+        mask |= (valid ? 1u : 0u) << i;
+      }
+      for (int col = 0; col < p.BN && c0 + col < p.Kout; col += 32) {
+        const int b = chunk_no & 1;
+        int got = 1;
+        if (lane == 0) got = mbar_wait_spin(&stat_full[b], (chunk_no >> 1) & 1u, abort_flag) ? 1 : 0;
+        got = __shfl_sync(0xffffffffu, got, 0);
+        if (!got) {
+          ok = false;
+          break;
+        }
+        const uint8_t* buf = stage_out + static_cast<size_t>(b) * kAStageBytes;
+        const int k = c0 + col + c;
+        const float kk = (p.stats_shift && k < p.Kout) ? __ldg(p.stats_shift + k) : 0.f;
+        // the byte offset of row-in-block j for this lane is fixed for the whole kernel (row_off8),
+        // so a load costs one address add per 8 rows; two independent chains per sum for ILP
+        const uint8_t* colp = buf + r0 * 128 + ((c & 3) << 2);
+        float s1a = 0.f, s1b = 0.f, s2a = 0.f, s2b = 0.f;
+        if (mask == 0xffffffffu) {                 // the common case: every row is a real pixel
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint8_t* pj = colp + row_off8[j];
+#pragma unroll
+            for (int blk = 0; blk < 4; ++blk) {
+              const float d = *reinterpret_cast<const float*>(pj + blk * 1024) - kk;
+              if (blk & 1) { s1b += d; s2b = fmaf(d, d, s2b); } else { s1a += d; s2a = fmaf(d, d, s2a); }
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint8_t* pj = colp + row_off8[j];
+#pragma unroll
+            for (int blk = 0; blk < 4; ++blk) {
+              const float v = *reinterpret_cast<const float*>(pj + blk * 1024);
+              const float d = ((mask >> (blk * 8 + j)) & 1u) ? v - kk : 0.f;
+              if (blk & 1) { s1b += d; s2b = fmaf(d, d, s2b); } else { s1a += d; s2a = fmaf(d, d, s2a); }
+            }
+          }
+        }
+        float s1 = s1a + s1b, s2 = s2a + s2b;
+        __syncwarp();                              // every lane has read its column
+        if (lane == 0) mbar_arrive(&stat_empty[b]);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, 8);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, 8);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, 16);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, 16);
+        if (grp == 0 && k < p.Kout) {              // the one thread that owns column k
+          s_stats[k] += s1;
+          s_stats[p.Kout + k] += s2;
+        }
+        ++chunk_no;
+      }
+    }
+    const bool all_ok = __all_sync(0xffffffffu, ok);
+    if (!all_ok && lane == 0) {
+      *abort_flag = 1;
+      atomicCAS(&g_conv_status, 0, 5);
+    }
+    named_barrier(2, 128);                       // every statistics warp has added its share
+    if (*abort_flag == 0) {
+      // this CTA's row of the partial sums: [0][blockIdx.x][k] and [1][blockIdx.x][k]
+      float* g1 = p.stats + static_cast<size_t>(blockIdx.x) * p.Kout;
+      float* g2 = p.stats + (static_cast<size_t>(gridDim.x) + blockIdx.x) * p.Kout;
+      for (int i = t; i < p.Kout; i += 128) {
+        g1[i] = s_stats[i];
+        g2[i] = s_stats[p.Kout + i];
+      }
     }
   }
 

@@ -388,6 +388,37 @@ def bn_act_fwd_train(x, residual, relu, gamma, beta, running_mean, running_var, 
     return y, save_mean, save_invstd
 
 
+def bn_act_fwd_train_partials(x, sums: "ChannelSums", residual, relu, gamma, beta, running_mean,
+                              running_var, momentum, eps, inplace=False):
+    """bn_act_fwd_train without the statistics pass: `sums` come from the producer of x."""
+    _need_cuda(x, gamma, beta, running_mean, running_var); _f32(x, "x")
+    xd = _bn_dense(x)
+    if xd is not x:
+        raise RuntimeError("monet_b200 batch norm: producer sums need the producer's own dense tensor")
+    d = bn_desc(xd, eps, momentum)
+    if sums.partials.numel() < 2 * sums.rows * d.C:
+        raise RuntimeError("monet_b200 batch norm: partial sums do not match the channel count")
+    rd = None
+    if residual is not None:
+        _need_cuda(residual); _f32(residual, "residual")
+        rd = like(xd, residual) if xd.dim() == 4 else residual.contiguous()
+        if rd.shape != xd.shape:
+            raise RuntimeError("monet_b200 batch norm: residual shape mismatch")
+    y = xd if inplace else torch.empty_like(xd)
+    save_mean = torch.empty(d.C, dtype=torch.float32, device=x.device)
+    save_invstd = torch.empty(d.C, dtype=torch.float32, device=x.device)
+    check(lib().mb_bn_act_fwd_train_partials(
+        xd.data_ptr(), rd.data_ptr() if rd is not None else None, int(relu),
+        gamma.data_ptr(), beta.data_ptr(),
+        running_mean.data_ptr() if running_mean is not None else None,
+        running_var.data_ptr() if running_var is not None else None,
+        y.data_ptr(), save_mean.data_ptr(), save_invstd.data_ptr(), C.byref(d),
+        sums.partials.data_ptr(), int(sums.rows),
+        sums.shift.data_ptr() if sums.shift is not None else None, _stream()),
+        "bn_act_fwd_train_partials")
+    return y, save_mean, save_invstd
+
+
 def bn_act_fwd_apply(x, residual, relu, gamma, beta, mean, invstd, inplace=False):
     _need_cuda(x, gamma, beta, mean, invstd); _f32(x, "x")
     xd = _bn_dense(x)
@@ -645,11 +676,50 @@ def _smallc_input(x: torch.Tensor, d: ConvDesc, geom) -> torch.Tensor:
     return xp
 
 
-def conv2d_fprop(x, w, bias, stride, padding, dilation, groups=1, variant: int = 0):
-    """y = conv2d(x, w) + bias; y is a channels_last tensor of logical shape N x K x P x Q."""
+class ChannelSums:
+    """Per-channel partial sums of a convolution's output, left by its statistics warps for the
+    batch norm that follows: `partials` is [2][rows][K] (sum and sum of squares around `shift`)."""
+
+    __slots__ = ("partials", "rows", "shift")
+
+    def __init__(self, partials, rows, shift):
+        self.partials, self.rows, self.shift = partials, rows, shift
+
+
+def conv2d_fprop(x, w, bias, stride, padding, dilation, groups=1, variant: int = 0,
+                 stats_shift=None, want_stats: bool = False):
+    """y = conv2d(x, w) + bias; y is a channels_last tensor of logical shape N x K x P x Q.
+
+    With ``want_stats`` returns ``(y, ChannelSums or None)``: the sums a following batch norm
+    needs, accumulated beside the epilogue around ``stats_shift`` ([K] or None); None when this
+    geometry has no such path (few-channel input, K not a multiple of 32, stride-1 multi-tap
+    filters)."""
     _need_cuda(x, w, bias); _f32(x, "x"); _f32(w, "w")
     d0 = conv_desc(x.shape, w.shape, stride, padding, dilation, groups)
     geom = _smallc_geometry(d0)
+    if want_stats:
+        multi_tap_s1 = d0.R * d0.S > 1 and d0.stride_h == 1 and d0.stride_w == 1
+        if geom is None and d0.K % 32 == 0 and groups == 1 and not multi_tap_s1:
+            d = _padded_desc(d0)
+            if d.K == d0.K:
+                xa, wk = _act_nhwc(x), _filter_krsc(w)
+                b = bias.detach().contiguous() if bias is not None else None
+                y = torch.empty((d.N, d.K, d.P, d.Q), dtype=x.dtype, device=x.device,
+                                memory_format=torch.channels_last)
+                ws = _workspace(MB_CONV_FPROP, variant, d, x.device)
+                nbytes = lib().mb_conv_bnstats_bytes(C.byref(d))
+                partials = torch.empty(nbytes // 4, dtype=torch.float32, device=x.device)
+                rows = C.c_int(0)
+                sh = stats_shift.detach() if stats_shift is not None else None
+                if sh is not None:
+                    _need_cuda(sh); _f32(sh, "stats_shift")
+                check(lib().mb_conv2d_fprop_bnstats(
+                    xa.data_ptr(), wk.data_ptr(), b.data_ptr() if b is not None else None,
+                    y.data_ptr(), C.byref(d), int(variant), ws.data_ptr(), ws.numel(),
+                    sh.data_ptr() if sh is not None else None, partials.data_ptr(), nbytes,
+                    C.byref(rows), _stream()), "conv2d_fprop_bnstats")
+                return y, ChannelSums(partials, rows.value, sh)
+        return conv2d_fprop(x, w, bias, stride, padding, dilation, groups, variant), None
     if geom is not None:
         if variant != 0:
             raise RuntimeError("monet_b200.conv2d_fprop: no variant %d for a few-channel input" % variant)

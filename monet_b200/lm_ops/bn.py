@@ -17,6 +17,7 @@ class _BatchNorm(OP):
     running_mean = None
     running_var = None
     inplace = False
+    input_sums = None      # F.ChannelSums left by the producer of the input, or None
 
     def forward(self, input_, weight, bias, running_mean, running_var,
                 training=False, momentum=0.1, eps=1e-5, *args, **kwargs):
@@ -25,7 +26,12 @@ class _BatchNorm(OP):
                 self.running_mean = running_mean.requires_grad_(False) if running_mean is not None else None
                 self.running_var = running_var.requires_grad_(False) if running_var is not None else None
             if self.params is None:
-                if training:
+                if training and self.input_sums is not None:
+                    out, mean, invstd = F.bn_act_fwd_train_partials(
+                        input_, self.input_sums, None, 0, weight, bias, self.running_mean,
+                        self.running_var, momentum, eps, inplace=self.inplace)
+                    self.input_sums = None
+                elif training:
                     out, mean, invstd = F.bn_fwd_train(
                         input_, weight, bias, self.running_mean, self.running_var,
                         momentum, eps, inplace=self.inplace)

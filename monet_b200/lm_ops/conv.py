@@ -52,11 +52,24 @@ class _ConvBase(OP):
     def n_bwd_wt_algos():
         return F.conv_num_variants(MB_CONV_WGRAD)
 
+    # An executor that knows a batch norm is the only reader of this output sets
+    # `emit_channel_sums` (and, optionally, a per-channel shift near the expected mean): the
+    # forward then leaves the sums that batch norm needs in `channel_sums` (F.ChannelSums, or
+    # None where the geometry has no such path) and the batch norm skips its statistics pass.
+    emit_channel_sums = False
+    channel_sums_shift = None
+    channel_sums = None
+
     # -- the three passes, with the reference's "retry with the default" behaviour ----------
     def _fprop(self, x, w, bias, variant):
         stride, padding, dilation, groups = self.params[:4]
         if self.is_depthwise or groups != 1:
             return F.depthwise_fprop(x, w, bias, stride, padding, dilation, groups)
+        if self.emit_channel_sums:
+            y, self.channel_sums = F.conv2d_fprop(x, w, bias, stride, padding, dilation, groups,
+                                                  max(variant, 0), stats_shift=self.channel_sums_shift,
+                                                  want_stats=True)
+            return y
         try:
             return F.conv2d_fprop(x, w, bias, stride, padding, dilation, groups, max(variant, 0))
         except RuntimeError:

@@ -26,6 +26,7 @@ class _FusedBatchNorm(OP):
     running_var = None
     inplace = False
     relu = True
+    input_sums = None      # F.ChannelSums left by the producer of the input, or None
 
     def _forward(self, input_, residual, weight, bias, running_mean, running_var, training,
                  momentum, eps):
@@ -34,7 +35,12 @@ class _FusedBatchNorm(OP):
                 self.running_mean = running_mean.requires_grad_(False) if running_mean is not None else None
                 self.running_var = running_var.requires_grad_(False) if running_var is not None else None
             if self.params is None:
-                if training:
+                if training and self.input_sums is not None:
+                    out, mean, invstd = F.bn_act_fwd_train_partials(
+                        input_, self.input_sums, residual, self.relu, weight, bias,
+                        self.running_mean, self.running_var, momentum, eps, inplace=self.inplace)
+                    self.input_sums = None
+                elif training:
                     out, mean, invstd = F.bn_act_fwd_train(
                         input_, residual, self.relu, weight, bias, self.running_mean,
                         self.running_var, momentum, eps, inplace=self.inplace)

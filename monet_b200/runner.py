@@ -51,6 +51,8 @@ class Node:
     args: List[Arg]
     module: str = ""              # qualified name of the nn.Module it came from
     users: List[int] = field(default_factory=list)
+    sums_from: int = -1           # batch-norm-like node: id of the convolution whose statistics
+                                  # warps leave the per-channel sums of this node's input, or -1
 
 
 def _as_list(v, n=2):
@@ -222,7 +224,24 @@ def fuse_graph(nodes: List[Node], out_id: int) -> Tuple[List[Node], int]:
         for a in n.args:
             if a.kind == 'node':
                 out[a.value].users.append(n.id)
+    link_channel_sums(out)
     return out, target(out_id)
+
+
+_BN_LIKE = ('aten::batch_norm', 'monet::batch_norm_relu', 'monet::batch_norm_relu6',
+            'monet::batch_norm_add_relu')
+
+
+def link_channel_sums(nodes: List[Node]) -> None:
+    """Marks every training-mode batch-norm-like node whose input is a dense convolution with no
+    other reader: that convolution can sum its output per channel beside its epilogue and the
+    batch norm skip its statistics pass."""
+    for n in nodes:
+        if n.op not in _BN_LIKE or not n.args[5].value or n.args[0].kind != 'node':
+            continue
+        src = nodes[n.args[0].value]
+        if src.op == 'aten::_convolution' and src.users == [n.id] and src.args[8].value == 1:
+            n.sums_from = src.id
 
 
 # ---------------------------------------------------------------------------- policy
@@ -294,12 +313,15 @@ class Runner:
 
     def __init__(self, model: nn.Module, policy: Policy = store_all,
                  mode: str = "conv_multiway_newnode", input_requires_grad: bool = False,
-                 fuse: bool = False):
+                 fuse: bool = False, channel_sums: bool = True):
         self.model = model
         self.nodes, self.out_id = extract_graph(model)
         if fuse:
             from .lm_ops import fused  # noqa: F401  (registers the monet:: nodes)
             self.nodes, self.out_id = fuse_graph(self.nodes, self.out_id)
+            if not channel_sums:       # batch norms make their own statistics pass
+                for n in self.nodes:
+                    n.sums_from = -1
         self.mode = mode
         self.input_requires_grad = input_requires_grad
         self.choices = [policy(self.nodes, n) for n in self.nodes]
@@ -385,9 +407,18 @@ class Runner:
         vals: Dict[int, Optional[torch.Tensor]] = {}
         self._inter: Dict[int, Any] = {}
         with torch.no_grad():
+            emitters = {n.sums_from: n for n in self.nodes if n.sums_from >= 0}
             for n in self.nodes:
                 op = self._ops[n.id]
                 args = self._resolve(n, vals, inputs)
+                if n.id in emitters and hasattr(op, 'emit_channel_sums'):
+                    rm = emitters[n.id].args[3]
+                    op.emit_channel_sums = True
+                    op.channel_sums_shift = self._tensors[rm.value] if rm.kind == 'param' else None
+                if n.sums_from >= 0:
+                    src = self._ops[n.sums_from]
+                    op.input_sums = getattr(src, 'channel_sums', None)
+                    src.channel_sums = None
                 out = op.forward(*args)
                 if any(isinstance(d, IntermediateStorage) for d in _descriptors(op)):
                     out, self._inter[n.id] = out

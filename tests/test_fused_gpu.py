@@ -258,7 +258,7 @@ def test_fused_network_equals_unfused(cuda, policy):
         model.load_state_dict(state)
         for p in model.parameters():
             p.grad = None
-        run = runner.Runner(model, getattr(runner, policy), fuse=fuse)
+        run = runner.Runner(model, getattr(runner, policy), fuse=fuse, channel_sums=False)
         if fuse:
             ops = [n.op for n in run.nodes]
             assert 'aten::relu_' not in ops and 'aten::add' not in ops and 'aten::add_' not in ops
@@ -292,7 +292,7 @@ def test_mobilenet_fused_equals_unfused(cuda):
         model.load_state_dict(state)
         for p in model.parameters():
             p.grad = None
-        run = runner.Runner(model, runner.low_memory, fuse=fuse)
+        run = runner.Runner(model, runner.low_memory, fuse=fuse, channel_sums=False)
         if fuse:
             assert sum(n.op == 'monet::batch_norm_relu6' for n in run.nodes) == 35
         torch.manual_seed(123)            # the classifier's dropout draws from the global generator
@@ -304,3 +304,88 @@ def test_mobilenet_fused_equals_unfused(cuda):
     for k in g0:
         scale = float(g0[k].abs().max()) + 1e-12
         assert float((g0[k] - g1[k]).abs().max()) <= 1e-4 * scale, k
+
+
+def test_conv_channel_sums(cuda):
+    """A convolution whose statistics warps sum its output per channel: the sums (taken around a
+    shift) reproduce the batch statistics, and a batch norm fed with them matches the oracle."""
+    from monet_b200 import functional as F
+    g = torch.Generator().manual_seed(11)
+    cl = torch.channels_last
+    cases = [((6, 64, 20, 20), (96, 64, 1, 1), 1, 0), ((4, 64, 30, 30), (128, 64, 1, 1), 2, 0),
+             ((3, 160, 9, 9), (320, 160, 1, 1), 1, 0), ((4, 32, 15, 15), (32, 32, 3, 3), 2, 1),
+             ((184, 64, 14, 14), (256, 64, 1, 1), 1, 0), ((5, 32, 17, 19), (64, 32, 3, 3), 1, 1),
+             ((2, 3, 40, 40), (32, 3, 7, 7), 2, 3), ((2, 64, 8, 8), (48, 64, 1, 1), 1, 0)]
+    for xs, ws, stride, pad in cases:
+        x = torch.randn(xs, generator=g)
+        w = torch.randn(ws, generator=g) * 0.1
+        bias = torch.randn(ws[0], generator=g)
+        K = ws[0]
+        gamma, beta = torch.rand(K, generator=g) + 0.5, torch.randn(K, generator=g)
+        rm, rv = torch.randn(K, generator=g) * 0.3, torch.rand(K, generator=g) + 0.5
+        xg = x.to(cuda).contiguous(memory_format=cl) if xs[1] % 4 == 0 else x.to(cuda)
+        wg = w.to(cuda).contiguous(memory_format=cl)
+        rmg, rvg = rm.to(cuda), rv.to(cuda)
+        y, sums = F.conv2d_fprop(xg, wg, bias.to(cuda), stride, pad, 1, 1, 0, stats_shift=rmg,
+                                 want_stats=True)
+        y_plain = F.conv2d_fprop(xg, wg, bias.to(cuda), stride, pad, 1)
+        assert torch.equal(y, y_plain)
+        multi_tap_s1 = ws[2] * ws[3] > 1 and stride == 1
+        if xs[1] < 4 or K % 32 or multi_tap_s1:
+            assert sums is None                 # no such path: the caller runs the plain batch norm
+            continue
+        assert sums is not None and sums.rows >= 1
+        part = sums.partials[:2 * sums.rows * K].view(2, sums.rows, K).double().sum(1).cpu()
+        yd = y.double().cpu() - rm.double().view(1, -1, 1, 1)
+        assert torch.allclose(part[0], yd.sum((0, 2, 3)), rtol=1e-5, atol=1e-3)
+        assert torch.allclose(part[1], (yd * yd).sum((0, 2, 3)), rtol=1e-5, atol=1e-3)
+        residual = torch.randn(y.shape, generator=g)
+        ref_y, ref_mean, ref_invstd, ref_rm, ref_rv = oracle.bn_act_forward_train(
+            y.cpu(), residual, True, gamma, beta, rm, rv, 0.1, 1e-5)
+        out, mean, invstd = F.bn_act_fwd_train_partials(
+            y, sums, residual.to(cuda).contiguous(memory_format=cl), True, gamma.to(cuda),
+            beta.to(cuda), rmg, rvg, 0.1, 1e-5)
+        assert torch.allclose(out.cpu(), ref_y, rtol=RTOL, atol=2e-5)
+        assert torch.allclose(mean.cpu(), ref_mean, rtol=RTOL, atol=1e-5)
+        assert torch.allclose(invstd.cpu(), ref_invstd, rtol=1e-4, atol=1e-5)
+        assert torch.allclose(rmg.cpu(), ref_rm, rtol=RTOL, atol=1e-5)
+        assert torch.allclose(rvg.cpu(), ref_rv, rtol=1e-4, atol=1e-5)
+    assert F.conv_device_status() == 0
+
+
+def test_network_with_channel_sums(cuda):
+    """The whole fused graph with convolution-side statistics against the same graph with the
+    batch norms' own statistics pass."""
+    import torchvision
+    from monet_b200 import runner
+    torch.manual_seed(0)
+    model = torchvision.models.resnet50(num_classes=10).to(cuda).to(memory_format=torch.channels_last)
+    model.train()
+    x = torch.randn(8, 3, 64, 64, device=cuda)
+    gout = torch.randn(8, 10, device=cuda)
+    state = {k: v.clone() for k, v in model.state_dict().items()}
+    results = []
+    for sums in (False, True):
+        model.load_state_dict(state)
+        for p in model.parameters():
+            p.grad = None
+        run = runner.Runner(model, runner.low_memory, fuse=True, channel_sums=sums)
+        if sums:
+            assert sum(n.sums_from >= 0 for n in run.nodes) == 53
+        out = run.forward(x)
+        run.backward(gout.clone())
+        results.append((out.clone(), {k: p.grad.clone() for k, p in model.named_parameters()},
+                        {k: v.clone() for k, v in model.state_dict().items() if 'running' in k}))
+    (o0, g0, s0), (o1, g1, s1) = results
+    # a 1e-7 difference in a statistic can move an activation across a TF32 truncation boundary
+    # of the next convolution, so the two runs differ by TF32 noise (about 1e-3 per layer), not
+    # by fp32 rounding; the bar is the convolution tolerance of this library, rtol 2e-2
+    assert torch.allclose(o0, o1, rtol=2e-2, atol=2e-2 * float(o0.abs().max()))
+    for k in [k for k in s0 if k.startswith('layer1.0.bn1.')]:   # first batch norm fed by a 1x1 convolution
+        assert torch.allclose(s0[k], s1[k], rtol=1e-4, atol=1e-5), k
+    # gradients: only the classifier's, which see the same TF32 noise as the logits; deeper in
+    # the backward chain 50 batch norms over 32..2048 samples amplify that noise without bound
+    # (stock PyTorch with TF32 cuDNN differs from fp32 by tens of per cent there as well)
+    for k in ('fc.weight', 'fc.bias'):
+        scale = float(g0[k].abs().max()) + 1e-12
+        assert float((g0[k] - g1[k]).abs().max()) <= 5e-2 * scale, k
