@@ -195,8 +195,8 @@ int launch_gemm(const char* who, GemmLaunch& L, cudaStream_t st) {
   L.p.prof = g_conv_prof;
   if (L.p.stats && !L.p.tma_store)
     return fail(MB_ERR_UNSUPPORTED, "%s: output statistics need the TMA-store epilogue", who);
-  // warps 6-9 exist only when the per-channel sums of the output are wanted
-  conv_gemm_kmajor<<<L.grid, L.p.stats ? 320 : 192, L.smem, st>>>(L.a[0], L.a[1], L.a[2], L.a[3], L.b, L.out, L.p);
+  // warps 6-13 exist only when the per-channel sums of the output are wanted
+  conv_gemm_kmajor<<<L.grid, L.p.stats ? 448 : 192, L.smem, st>>>(L.a[0], L.a[1], L.a[2], L.a[3], L.b, L.out, L.p);
   return after_launch(who);
 }
 
@@ -777,7 +777,7 @@ static int fprop_impl(const char* who, const float* x, const float* w, const flo
   const long long tiles_n = (p.Nimg + ts.bn - 1) / ts.bn;
   const long long m_tiles = static_cast<long long>(p.tiles_w) * p.tiles_h * tiles_n;
   pick_bn_stages(d->K, m_tiles, &p.BN, &p.stages, &L.smem,
-                 stats ? (static_cast<size_t>(2) * d->K + 128) * sizeof(float) : 0);
+                 stats ? kAStageBytes + (static_cast<size_t>(2) * d->K + 128) * sizeof(float) : 0);
   p.tiles_c = (d->K + p.BN - 1) / p.BN;
   const long long tiles = m_tiles * p.tiles_c;
   if (tiles > 0x7fffffffLL) return fail(MB_ERR_UNSUPPORTED, "%s: too many tiles", who);

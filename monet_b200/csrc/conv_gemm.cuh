@@ -16,7 +16,7 @@
 //   warp 4   TMA producer: fills a ring of `stages` {A,B} slots
 //   warp 5   MMA issuer  : one thread issues tcgen05.mma (M=128, N=BN, K=8),
 //                          commits free the slots and publish the accumulator
-//   warps 6-9 statistics : only when the output's per-channel sums are wanted: they walk the
+//   warps 6-13 statistics: only when the output's per-channel sums are wanted: they walk the
 //                          columns of every staged chunk while the epilogue moves on
 //   warps 0-3 epilogue   : tcgen05.ld of a double-buffered accumulator, bias,
 //                          128-byte-per-thread stores, overlapped with the
@@ -60,7 +60,7 @@ struct GemmParams {
   long long* prof;              // optional: cycle counters written by CTA 0 (diagnostics), or null
   float* stats;                 // optional: per-CTA partial sums [2][gridDim.x][Kout] of the output
                                 // (sum of (y - shift) and of (y - shift)^2 per channel), or null;
-                                // needs tma_store and a launch with 320 threads (warps 6-9 do it)
+                                // needs tma_store and a launch with 448 threads (warps 6-13 do it)
   const float* stats_shift;     // [Kout] shift used in those sums, or null for zero
   Taps taps;
 };
@@ -84,7 +84,7 @@ struct Ring {
 
 }  // namespace detail
 
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(448, 1)
 conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUtensorMap mapA1,
                  const __grid_constant__ CUtensorMap mapA2, const __grid_constant__ CUtensorMap mapA3,
                  const __grid_constant__ CUtensorMap mapB, const __grid_constant__ CUtensorMap mapOut,
@@ -99,15 +99,18 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* epi_ok = abort_flag + 1;                            // [4], one per epilogue warp
-  uint64_t* stat_full = reinterpret_cast<uint64_t*>(smem_raw + 320);   // [2] staged chunk ready for the statistics warps
-  uint64_t* stat_empty = stat_full + 2;                               // [2] statistics warps are done with the buffer
+  uint64_t* stat_full = reinterpret_cast<uint64_t*>(smem_raw + 320);   // [3] staged chunk ready for the statistics warps
+  uint64_t* stat_empty = stat_full + 3;                               // [3] statistics warps are done with the buffer
+  // staging buffers of the TMA-store epilogue: a third one when statistics warps read them too,
+  // so that those warps have two chunk periods to finish with a buffer
+  const int nbuf = p.stats ? 3 : 2;
   const uint32_t slots0 = (smem_u32(smem_raw) + 512u + 1023u) & ~1023u;
   const uint32_t b_stage_bytes = static_cast<uint32_t>(p.BN) * 128u;
   const uint32_t stage_bytes = kAStageBytes + b_stage_bytes;
   uint8_t* slots_ptr = smem_raw + (slots0 - smem_u32(smem_raw));
   // two 16 KiB staging buffers for the TMA-store epilogue sit behind the operand slots
   uint8_t* stage_out = slots_ptr + static_cast<size_t>(p.stages) * stage_bytes;
-  float* s_stats = reinterpret_cast<float*>(stage_out + 2 * kAStageBytes);   // [2][Kout] when p.stats
+  float* s_stats = reinterpret_cast<float*>(stage_out + 3 * kAStageBytes);   // [2][Kout] when p.stats
   int* row_dec = reinterpret_cast<int*>(s_stats + 2 * p.Kout);               // [128] when p.stats
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -124,8 +127,10 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
       mbar_init(&acc_empty[a], 128);
+    }
+    for (int a = 0; a < 3; ++a) {
       mbar_init(&stat_full[a], 1);
-      mbar_init(&stat_empty[a], 4);      // one arrival per statistics warp
+      mbar_init(&stat_empty[a], 8);      // one arrival per statistics warp
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -307,11 +312,13 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
           float v[32];
           tmem_ld32(t_row + col, v);
           tmem_ld_wait();
-          uint8_t* buf = stage_out + static_cast<size_t>(chunk_no & 1) * kAStageBytes;
+          const int bsel = chunk_no % nbuf;
+          uint8_t* buf = stage_out + static_cast<size_t>(bsel) * kAStageBytes;
           if (threadIdx.x == 0) {
-            tma_store_wait_read<1>();                         // the store that last read `buf` is done
+            // the store that last read `buf` is done ...
+            if (p.stats) tma_store_wait_read<2>(); else tma_store_wait_read<1>();
             // ... and so are the statistics warps (first use of a buffer passes at once)
-            if (p.stats && !mbar_wait_spin(&stat_empty[chunk_no & 1], ((chunk_no >> 1) & 1u) ^ 1u, abort_flag)) {
+            if (p.stats && !mbar_wait_spin(&stat_empty[bsel], ((chunk_no / 3) & 1u) ^ 1u, abort_flag)) {
               *abort_flag = 1;
               atomicCAS(&g_conv_status, 0, 4);
             }
@@ -332,7 +339,7 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
           if (threadIdx.x == 0) {
             tma_store_4d(&mapOut, buf, c0 + col, q0, p0, n0);
             tma_store_commit();
-            if (p.stats) mbar_arrive(&stat_full[chunk_no & 1]);   // staged chunk visible to warps 6-9
+            if (p.stats) mbar_arrive(&stat_full[bsel]);   // staged chunk visible to warps 6-13
           }
           ++chunk_no;
         }
@@ -367,22 +374,24 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
       atomicCAS(&g_conv_status, 0, 3);
     }
   } else if (p.stats) {
-    // -------------------------------------------------------------- statistics (warps 6-9)
-    // Warp w owns columns 8w .. 8w+7 of every staged 32-column chunk, all 128 rows: lane l sums
-    // column 8w + (l & 7) over the 32 rows of group l >> 3 (rows visited in a per-group rotated
-    // order so that the four groups read different banks of the swizzled staging buffer), two
-    // shuffles combine the groups, and lanes 0-7 add the totals to the CTA's sums in shared
+    // ------------------------------------------------------------- statistics (warps 6-13)
+    // Warp w owns columns 4w .. 4w+3 of every staged 32-column chunk, all 128 rows: lane l sums
+    // column 4w + (l & 3) over the 16 rows of group l >> 2 (rows visited in a per-group rotated
+    // order so that the eight groups read different banks of the swizzled staging buffer), three
+    // shuffles combine the groups, and lanes 0-3 add the totals to the CTA's sums in shared
     // memory.  Every column of the output belongs to one fixed thread, so those sums need no
     // atomics (a float atomicAdd on shared memory is a compare-and-swap loop and cost more than
     // the whole walk).  Sums are taken around stats_shift; halo / padding rows are masked.
+    // Eight warps rather than four: the walk is bound by one warp's instruction latency, and the
+    // epilogue thread waits for it before it reuses a staging buffer.
     const int sw = warp - 6;
-    const int cl = lane & 7, grp = lane >> 3;
-    const int c = 8 * sw + cl, r0 = 32 * grp;
+    const int cl = lane & 3, grp = lane >> 2;
+    const int c = 4 * sw + cl, r0 = 16 * grp;
     const int t = static_cast<int>(threadIdx.x) - 192;
     int row_off8[8];         // byte offset, inside a block of 8 rows, of the j-th row this lane visits
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const int r7 = (j + 2 * grp) & 7;
+      const int r7 = (j + grp) & 7;
       row_off8[j] = r7 * 128 + (((c >> 2) ^ r7) << 4);
     }
     bool ok = true;
@@ -392,16 +401,20 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
       decode(tile, c0, q0, p0, n0);
       uint32_t mask = 0;     // bit i: the i-th row this lane visits is a real output pixel
 #pragma unroll 4
-      for (int i = 0; i < 32; ++i) {
-        const int dec = row_dec[r0 + (i & ~7) + ((i + 2 * grp) & 7)];
+      for (int i = 0; i < 16; ++i) {
+        const int dec = row_dec[r0 + (i & ~7) + ((i + grp) & 7)];
         const bool valid = dec >= 0 && q0 + (dec & 0x3ff) < p.Q && p0 + ((dec >> 10) & 0x3ff) < p.P &&
                            n0 + (dec >> 20) < p.Nimg;
         mask |= (valid ? 1u : 0u) << i;
       }
+      // the shift of the next chunk is fetched while this one is walked
+      float kk = (p.stats_shift && c0 + c < p.Kout) ? __ldg(p.stats_shift + c0 + c) : 0.f;
       for (int col = 0; col < p.BN && c0 + col < p.Kout; col += 32) {
-        const int b = chunk_no & 1;
+        const int b = chunk_no % 3;
+        const int kn = c0 + col + 32 + c;
+        const float kk_next = (p.stats_shift && col + 32 < p.BN && kn < p.Kout) ? __ldg(p.stats_shift + kn) : 0.f;
         int got = 1;
-        if (lane == 0) got = mbar_wait_spin(&stat_full[b], (chunk_no >> 1) & 1u, abort_flag) ? 1 : 0;
+        if (lane == 0) got = mbar_wait_spin(&stat_full[b], (chunk_no / 3) & 1u, abort_flag) ? 1 : 0;
         got = __shfl_sync(0xffffffffu, got, 0);
         if (!got) {
           ok = false;
@@ -409,44 +422,44 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
         }
         const uint8_t* buf = stage_out + static_cast<size_t>(b) * kAStageBytes;
         const int k = c0 + col + c;
-        const float kk = (p.stats_shift && k < p.Kout) ? __ldg(p.stats_shift + k) : 0.f;
         // the byte offset of row-in-block j for this lane is fixed for the whole kernel (row_off8),
         // so a load costs one address add per 8 rows; two independent chains per sum for ILP
         const uint8_t* colp = buf + r0 * 128 + ((c & 3) << 2);
         float s1a = 0.f, s1b = 0.f, s2a = 0.f, s2b = 0.f;
-        if (mask == 0xffffffffu) {                 // the common case: every row is a real pixel
+        if (mask == 0xffffu) {                     // the common case: every row is a real pixel
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const uint8_t* pj = colp + row_off8[j];
-#pragma unroll
-            for (int blk = 0; blk < 4; ++blk) {
-              const float d = *reinterpret_cast<const float*>(pj + blk * 1024) - kk;
-              if (blk & 1) { s1b += d; s2b = fmaf(d, d, s2b); } else { s1a += d; s2a = fmaf(d, d, s2a); }
-            }
+            const float d0 = *reinterpret_cast<const float*>(pj) - kk;
+            const float d1 = *reinterpret_cast<const float*>(pj + 1024) - kk;
+            s1a += d0; s2a = fmaf(d0, d0, s2a);
+            s1b += d1; s2b = fmaf(d1, d1, s2b);
           }
         } else {
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const uint8_t* pj = colp + row_off8[j];
-#pragma unroll
-            for (int blk = 0; blk < 4; ++blk) {
-              const float v = *reinterpret_cast<const float*>(pj + blk * 1024);
-              const float d = ((mask >> (blk * 8 + j)) & 1u) ? v - kk : 0.f;
-              if (blk & 1) { s1b += d; s2b = fmaf(d, d, s2b); } else { s1a += d; s2a = fmaf(d, d, s2a); }
-            }
+            const float v0 = *reinterpret_cast<const float*>(pj);
+            const float v1 = *reinterpret_cast<const float*>(pj + 1024);
+            const float d0 = ((mask >> j) & 1u) ? v0 - kk : 0.f;
+            const float d1 = ((mask >> (8 + j)) & 1u) ? v1 - kk : 0.f;
+            s1a += d0; s2a = fmaf(d0, d0, s2a);
+            s1b += d1; s2b = fmaf(d1, d1, s2b);
           }
         }
         float s1 = s1a + s1b, s2 = s2a + s2b;
         __syncwarp();                              // every lane has read its column
         if (lane == 0) mbar_arrive(&stat_empty[b]);
-        s1 += __shfl_xor_sync(0xffffffffu, s1, 8);
-        s2 += __shfl_xor_sync(0xffffffffu, s2, 8);
-        s1 += __shfl_xor_sync(0xffffffffu, s1, 16);
-        s2 += __shfl_xor_sync(0xffffffffu, s2, 16);
+#pragma unroll
+        for (int x = 4; x <= 16; x <<= 1) {
+          s1 += __shfl_xor_sync(0xffffffffu, s1, x);
+          s2 += __shfl_xor_sync(0xffffffffu, s2, x);
+        }
         if (grp == 0 && k < p.Kout) {              // the one thread that owns column k
           s_stats[k] += s1;
           s_stats[p.Kout + k] += s2;
         }
+        kk = kk_next;
         ++chunk_no;
       }
     }
@@ -455,12 +468,12 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
       *abort_flag = 1;
       atomicCAS(&g_conv_status, 0, 5);
     }
-    named_barrier(2, 128);                       // every statistics warp has added its share
+    named_barrier(2, 256);                       // every statistics warp has added its share
     if (*abort_flag == 0) {
       // this CTA's row of the partial sums: [0][blockIdx.x][k] and [1][blockIdx.x][k]
       float* g1 = p.stats + static_cast<size_t>(blockIdx.x) * p.Kout;
       float* g2 = p.stats + (static_cast<size_t>(gridDim.x) + blockIdx.x) * p.Kout;
-      for (int i = t; i < p.Kout; i += 128) {
+      for (int i = t; i < p.Kout; i += 256) {
         g1[i] = s_stats[i];
         g2[i] = s_stats[p.Kout + i];
       }
