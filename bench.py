@@ -61,6 +61,7 @@ MICRO = {
     "fprop3x3_c256": ("fprop", 256, 14, 256, 3, 1, 1), "wgrad3x3_c256": ("wgrad", 256, 14, 256, 3, 1, 1),
     "fprop1x1_c64_k256": ("fprop", 64, 56, 256, 1, 1, 0), "dgrad1x1_c64_k256": ("dgrad", 64, 56, 256, 1, 1, 0),
     "wgrad1x1_c64_k256": ("wgrad", 64, 56, 256, 1, 1, 0), "fprop1x1_c1024_k256": ("fprop", 1024, 14, 256, 1, 1, 0),
+    "fprop1x1_c256_k64_sums": ("fprop_sums", 256, 56, 64, 1, 1, 0), "fprop1x1_c64_k256_sums": ("fprop_sums", 64, 56, 256, 1, 1, 0),
     "fprop3x3s2_c128": ("fprop", 128, 56, 128, 3, 2, 1), "wgrad3x3s2_c128": ("wgrad", 128, 56, 128, 3, 2, 1),
     "stem_fprop": ("fprop", 3, 224, 64, 7, 2, 3), "stem_wgrad": ("wgrad", 3, 224, 64, 7, 2, 3),
     "bn_fwd": ("bn_fwd", 256, 56, 0, 0, 0, 0), "bn_bwd": ("bn_bwd", 256, 56, 0, 0, 0, 0),
@@ -84,13 +85,15 @@ def run_micro(args):
     cl = torch.channels_last
     x = torch.randn(N, Cc, H, H, device=dev)
     x = x.contiguous(memory_format=cl) if Cc % 4 == 0 else x
-    if kind in ("fprop", "dgrad", "wgrad"):
+    if kind in ("fprop", "dgrad", "wgrad", "fprop_sums"):
         w = (torch.randn(K, Cc, R, R, device=dev) * 0.05).contiguous(memory_format=cl)
         y = F.conv2d_fprop(x, w, None, s, p, 1)
         dy = torch.randn_like(y)
         nbytes = 4.0 * (x.numel() + w.numel() + y.numel())
         flops = 2.0 * y.numel() * Cc * R * R
+        shift = torch.zeros(K, device=dev)
         fn = {"fprop": lambda: F.conv2d_fprop(x, w, None, s, p, 1),
+              "fprop_sums": lambda: F.conv2d_fprop(x, w, None, s, p, 1, 1, 0, stats_shift=shift, want_stats=True),
               "dgrad": lambda: F.conv2d_dgrad(dy, w, x.shape, s, p, 1),
               "wgrad": lambda: F.conv2d_wgrad(x, dy, w.shape, s, p, 1)}[kind]
     else:
