@@ -240,8 +240,9 @@ def family_costs(runner_obj, batch_shape):
             return False
         w = runner_obj._tensors[n.args[1].value]
         stride = n.args[3].value
-        multi_tap_s1 = w.shape[2] * w.shape[3] > 1 and stride[0] == 1 and stride[1] == 1
-        return w.shape[0] % 32 == 0 and w.shape[1] > 4 and not multi_tap_s1
+        swapped = (w.shape[2] * w.shape[3] > 1 and stride[0] == 1 and stride[1] == 1
+                   and 64 < w.shape[0] <= 128)
+        return w.shape[0] % 32 == 0 and w.shape[1] > 4 and not swapped
 
     for n in runner_obj.nodes:
         out = shapes[n.id]

@@ -693,13 +693,15 @@ def conv2d_fprop(x, w, bias, stride, padding, dilation, groups=1, variant: int =
     With ``want_stats`` returns ``(y, ChannelSums or None)``: the sums a following batch norm
     needs, accumulated beside the epilogue around ``stats_shift`` ([K] or None); None when this
     geometry has no such path (few-channel input, K not a multiple of 32, stride-1 multi-tap
-    filters)."""
+    filters with 65..128 output channels)."""
     _need_cuda(x, w, bias); _f32(x, "x"); _f32(w, "w")
     d0 = conv_desc(x.shape, w.shape, stride, padding, dilation, groups)
     geom = _smallc_geometry(d0)
     if want_stats:
-        multi_tap_s1 = d0.R * d0.S > 1 and d0.stride_h == 1 and d0.stride_w == 1
-        if geom is None and d0.K % 32 == 0 and groups == 1 and not multi_tap_s1:
+        # stride-1 multi-tap layers with 65..128 output channels run the swapped-operand kernel,
+        # which has no staging buffer to sum from: it is worth more than the statistics pass
+        swapped = d0.R * d0.S > 1 and d0.stride_h == 1 and d0.stride_w == 1 and 64 < d0.K <= 128
+        if geom is None and d0.K % 32 == 0 and groups == 1 and not swapped:
             d = _padded_desc(d0)
             if d.K == d0.K:
                 xa, wk = _act_nhwc(x), _filter_krsc(w)
@@ -713,12 +715,14 @@ def conv2d_fprop(x, w, bias, stride, padding, dilation, groups=1, variant: int =
                 sh = stats_shift.detach() if stats_shift is not None else None
                 if sh is not None:
                     _need_cuda(sh); _f32(sh, "stats_shift")
-                check(lib().mb_conv2d_fprop_bnstats(
+                rc = lib().mb_conv2d_fprop_bnstats(
                     xa.data_ptr(), wk.data_ptr(), b.data_ptr() if b is not None else None,
                     y.data_ptr(), C.byref(d), int(variant), ws.data_ptr(), ws.numel(),
                     sh.data_ptr() if sh is not None else None, partials.data_ptr(), nbytes,
-                    C.byref(rows), _stream()), "conv2d_fprop_bnstats")
-                return y, ChannelSums(partials, rows.value, sh)
+                    C.byref(rows), _stream())
+                if rc != 2:      # MB_ERR_UNSUPPORTED: nothing was launched, run the plain pair
+                    check(rc, "conv2d_fprop_bnstats")
+                    return y, ChannelSums(partials, rows.value, sh)
         return conv2d_fprop(x, w, bias, stride, padding, dilation, groups, variant), None
     if geom is not None:
         if variant != 0:
