@@ -62,6 +62,7 @@ MICRO = {
     "fprop1x1_c64_k256": ("fprop", 64, 56, 256, 1, 1, 0), "dgrad1x1_c64_k256": ("dgrad", 64, 56, 256, 1, 1, 0),
     "wgrad1x1_c64_k256": ("wgrad", 64, 56, 256, 1, 1, 0), "fprop1x1_c1024_k256": ("fprop", 1024, 14, 256, 1, 1, 0),
     "fprop1x1_c256_k64_sums": ("fprop_sums", 256, 56, 64, 1, 1, 0), "fprop1x1_c64_k256_sums": ("fprop_sums", 64, 56, 256, 1, 1, 0),
+    "fprop3x3_c512": ("fprop", 512, 7, 512, 3, 1, 1),
     "fprop3x3s2_c128": ("fprop", 128, 56, 128, 3, 2, 1), "wgrad3x3s2_c128": ("wgrad", 128, 56, 128, 3, 2, 1),
     "stem_fprop": ("fprop", 3, 224, 64, 7, 2, 3), "stem_wgrad": ("wgrad", 3, 224, 64, 7, 2, 3),
     "bn_fwd": ("bn_fwd", 256, 56, 0, 0, 0, 0), "bn_bwd": ("bn_bwd", 256, 56, 0, 0, 0, 0),
@@ -240,9 +241,8 @@ def family_costs(runner_obj, batch_shape):
             return False
         w = runner_obj._tensors[n.args[1].value]
         stride = n.args[3].value
-        swapped = (w.shape[2] * w.shape[3] > 1 and stride[0] == 1 and stride[1] == 1
-                   and 64 < w.shape[0] <= 128)
-        return w.shape[0] % 32 == 0 and w.shape[1] > 4 and not swapped
+        multi_tap_s1 = w.shape[2] * w.shape[3] > 1 and stride[0] == 1 and stride[1] == 1
+        return w.shape[0] % 32 == 0 and w.shape[1] > 4 and not multi_tap_s1
 
     for n in runner_obj.nodes:
         out = shapes[n.id]

@@ -297,14 +297,13 @@ int mb_conv2d_fprop(const float* x, const float* w, const float* bias, float* y,
                     void* stream);
 /* The same convolution, also leaving the per-channel sums of its output that a
  * following batch norm needs (the reference's batch norm re-reads the whole
- * activation for them, lrbn.cpp:32-40): eight extra warps per CTA (the epilogue
- * warps themselves for stride-1 multi-tap filters) walk every staged output
- * chunk and add partials[0][cta][k] = sum(y - shift[k]),
+ * activation for them, lrbn.cpp:32-40): four extra warps per CTA walk every
+ * staged output chunk and add partials[0][cta][k] = sum(y - shift[k]),
  * partials[1][cta][k] = sum((y - shift[k])^2); *partial_rows returns the number
  * of CTA rows written.  `partials` must hold mb_conv_bnstats_bytes(d); `shift` is
  * [K] or NULL (zero) - a value near the channel mean (the running mean) keeps the
- * variance from cancelling.  K must be a multiple of 32; a geometry without
- * such a path returns MB_ERR_UNSUPPORTED with nothing launched (run the plain pair).  Hand the result to
+ * variance from cancelling.  K must be a multiple of 32; stride-1 multi-tap
+ * filters return MB_ERR_UNSUPPORTED (run the plain pair).  Hand the result to
  * mb_bn_act_fwd_train_partials.                                               */
 size_t mb_conv_bnstats_bytes(const mb_conv_desc* d);
 int mb_conv2d_fprop_bnstats(const float* x, const float* w, const float* bias, float* y,

@@ -217,8 +217,7 @@ struct HaloTap { int dh, dw, btap; };
 // geometry does not fit, so that the caller can fall back to the per-tap kernel.
 int run_halo(const char* who, const float* in, int Cin, int Win, int Hin, const float* filt, int T,
              float* out, int Kout, int Qo, int Po, int N, const HaloTap* taps, int ntaps,
-             const float* bias, cudaStream_t st, bool filter_mn = false, float* stats = nullptr,
-             const float* stats_shift = nullptr, int* stats_rows = nullptr) {
+             const float* bias, cudaStream_t st, bool filter_mn = false) {
   if (ntaps < 2 || ntaps > kMaxTaps) return MB_ERR_UNSUPPORTED;
   int min_dh = taps[0].dh, max_dh = taps[0].dh, min_dw = taps[0].dw, max_dw = taps[0].dw;
   for (int t = 1; t < ntaps; ++t) {
@@ -273,14 +272,10 @@ int run_halo(const char* who, const float* in, int Cin, int Win, int Hin, const 
   }
   p.acc_bufs = 2 * p.MT * p.BN <= 512 ? 2 : 1;
   p.prof = g_conv_prof;
-  p.stats = stats;
-  p.stats_shift = stats_shift;
-  p.Q = Qo; p.P = Po; p.Nimg = N;
-  const size_t stats_bytes = stats ? (static_cast<size_t>(2) * Kout + 256) * sizeof(float) : 0;
   p.a_stages = 2;
   const size_t a_slot = static_cast<size_t>(p.a_rows_alloc) * 128, b_slot = static_cast<size_t>(p.BN) * 128;
   const size_t staging = (static_cast<size_t>(p.out_rows) * 128 + 1023) / 1024 * 1024;
-  const size_t budget = 222 * 1024 - 2048 - stats_bytes;
+  const size_t budget = 222 * 1024 - 2048;
   if (2 * a_slot + staging + 2 * b_slot > budget) return MB_ERR_UNSUPPORTED;
   int bs = static_cast<int>((budget - 2 * a_slot - staging) / b_slot);
   if (bs > 16) bs = 16;
@@ -288,7 +283,7 @@ int run_halo(const char* who, const float* in, int Cin, int Win, int Hin, const 
   const long long items = static_cast<long long>(p.tiles_h) * p.tiles_n * p.tiles_c;
   if (items > 0x7fffffffLL) return MB_ERR_UNSUPPORTED;
   p.num_items = static_cast<int>(items);
-  const size_t smem = 512 + 1024 + 2 * a_slot + bs * b_slot + staging + stats_bytes;
+  const size_t smem = 512 + 1024 + 2 * a_slot + bs * b_slot + staging;
 
   CUtensorMap ma, mb_, mo;
   const long long C4 = static_cast<long long>(Cin) * 4, K4 = static_cast<long long>(Kout) * 4;
@@ -303,7 +298,6 @@ int run_halo(const char* who, const float* in, int Cin, int Win, int Hin, const 
   static const int attr_rc = raise_smem_limit(who, conv_gemm_halo);
   if (attr_rc) return attr_rc;
   const int grid = p.num_items < kNumSMs ? p.num_items : kNumSMs;
-  if (stats_rows) *stats_rows = grid;
   conv_gemm_halo<<<grid, 192, smem, st>>>(ma, mb_, mo, p);
   return after_launch("conv_gemm_halo");
 }
@@ -700,22 +694,19 @@ static int fprop_impl(const char* who, const float* x, const float* w, const flo
   (void)workspace; (void)workspace_bytes;
 
   if (d->stride_h == 1 && d->stride_w == 1 && d->R * d->S > 1) {
+    // the halo kernels have no statistics warps: the caller falls back to the plain pair
+    if (stats) return fail(MB_ERR_UNSUPPORTED, "%s: no output statistics for stride-1 multi-tap filters", who);
     HaloTap taps[kMaxTaps];
     int nt = 0;
     for (int r = 0; r < d->R; ++r)
       for (int s = 0; s < d->S; ++s)
         taps[nt++] = HaloTap{r * d->dil_h - d->pad_h, s * d->dil_w - d->pad_w, r * d->S + s};
-    // the swapped-operand kernel has no staging buffer to take statistics from: with them
-    // wanted, its layers (65..128 output channels) go through the plain halo kernel
-    if (!stats) {
-      rc = run_halo_swapped(who, x, d->C, d->W, d->H, w, d->R * d->S, y, d->K, d->Q, d->P, d->N, taps,
-                            nt, bias, as_stream(stream), false);
-      if (rc != MB_ERR_UNSUPPORTED) return rc;
-    }
-    rc = run_halo(who, x, d->C, d->W, d->H, w, d->R * d->S, y, d->K, d->Q, d->P, d->N, taps, nt, bias,
-                  as_stream(stream), false, stats, stats_shift, stats_rows);
+    rc = run_halo_swapped(who, x, d->C, d->W, d->H, w, d->R * d->S, y, d->K, d->Q, d->P, d->N, taps, nt,
+                          bias, as_stream(stream), false);
     if (rc != MB_ERR_UNSUPPORTED) return rc;
-    if (stats) return fail(MB_ERR_UNSUPPORTED, "%s: no output statistics for this stride-1 multi-tap geometry", who);
+    rc = run_halo(who, x, d->C, d->W, d->H, w, d->R * d->S, y, d->K, d->Q, d->P, d->N, taps, nt, bias,
+                  as_stream(stream));
+    if (rc != MB_ERR_UNSUPPORTED) return rc;
   }
   GemmLaunch L;
   std::memset(&L.p, 0, sizeof(L.p));

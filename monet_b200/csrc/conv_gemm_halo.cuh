@@ -39,11 +39,6 @@ struct HaloParams {
   int acc_bufs;              // 1 or 2 accumulator sets in tensor memory
   int b_mn;                  // 1: MN-major filter tiles (see GemmParams)
   long long* prof;           // optional: 16 cycle counters written by CTA 0 (diagnostics), or null
-  float* stats;              // optional per-CTA partial sums [2][gridDim.x][Kout] of the output (see
-                             // GemmParams), taken by the epilogue warps themselves: this kernel is
-                             // bound by its MMAs and the epilogue has time to spare
-  const float* stats_shift;
-  int Q, P, Nimg;            // output extent, to tell real pixels from halo rows for the statistics
   short tap_off[kMaxTaps];   // operand row offset of each tap
   unsigned char btap[kMaxTaps];
 };
@@ -69,8 +64,6 @@ conv_gemm_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
   const uint32_t a_region = a_slot_bytes * p.a_stages;
   const uint32_t b_region = b_slot_bytes * p.b_stages;
   uint8_t* stage_out = base_ptr + a_region + b_region;              // out_rows * 128 bytes
-  float* s_stats = reinterpret_cast<float*>(stage_out + (static_cast<size_t>(p.out_rows) * 128 + 1023) / 1024 * 1024);
-  float* row_ok = s_stats + 2 * p.Kout;                             // [256], 1 = real output pixel
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t acc_cols = static_cast<uint32_t>(p.MT * p.BN);
@@ -215,14 +208,6 @@ conv_gemm_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     bool ok = true;
     int it = 0;
     long long w_full = 0, t_store = 0;
-    if (p.stats) {
-      for (int i = threadIdx.x; i < 2 * p.Kout; i += 128) s_stats[i] = 0.f;
-      named_barrier(1, 128);
-    }
-    // statistics: warp w owns columns 8w .. 8w+7 of a chunk, lane l column 8w + (l & 7) over the
-    // rows of group l >> 3 (a quarter of the staged rows, visited in a rotated order so that the
-    // four groups read different banks); every output column has one owning thread
-    const int st_c = 8 * warp + (lane & 7), st_grp = lane >> 3;
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++it) {
       const int acc = p.acc_bufs == 2 ? (it & 1) : 0;
       const uint32_t acc_phase = p.acc_bufs == 2 ? ((it >> 1) & 1u) : (it & 1u);
@@ -238,16 +223,6 @@ conv_gemm_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) +
                              static_cast<uint32_t>(acc) * acc_cols;
-      if (p.stats) {
-        // row m of the store box {Wh, Hout, bn} is a real output pixel only inside Q x P x N
-        // (written once every warp has left the previous tile's last walk, read after the
-        // barriers of the first chunk)
-        named_barrier(1, 128);
-        for (int m = threadIdx.x; m < p.MT * kTileM; m += 128) {
-          const int wi = m % p.Wh, hi = (m / p.Wh) % p.Hout, ni = m / (p.Wh * p.Hout);
-          row_ok[m] = (m < p.out_rows && wi < p.Q && hi < p.bh && p0 + hi < p.P && n0 + ni < p.Nimg) ? 1.f : 0.f;
-        }
-      }
       for (int col = 0; col < p.BN && c0 + col < p.Kout; col += 32) {
         if (threadIdx.x == 0) tma_store_wait_read<0>();   // the previous store has read the staging
         named_barrier(1, 128);
@@ -275,31 +250,6 @@ conv_gemm_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
           tma_store_4d(&mapOut, stage_out, c0 + col, 0, p0, n0);
           tma_store_commit();
         }
-        if (p.stats) {
-          const int k = c0 + col + st_c;
-          const float kk = (p.stats_shift && k < p.Kout) ? __ldg(p.stats_shift + k) : 0.f;
-          const int rows_per = (p.MT * kTileM) / 4;          // 32 or 64 rows per group
-          const int r0 = st_grp * rows_per;
-          float s1 = 0.f, s2 = 0.f;
-          for (int i = 0; i < rows_per; ++i) {
-            const int r = r0 + (i & ~7) + ((i + 2 * st_grp) & 7);
-            if (r < p.out_rows && row_ok[r] != 0.f) {
-              const float v = *reinterpret_cast<const float*>(
-                  stage_out + r * 128 + (((st_c >> 2) ^ (r & 7)) << 4) + ((st_c & 3) << 2));
-              const float d = v - kk;
-              s1 += d;
-              s2 = fmaf(d, d, s2);
-            }
-          }
-          s1 += __shfl_xor_sync(0xffffffffu, s1, 8);
-          s2 += __shfl_xor_sync(0xffffffffu, s2, 8);
-          s1 += __shfl_xor_sync(0xffffffffu, s1, 16);
-          s2 += __shfl_xor_sync(0xffffffffu, s2, 16);
-          if (st_grp == 0 && k < p.Kout) {
-            s_stats[k] += s1;
-            s_stats[p.Kout + k] += s2;
-          }
-        }
       }
       tc_fence_before();
       mbar_arrive(&acc_empty[acc]);
@@ -307,15 +257,6 @@ conv_gemm_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     }
     if (prof && threadIdx.x == 0) { p.prof[6] = w_full; p.prof[7] = t_store; }
     if (threadIdx.x == 0) tma_store_wait_read<0>();
-    if (p.stats && ok) {
-      named_barrier(1, 128);
-      float* g1 = p.stats + static_cast<size_t>(blockIdx.x) * p.Kout;
-      float* g2 = p.stats + (static_cast<size_t>(gridDim.x) + blockIdx.x) * p.Kout;
-      for (int i = threadIdx.x; i < p.Kout; i += 128) {
-        g1[i] = s_stats[i];
-        g2[i] = s_stats[p.Kout + i];
-      }
-    }
     if (!ok && lane == 0) {
       *abort_flag = 1;
       atomicCAS(&g_conv_status, 0, 33);

@@ -693,15 +693,13 @@ def conv2d_fprop(x, w, bias, stride, padding, dilation, groups=1, variant: int =
     With ``want_stats`` returns ``(y, ChannelSums or None)``: the sums a following batch norm
     needs, accumulated beside the epilogue around ``stats_shift`` ([K] or None); None when this
     geometry has no such path (few-channel input, K not a multiple of 32, stride-1 multi-tap
-    filters with 65..128 output channels)."""
+    filters)."""
     _need_cuda(x, w, bias); _f32(x, "x"); _f32(w, "w")
     d0 = conv_desc(x.shape, w.shape, stride, padding, dilation, groups)
     geom = _smallc_geometry(d0)
     if want_stats:
-        # stride-1 multi-tap layers with 65..128 output channels run the swapped-operand kernel,
-        # which has no staging buffer to sum from: it is worth more than the statistics pass
-        swapped = d0.R * d0.S > 1 and d0.stride_h == 1 and d0.stride_w == 1 and 64 < d0.K <= 128
-        if geom is None and d0.K % 32 == 0 and groups == 1 and not swapped:
+        multi_tap_s1 = d0.R * d0.S > 1 and d0.stride_h == 1 and d0.stride_w == 1
+        if geom is None and d0.K % 32 == 0 and groups == 1 and not multi_tap_s1:
             d = _padded_desc(d0)
             if d.K == d0.K:
                 xa, wk = _act_nhwc(x), _filter_krsc(w)
