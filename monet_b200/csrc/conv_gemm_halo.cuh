@@ -17,6 +17,8 @@
 // rows.  Two rings: one of halo boxes (per channel chunk), one of filter tiles
 // (per chunk and tap).  Roles as in conv_gemm.cuh.
 #pragma once
+#include <type_traits>
+
 #include "conv_gemm.cuh"
 
 namespace mb {
@@ -165,6 +167,66 @@ conv_gemm_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       int it = 0;
       long long w_af = 0, w_bf = 0, w_acc = 0;
       const long long t_start = prof ? clock64() : 0;
+      // 3x3 filters (every layer of the networks measured): the tap loop is unrolled with the tap
+      // offsets in registers, descriptors advance by their low word only and barriers are
+      // addressed by integer, so that few scalar instructions sit between two MMAs -- with
+      // the generic loop below the issuing thread, not the tensor pipe, set the pace.
+      auto issue_unrolled = [&](auto taps_c, auto mt_c) {
+        constexpr int TAPS = decltype(taps_c)::value;
+        constexpr int MTC = decltype(mt_c)::value;
+        uint32_t tap16[TAPS];                               // tap offsets in 16-byte units
+#pragma unroll
+        for (int t = 0; t < TAPS; ++t) tap16[t] = static_cast<uint32_t>(p.tap_off[t]) * 8u;
+        const uint64_t da0 = smem_desc_sw128(base0, 16, 1024);
+        const uint64_t db0 = p.b_mn ? smem_desc(base0 + a_region, 4096, 512, kSwizzle128BBase32B)
+                                    : smem_desc_sw128(base0 + a_region, 16, 1024);
+        const uint32_t a_hi = static_cast<uint32_t>(da0 >> 32), a_lo0 = static_cast<uint32_t>(da0);
+        const uint32_t b_hi = static_cast<uint32_t>(db0 >> 32), b_lo0 = static_cast<uint32_t>(db0);
+        const uint32_t a_stage16 = a_slot_bytes >> 4, b_stage16 = b_slot_bytes >> 4;
+        const uint32_t bs1 = b_step, bs2 = 2u * b_step, bs3 = 3u * b_step;
+        const uint32_t a_full_u = smem_u32(a_full), a_empty_u = smem_u32(a_empty);
+        const uint32_t b_full_u = smem_u32(b_full), b_empty_u = smem_u32(b_empty);
+        const uint32_t bn = static_cast<uint32_t>(p.BN);
+        for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++it) {
+          const int acc = p.acc_bufs == 2 ? (it & 1) : 0;
+          const uint32_t acc_phase = p.acc_bufs == 2 ? ((it >> 1) & 1u) : (it & 1u);
+          if (!timed_wait(&acc_empty[acc], acc_phase ^ 1u, w_acc)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d_base = tmem_base + static_cast<uint32_t>(acc) * acc_cols;
+          for (int kc = 0; ok && kc < p.kchunks; ++kc) {
+            if (!mbar_wait_u32(a_full_u + 8u * ra.stage, ra.phase, abort_flag)) { ok = false; break; }
+            const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(ra.stage) * a_stage16;
+#pragma unroll
+            for (int t = 0; t < TAPS; ++t) {
+              if (!mbar_wait_u32(b_full_u + 8u * rb.stage, rb.phase, abort_flag)) { ok = false; break; }
+              tc_fence_after();
+              const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(rb.stage) * b_stage16;
+#pragma unroll
+              for (int mt = 0; mt < MTC; ++mt) {
+                const uint32_t al = a_lo + static_cast<uint32_t>(mt * kTileM * 8) + tap16[t];
+                const uint32_t dt = d_base + static_cast<uint32_t>(mt) * bn;
+                if (t == 0)
+                  mma_tf32(dt, pack64(al, a_hi), pack64(b_lo, b_hi), idesc, kc != 0 ? 1u : 0u);
+                else
+                  mma_tf32_acc(dt, pack64(al, a_hi), pack64(b_lo, b_hi), idesc);
+                mma_tf32_acc(dt, pack64(al + 2u, a_hi), pack64(b_lo + bs1, b_hi), idesc);
+                mma_tf32_acc(dt, pack64(al + 4u, a_hi), pack64(b_lo + bs2, b_hi), idesc);
+                mma_tf32_acc(dt, pack64(al + 6u, a_hi), pack64(b_lo + bs3, b_hi), idesc);
+              }
+              mma_commit_u32(b_empty_u + 8u * rb.stage);
+              rb.advance();
+            }
+            if (ok) mma_commit_u32(a_empty_u + 8u * ra.stage);
+            ra.advance();
+          }
+          if (ok) mma_commit(&acc_full[acc]);
+        }
+      };
+      if (p.num_taps == 9 && p.MT == 2 && !prof)
+        issue_unrolled(std::integral_constant<int, 9>{}, std::integral_constant<int, 2>{});
+      else if (p.num_taps == 9 && p.MT == 1 && !prof)
+        issue_unrolled(std::integral_constant<int, 9>{}, std::integral_constant<int, 1>{});
+      else
       for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++it) {
         const int acc = p.acc_bufs == 2 ? (it & 1) : 0;
         const uint32_t acc_phase = p.acc_bufs == 2 ? ((it >> 1) & 1u) : (it & 1u);

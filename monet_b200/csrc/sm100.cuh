@@ -60,6 +60,33 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
   return true;
 }
 
+// The same wait on a barrier given by its 32-bit shared-memory address: the MMA-issuing thread
+// keeps barrier addresses as integers so that no generic-to-shared conversion sits between two
+// MMAs.
+__device__ __forceinline__ bool mbar_try_wait_u32(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n"
+      " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      " selp.b32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_u32(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait_u32(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (!mbar_try_wait_u32(bar, parity)) {
+    if ((++spins & 1023u) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitLimitCycles) return false;
+    }
+  }
+  return true;
+}
+
 // The same bounded wait built on the non-blocking test_wait: try_wait may park the thread for a
 // system-defined time, which is fine for deep pipelines but adds hundreds of cycles to a
 // hand-shake that sits on a critical path.
@@ -187,6 +214,28 @@ __device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t desc_a, uint6
       " setp.ne.b32 p, %4, 0;\n"
       " tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The same with the descriptors given as (low word, high word) and the accumulate flag fixed at
+// one: the issuing thread advances only the low word (the 14-bit start-address field), and no
+// predicate has to be computed.
+__device__ __forceinline__ uint64_t pack64(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+__device__ __forceinline__ void mma_tf32_acc(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                             uint32_t idesc) {
+  asm volatile(
+      "{\n .reg .pred p;\n"
+      " setp.eq.b32 p, 0, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit_u32(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
       : "memory");
 }
 // Arrives on `bar` once every MMA issued so far by this thread has completed.
