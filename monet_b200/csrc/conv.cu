@@ -13,7 +13,6 @@
 //   wgrad  dw = x (*) dy, db = sum dy   see conv_wgrad.cuh
 #include "conv_gemm.cuh"
 #include "conv_gemm_halo.cuh"
-#include "conv_gemm_halo_swap.cuh"
 #include "conv_wgrad.cuh"
 #include "conv_wgrad_halo.cuh"
 
@@ -263,6 +262,18 @@ int run_halo(const char* who, const float* in, int Cin, int Win, int Hin, const 
   p.Kout = Kout;
   p.BN = Kout >= 256 ? 256 : round_up(Kout, 32);
   p.tiles_c = (Kout + p.BN - 1) / p.BN;
+  if (p.BN == 256) {
+    // 128-column tiles when they fill the SMs' rounds better: an M = 128 MMA takes about 140
+    // cycles with 256 columns and 86 with 128 in this kernel, and a round costs its MMAs
+    const long long pix_items = static_cast<long long>(p.tiles_h) * ((N + p.bn - 1) / p.bn);
+    const long long rounds256 = (pix_items * p.tiles_c + kNumSMs - 1) / kNumSMs;
+    const int tiles128 = (Kout + 127) / 128;
+    const long long rounds128 = (pix_items * tiles128 + kNumSMs - 1) / kNumSMs;
+    if (rounds128 * 86 < rounds256 * 140) {
+      p.BN = 128;
+      p.tiles_c = tiles128;
+    }
+  }
   p.kchunks = (Cin + kChunkK - 1) / kChunkK;
   p.num_taps = ntaps;
   p.org_w = min_dw; p.org_h = min_dh;
@@ -300,96 +311,6 @@ int run_halo(const char* who, const float* in, int Cin, int Win, int Hin, const 
   const int grid = p.num_items < kNumSMs ? p.num_items : kNumSMs;
   conv_gemm_halo<<<grid, 192, smem, st>>>(ma, mb_, mo, p);
   return after_launch("conv_gemm_halo");
-}
-
-// Few output channels (64 < Kout <= 128, a multiple of 32): the swapped-operand halo kernel
-// (conv_gemm_halo_swap.cuh).  Same tile geometry as run_halo.  `filter_mn`: `filt` is the
-// original [Cin][taps][Kout]-ordered filter of a backward-data pass read in place.
-int run_halo_swapped(const char* who, const float* in, int Cin, int Win, int Hin, const float* filt,
-                     int T, float* out, int Kout, int Qo, int Po, int N, const HaloTap* taps, int ntaps,
-                     const float* bias, cudaStream_t st, bool filter_mn) {
-  // measured on 3x3 layers: 128 output channels 22 % faster than conv_gemm_halo, 64 channels
-  // equal at best (only two epilogue warps have channels, and the layer is near its HBM time)
-  if (ntaps < 2 || ntaps > kMaxTaps || Kout > kTileM || Kout <= 64 || Kout % 32) return MB_ERR_UNSUPPORTED;
-  if (static_cast<long long>(N) * Po * Qo > 0x7fffffffLL) return MB_ERR_UNSUPPORTED;
-  int min_dh = taps[0].dh, max_dh = taps[0].dh, min_dw = taps[0].dw, max_dw = taps[0].dw;
-  for (int t = 1; t < ntaps; ++t) {
-    if (taps[t].dh < min_dh) min_dh = taps[t].dh;
-    if (taps[t].dh > max_dh) max_dh = taps[t].dh;
-    if (taps[t].dw < min_dw) min_dw = taps[t].dw;
-    if (taps[t].dw > max_dw) max_dw = taps[t].dw;
-  }
-  const int halo_h = max_dh - min_dh, halo_w = max_dw - min_dw;
-  HaloSwapParams p;
-  std::memset(&p, 0, sizeof(p));
-  p.Wh = Qo + halo_w;
-  if (p.Wh > 256) return MB_ERR_UNSUPPORTED;
-  const int rows_cap = 2 * kTileM;
-  if ((Po + halo_h) * p.Wh <= rows_cap) {        // whole (padded) images, several per item
-    p.Hb = Po + halo_h;
-    p.bn = rows_cap / (p.Hb * p.Wh);
-    if (p.bn > N) p.bn = N;
-    p.bh = Po;
-    p.tiles_h = 1;
-    p.Hout = p.bn > 1 ? p.Hb : p.bh;
-  } else {
-    p.bn = 1;
-    const int bh_max = rows_cap / p.Wh;
-    if (bh_max < 1) return MB_ERR_UNSUPPORTED;
-    p.tiles_h = (Po + bh_max - 1) / bh_max;
-    p.bh = (Po + p.tiles_h - 1) / p.tiles_h;
-    p.Hb = p.bh + halo_h;
-    p.Hout = p.bh;
-  }
-  if (p.Hb > 256) return MB_ERR_UNSUPPORTED;
-  p.tiles_n = (N + p.bn - 1) / p.bn;
-  p.box_rows = p.Wh * p.Hb * p.bn;
-  p.out_rows = p.Wh * p.Hout * p.bn;
-  const int span = ((p.bn - 1) * p.Hb + p.bh) * p.Wh;
-  const int mt = ((span > p.out_rows ? span : p.out_rows) + kTileM - 1) / kTileM;
-  if (mt > 2) return MB_ERR_UNSUPPORTED;
-  p.ncols = mt * kTileM;
-  const int max_off = halo_h * p.Wh + halo_w;
-  int need_rows = p.ncols + max_off;
-  if (need_rows < p.box_rows) need_rows = p.box_rows;
-  p.a_rows_alloc = (need_rows + 7) / 8 * 8;
-  p.out = out;
-  p.bias = bias;
-  p.Kout = Kout;
-  p.Q = Qo; p.P = Po; p.Nimg = N;
-  p.kchunks = (Cin + kChunkK - 1) / kChunkK;
-  p.num_taps = ntaps;
-  p.org_w = min_dw; p.org_h = min_dh;
-  for (int t = 0; t < ntaps; ++t) {
-    p.tap_off[t] = static_cast<short>((taps[t].dh - min_dh) * p.Wh + (taps[t].dw - min_dw));
-    p.btap[t] = static_cast<unsigned char>(taps[t].btap);
-  }
-  p.f_mn = filter_mn ? 1 : 0;
-  p.act_stages = 2;
-  const size_t act_slot = static_cast<size_t>(p.a_rows_alloc) * 128, f_slot = static_cast<size_t>(Kout) * 128;
-  const size_t fixed = 512 + 1024 + 2 * act_slot + 16384 + 1024;    // control, alignment, halo ring, spare tile, table
-  const size_t budget = 225 * 1024;
-  if (fixed + 2 * f_slot > budget) return MB_ERR_UNSUPPORTED;
-  int fs = static_cast<int>((budget - fixed) / f_slot);
-  if (fs > 16) fs = 16;
-  p.f_stages = fs;
-  const long long items = static_cast<long long>(p.tiles_h) * p.tiles_n;
-  if (items > 0x7fffffffLL) return MB_ERR_UNSUPPORTED;
-  p.num_items = static_cast<int>(items);
-  const size_t smem = fixed + fs * f_slot;
-
-  CUtensorMap ma, mf;
-  const long long C4 = static_cast<long long>(Cin) * 4;
-  int rc = encode_act(who, &ma, in, Cin, Win, Hin, N, C4, C4 * Win, C4 * Win * Hin, p.Wh, p.Hb, p.bn);
-  if (rc) return rc;
-  rc = filter_mn ? encode_filter_mn(who, &mf, filt, Cin, T, Kout, Kout)
-                 : encode_filter(who, &mf, filt, Cin, T, Kout, Kout);
-  if (rc) return rc;
-  static const int attr_rc = raise_smem_limit(who, conv_gemm_halo_swapped);
-  if (attr_rc) return attr_rc;
-  const int grid = p.num_items < kNumSMs ? p.num_items : kNumSMs;
-  conv_gemm_halo_swapped<<<grid, 192, smem, st>>>(ma, mf, p);
-  return after_launch("conv_gemm_halo_swapped");
 }
 
 int floordiv(int a, int b) { return (a >= 0) ? a / b : -((-a + b - 1) / b); }
@@ -701,9 +622,6 @@ static int fprop_impl(const char* who, const float* x, const float* w, const flo
     for (int r = 0; r < d->R; ++r)
       for (int s = 0; s < d->S; ++s)
         taps[nt++] = HaloTap{r * d->dil_h - d->pad_h, s * d->dil_w - d->pad_w, r * d->S + s};
-    rc = run_halo_swapped(who, x, d->C, d->W, d->H, w, d->R * d->S, y, d->K, d->Q, d->P, d->N, taps, nt,
-                          bias, as_stream(stream), false);
-    if (rc != MB_ERR_UNSUPPORTED) return rc;
     rc = run_halo(who, x, d->C, d->W, d->H, w, d->R * d->S, y, d->K, d->Q, d->P, d->N, taps, nt, bias,
                   as_stream(stream));
     if (rc != MB_ERR_UNSUPPORTED) return rc;
@@ -853,11 +771,6 @@ int mb_conv2d_dgrad(const float* dy, const float* w, float* dx, const mb_conv_de
     for (int r = 0; r < d->R; ++r)
       for (int s = 0; s < d->S; ++s)
         taps[nt++] = HaloTap{d->pad_h - r * d->dil_h, d->pad_w - s * d->dil_w, r * d->S + s};
-    if (filter_mn) {
-      rc = run_halo_swapped(who, dy, d->K, d->Q, d->P, wt, T, dx, d->C, d->W, d->H, d->N, taps, nt,
-                            nullptr, st, true);
-      if (rc != MB_ERR_UNSUPPORTED) return rc;
-    }
     rc = run_halo(who, dy, d->K, d->Q, d->P, wt, T, dx, d->C, d->W, d->H, d->N, taps, nt, nullptr, st,
                   filter_mn);
     if (rc != MB_ERR_UNSUPPORTED) return rc;

@@ -279,7 +279,8 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
     // ---------------------------------------------------------------- epilogue
     bool ok = true;
     int it = 0;
-    int chunk_no = 0;             // counts staged 32-column chunks (selects the staging buffer)
+    int bsel = 0;                 // staging buffer of the next 32-column chunk ...
+    uint32_t bphase = 0;          // ... and how many times (mod 2) the buffers have gone round
     for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
@@ -312,13 +313,12 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
           float v[32];
           tmem_ld32(t_row + col, v);
           tmem_ld_wait();
-          const int bsel = chunk_no % nbuf;
           uint8_t* buf = stage_out + static_cast<size_t>(bsel) * kAStageBytes;
           if (threadIdx.x == 0) {
             // the store that last read `buf` is done ...
             if (p.stats) tma_store_wait_read<2>(); else tma_store_wait_read<1>();
             // ... and so are the statistics warps (first use of a buffer passes at once)
-            if (p.stats && !mbar_wait_spin(&stat_empty[bsel], ((chunk_no / 3) & 1u) ^ 1u, abort_flag)) {
+            if (p.stats && !mbar_wait_spin(&stat_empty[bsel], bphase ^ 1u, abort_flag)) {
               *abort_flag = 1;
               atomicCAS(&g_conv_status, 0, 4);
             }
@@ -341,7 +341,10 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
             tma_store_commit();
             if (p.stats) mbar_arrive(&stat_full[bsel]);   // staged chunk visible to warps 6-13
           }
-          ++chunk_no;
+          if (++bsel == nbuf) {      // (a counter, not chunk number % nbuf: a runtime modulo here
+            bsel = 0;                //  sat on every chunk's critical path)
+            bphase ^= 1u;
+          }
         }
       } else {
         for (int col = 0; col < p.BN && c0 + col < p.Kout; col += 32) {

@@ -222,9 +222,9 @@ conv_gemm_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
           if (ok) mma_commit(&acc_full[acc]);
         }
       };
-      if (p.num_taps == 9 && p.MT == 2 && !prof)
+      if (p.num_taps == 9 && p.MT == 2)
         issue_unrolled(std::integral_constant<int, 9>{}, std::integral_constant<int, 2>{});
-      else if (p.num_taps == 9 && p.MT == 1 && !prof)
+      else if (p.num_taps == 9 && p.MT == 1)
         issue_unrolled(std::integral_constant<int, 9>{}, std::integral_constant<int, 1>{});
       else
       for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++it) {
