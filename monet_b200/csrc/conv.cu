@@ -172,7 +172,9 @@ int launch_gemm(const char* who, GemmLaunch& L, cudaStream_t st) {
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(conv_gemm_kmajor, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    attr_err = cudaFuncSetAttribute(conv_gemm_kmajor<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(conv_gemm_kmajor<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
   });
   if (attr_err != cudaSuccess)
     return fail(MB_ERR_LAUNCH, "%s: cannot raise the shared-memory limit: %s", who, cudaGetErrorString(attr_err));
@@ -195,7 +197,10 @@ int launch_gemm(const char* who, GemmLaunch& L, cudaStream_t st) {
   if (L.p.stats && !L.p.tma_store)
     return fail(MB_ERR_UNSUPPORTED, "%s: output statistics need the TMA-store epilogue", who);
   // warps 6-13 exist only when the per-channel sums of the output are wanted
-  conv_gemm_kmajor<<<L.grid, L.p.stats ? 448 : 192, L.smem, st>>>(L.a[0], L.a[1], L.a[2], L.a[3], L.b, L.out, L.p);
+  if (L.p.stats)
+    conv_gemm_kmajor<true><<<L.grid, 448, L.smem, st>>>(L.a[0], L.a[1], L.a[2], L.a[3], L.b, L.out, L.p);
+  else
+    conv_gemm_kmajor<false><<<L.grid, 192, L.smem, st>>>(L.a[0], L.a[1], L.a[2], L.a[3], L.b, L.out, L.p);
   return after_launch(who);
 }
 

@@ -84,7 +84,10 @@ struct Ring {
 
 }  // namespace detail
 
-__global__ void __launch_bounds__(448, 1)
+// kStats: the instantiation with the statistics warps (448 threads); the plain one has none of
+// their code and keeps the 192-thread launch bound.
+template <bool kStats>
+__global__ void __launch_bounds__(kStats ? 448 : 192, 1)
 conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUtensorMap mapA1,
                  const __grid_constant__ CUtensorMap mapA2, const __grid_constant__ CUtensorMap mapA3,
                  const __grid_constant__ CUtensorMap mapB, const __grid_constant__ CUtensorMap mapOut,
@@ -103,7 +106,7 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
   uint64_t* stat_empty = stat_full + 3;                               // [3] statistics warps are done with the buffer
   // staging buffers of the TMA-store epilogue: a third one when statistics warps read them too,
   // so that those warps have two chunk periods to finish with a buffer
-  const int nbuf = p.stats ? 3 : 2;
+  constexpr int nbuf = kStats ? 3 : 2;
   const uint32_t slots0 = (smem_u32(smem_raw) + 512u + 1023u) & ~1023u;
   const uint32_t b_stage_bytes = static_cast<uint32_t>(p.BN) * 128u;
   const uint32_t stage_bytes = kAStageBytes + b_stage_bytes;
@@ -139,7 +142,7 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
     tmem_alloc(tmem_slot, tmem_cols);
     tmem_relinquish();
   }
-  if (p.stats) {
+  if (kStats) {
     // per-CTA sums start at zero; row_dec[m] = (w, h, n) of tile row m packed 10 bits each, or
     // -1 for rows past the pixel box (the same for every tile of this launch)
     for (int i = threadIdx.x; i < 2 * p.Kout; i += blockDim.x) s_stats[i] = 0.f;
@@ -203,8 +206,7 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
             uint8_t* slot = slots_ptr + static_cast<size_t>(ring.stage) * stage_bytes;
             if (lane == 0)
               tma_load_4d(ma, slot, &full[ring.stage], kc * kChunkK, cw, ch, n0);
-            else if (lane == 1)
-{
+            else if (lane == 1) {
               if (p.b_mn)
                 tma_load_4d(&mapB, slot + kAStageBytes, &full[ring.stage], 0, kc * kChunkK, bt, c0 / 32);
               else
@@ -259,8 +261,9 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
           tc_fence_after();
           const uint32_t a_addr = slots0 + static_cast<uint32_t>(ring.stage) * stage_bytes;
           const uint64_t da = smem_desc_sw128(a_addr, 16, 1024);
-          const uint64_t db = p.b_mn ? smem_desc(a_addr + kAStageBytes, 4096, 512, kSwizzle128BBase32B)
-                                     : smem_desc_sw128(a_addr + kAStageBytes, 16, 1024);
+          const uint32_t b_addr = a_addr + kAStageBytes;
+          const uint64_t db = p.b_mn ? smem_desc(b_addr, 4096, 512, kSwizzle128BBase32B)
+                                     : smem_desc_sw128(b_addr, 16, 1024);
 #pragma unroll
           for (int k = 0; k < 4; ++k)   // 4 x K=8 per 32-channel chunk, 32 bytes apart
             mma_tf32(d_tmem, da + 2u * k, db + b_step * k, idesc, (kb | k) != 0 ? 1u : 0u);
@@ -316,9 +319,9 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
           uint8_t* buf = stage_out + static_cast<size_t>(bsel) * kAStageBytes;
           if (threadIdx.x == 0) {
             // the store that last read `buf` is done ...
-            if (p.stats) tma_store_wait_read<2>(); else tma_store_wait_read<1>();
+            if (kStats) tma_store_wait_read<2>(); else tma_store_wait_read<1>();
             // ... and so are the statistics warps (first use of a buffer passes at once)
-            if (p.stats && !mbar_wait_spin(&stat_empty[bsel], bphase ^ 1u, abort_flag)) {
+            if (kStats && !mbar_wait_spin(&stat_empty[bsel], bphase ^ 1u, abort_flag)) {
               *abort_flag = 1;
               atomicCAS(&g_conv_status, 0, 4);
             }
@@ -339,7 +342,7 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
           if (threadIdx.x == 0) {
             tma_store_4d(&mapOut, buf, c0 + col, q0, p0, n0);
             tma_store_commit();
-            if (p.stats) mbar_arrive(&stat_full[bsel]);   // staged chunk visible to warps 6-13
+            if (kStats) mbar_arrive(&stat_full[bsel]);   // staged chunk visible to warps 6-13
           }
           if (++bsel == nbuf) {      // (a counter, not chunk number % nbuf: a runtime modulo here
             bsel = 0;                //  sat on every chunk's critical path)
@@ -376,7 +379,7 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
       *abort_flag = 1;
       atomicCAS(&g_conv_status, 0, 3);
     }
-  } else if (p.stats) {
+  } else if (kStats) {
     // ------------------------------------------------------------- statistics (warps 6-13)
     // Warp w owns columns 4w .. 4w+3 of every staged 32-column chunk, all 128 rows: lane l sums
     // column 4w + (l & 3) over the 16 rows of group l >> 2 (rows visited in a per-group rotated
@@ -417,7 +420,9 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
         const int kn = c0 + col + 32 + c;
         const float kk_next = (p.stats_shift && col + 32 < p.BN && kn < p.Kout) ? __ldg(p.stats_shift + kn) : 0.f;
         int got = 1;
-        if (lane == 0) got = mbar_wait_spin(&stat_full[b], (chunk_no / 3) & 1u, abort_flag) ? 1 : 0;
+        // (try_wait, which parks the lane, not a spin: eight spinning warps would take issue slots
+        //  and shared-memory cycles from the epilogue warps; three staging buffers hide the wake-up)
+        if (lane == 0) got = mbar_wait(&stat_full[b], (chunk_no / 3) & 1u, abort_flag) ? 1 : 0;
         got = __shfl_sync(0xffffffffu, got, 0);
         if (!got) {
           ok = false;
