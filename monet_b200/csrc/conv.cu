@@ -700,7 +700,7 @@ static int fprop_impl(const char* who, const float* x, const float* w, const flo
   const long long tiles_n = (p.Nimg + ts.bn - 1) / ts.bn;
   const long long m_tiles = static_cast<long long>(p.tiles_w) * p.tiles_h * tiles_n;
   pick_bn_stages(d->K, m_tiles, &p.BN, &p.stages, &L.smem,
-                 stats ? kAStageBytes + (static_cast<size_t>(2) * d->K + 128) * sizeof(float) : 0);
+                 stats ? kAStageBytes + (static_cast<size_t>(3) * d->K + 128) * sizeof(float) : 0);
   p.tiles_c = (d->K + p.BN - 1) / p.BN;
   const long long tiles = m_tiles * p.tiles_c;
   if (tiles > 0x7fffffffLL) return fail(MB_ERR_UNSUPPORTED, "%s: too many tiles", who);

@@ -115,6 +115,7 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
   uint8_t* stage_out = slots_ptr + static_cast<size_t>(p.stages) * stage_bytes;
   float* s_stats = reinterpret_cast<float*>(stage_out + 3 * kAStageBytes);   // [2][Kout] when p.stats
   int* row_dec = reinterpret_cast<int*>(s_stats + 2 * p.Kout);               // [128] when p.stats
+  float* s_shift = reinterpret_cast<float*>(row_dec + kTileM);               // [Kout] when p.stats: the shift, read once
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // two accumulators of BN columns; the epilogue reads whole 32-column groups, so the
@@ -146,6 +147,7 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
     // per-CTA sums start at zero; row_dec[m] = (w, h, n) of tile row m packed 10 bits each, or
     // -1 for rows past the pixel box (the same for every tile of this launch)
     for (int i = threadIdx.x; i < 2 * p.Kout; i += blockDim.x) s_stats[i] = 0.f;
+    for (int i = threadIdx.x; i < p.Kout; i += blockDim.x) s_shift[i] = p.stats_shift ? __ldg(p.stats_shift + i) : 0.f;
     for (int m = threadIdx.x; m < kTileM; m += blockDim.x) {
       const int wi = m % p.bw, hi = (m / p.bw) % p.bh, ni = m / (p.bw * p.bh);
       row_dec[m] = m < p.bn * p.bh * p.bw ? (wi | (hi << 10) | (ni << 20)) : -1;
@@ -414,11 +416,11 @@ conv_gemm_kmajor(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
         mask |= (valid ? 1u : 0u) << i;
       }
       // the shift of the next chunk is fetched while this one is walked
-      float kk = (p.stats_shift && c0 + c < p.Kout) ? __ldg(p.stats_shift + c0 + c) : 0.f;
+      float kk = c0 + c < p.Kout ? s_shift[c0 + c] : 0.f;
       for (int col = 0; col < p.BN && c0 + col < p.Kout; col += 32) {
         const int b = chunk_no % 3;
         const int kn = c0 + col + 32 + c;
-        const float kk_next = (p.stats_shift && col + 32 < p.BN && kn < p.Kout) ? __ldg(p.stats_shift + kn) : 0.f;
+        const float kk_next = (col + 32 < p.BN && kn < p.Kout) ? s_shift[kn] : 0.f;
         int got = 1;
         // (try_wait, which parks the lane, not a spin: eight spinning warps would take issue slots
         //  and shared-memory cycles from the epilogue warps; three staging buffers hide the wake-up)
