@@ -588,3 +588,56 @@ class Runner:
                 self._vals[t] = None
         if self._vals.get(node_id) is not None and self._need.get(node_id, node_id) >= node_id:
             self._vals[node_id] = None
+
+
+class GraphedStep:
+    """One whole training step (forward, loss, backward, optimiser) captured as a CUDA graph.
+
+    The executor above is a Python loop over a few hundred nodes; it enqueues a ResNet-50 step in
+    about 12 ms whatever the batch size, which is hidden behind a large batch and dominant for a
+    small one.  The reference has the same per-node host loop (schedule.py:145-311) with a
+    synchronisation per operator on top.  A captured step replays all launches from one host
+    call; the batch and the target live in fixed buffers that ``__call__`` overwrites.
+
+    ``criterion`` has ``forward(output, target) -> loss`` and ``backward() -> grad_output``
+    (e.g. ``lm_ops.softmax.SoftmaxCrossEntropy``).  Gradients, the loss and every activation
+    are allocated in the graph's private pool during capture and keep their addresses.  The
+    schedule (what is kept, dropped, recomputed) is the runner's and is frozen by the capture.
+    """
+
+    def __init__(self, run: Runner, criterion, optimizer, example_input: torch.Tensor,
+                 example_target: torch.Tensor, warmup: int = 3):
+        if not example_input.is_cuda:
+            raise RuntimeError("GraphedStep needs CUDA tensors")
+        self.run, self.criterion, self.optimizer = run, criterion, optimizer
+        self.params = [p for g in optimizer.param_groups for p in g['params']]
+        self.input = example_input.clone()
+        self.target = example_target.clone()
+        # warm-up on a side stream (first calls raise shared-memory limits, fill workspaces and
+        # create the optimiser's state: none of that may happen during capture)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(max(warmup, 1)):
+                self._eager()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.loss = self._eager()
+
+    def _eager(self) -> torch.Tensor:
+        for p in self.params:
+            p.grad = None
+        out = self.run.forward(self.input)
+        loss = self.criterion.forward(out, self.target)
+        self.run.backward(self.criterion.backward())
+        self.optimizer.step()
+        return loss
+
+    def __call__(self, input_: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
+        """Runs one step on this batch; returns the loss tensor (overwritten by the next call)."""
+        self.input.copy_(input_, non_blocking=True)
+        self.target.copy_(target, non_blocking=True)
+        self.graph.replay()
+        return self.loss

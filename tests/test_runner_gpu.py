@@ -128,3 +128,58 @@ def test_low_memory_policy_keeps_less(cuda):
         for p in model.parameters():
             p.grad = None
     assert peaks["low_memory"] < peaks["store_all"], peaks
+
+
+@pytest.mark.parametrize("policy", ["low_memory", "budget_10gb"])
+def test_graphed_step_matches_eager(cuda, policy):
+    """A training step captured as a CUDA graph and replayed on new batches follows the same
+    trajectory as the executor called step by step (same kernels, same order)."""
+    from monet_b200 import runner
+    from monet_b200.lm_ops.softmax import SoftmaxCrossEntropy
+    cl = torch.channels_last
+    torch.manual_seed(11)
+    base = torchvision.models.resnet18(num_classes=10).train()
+    g = torch.Generator().manual_seed(5)
+    batches = [(torch.randn(4, 3, 64, 64, generator=g), torch.randint(0, 10, (4,), generator=g))
+               for _ in range(4)]
+
+    def make():
+        m = copy.deepcopy(base).to(cuda).to(memory_format=cl)
+        opt = torch.optim.SGD(m.parameters(), lr=0.05, momentum=0.9)
+        r = runner.Runner(m, getattr(runner, policy), fuse=True)
+        return m, opt, r
+
+    # eager trajectory; the graphed one spends its warm-up steps on the first batch too (the
+    # capture itself records the step without running it)
+    warm = 2
+    m1, opt1, r1 = make()
+    ce1 = SoftmaxCrossEntropy()
+    eager_losses = []
+    for i, (x, y) in enumerate([batches[0]] * warm + batches):
+        for p in m1.parameters():
+            p.grad = None
+        out = r1.forward(x.to(cuda).contiguous(memory_format=cl))
+        loss = ce1.forward(out, y.to(cuda))
+        r1.backward(ce1.backward())
+        opt1.step()
+        if i >= warm:
+            eager_losses.append(float(loss))
+
+    m2, opt2, r2 = make()
+    x0, y0 = batches[0]
+    gs = runner.GraphedStep(r2, SoftmaxCrossEntropy(), opt2,
+                            x0.to(cuda).contiguous(memory_format=cl), y0.to(cuda), warmup=warm)
+    graph_losses = []
+    for x, y in batches:
+        loss = gs(x.to(cuda).contiguous(memory_format=cl), y.to(cuda))
+        graph_losses.append(float(loss))
+    torch.cuda.synchronize()
+    assert all(l == l for l in graph_losses)
+    for a, b in zip(graph_losses, eager_losses):
+        assert abs(a - b) <= 2e-3 * max(1.0, abs(b)), (graph_losses, eager_losses)
+    # the weights after the same number of steps agree to accumulation-order noise
+    for (k, p1), (_, p2) in zip(m1.named_parameters(), m2.named_parameters()):
+        assert _rel(p2.detach(), p1.detach()) < 2e-2, k
+    for (k, b1), (_, b2) in zip(m1.named_buffers(), m2.named_buffers()):
+        if b1.is_floating_point():
+            assert _rel(b2, b1) < 2e-2, k
