@@ -32,6 +32,7 @@
 //   backward  through y = relu(bn(x) + r) from x and y: the reduce pass also forms the gated
 //             gradient d = (dy1 [+ dy2]) * (y > 0), writes it (it is the residual's gradient)
 //             and sums it, so the separate ReLU-backward pass disappears.
+#include <cstdlib>
 #include "common.cuh"
 
 #include <mutex>
@@ -92,6 +93,35 @@ size_t ws_floats(const Geometry& g) { return (2 * static_cast<size_t>(g.S) + 2) 
 
 enum { kFwd = 0, kBwd = 1, kBwdRelu = 2, kFwdRes = 3, kBwdGate = 4 };
 
+// ------------------------------------------- programmatic dependent launch
+// A batch-norm call is a chain of two or three short kernels (reduce, finalize, sweep), 138 times
+// per ResNet-50 step.  The dependent ones are launched with programmatic stream serialization:
+// they may become resident while their predecessor is still running and block in
+// `griddepcontrol.wait` (which returns once the predecessor grid has completed and its writes
+// are visible) before they touch memory, so the launch latency of each link overlaps the tail of
+// the previous one.  A kernel launched without the attribute sees `wait` as a no-op; a
+// predecessor that never triggers releases its dependents when it exits.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                             cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  // MB_NO_PDL=1 in the environment launches the chain with plain stream order (for A/B timing)
+  static const bool plain = std::getenv("MB_NO_PDL") != nullptr;
+  cfg.attrs = attr;
+  cfg.numAttrs = plain ? 0 : 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ------------------------------------------------------------- NHWC reduce
 // MODE kFwd: a = x;          accumulates (x-K), (x-K)^2
 // MODE kBwd: a = dy, b = v;  accumulates dy, dy*(v-p0)*p1
@@ -114,6 +144,7 @@ __global__ void __launch_bounds__(kBlock) bn_reduce_nhwc(const float* __restrict
                                                          float* dout = nullptr,
                                                          float act_hi = __builtin_huge_valf()) {
   extern __shared__ float sm[];  // [ty_n][tx_n][2*VEC]
+  pdl_trigger();                 // the finalize kernel may take its seats; it waits for this grid
   const int tx = threadIdx.x % tx_n, ty = threadIdx.x / tx_n;
   const int c0 = (blockIdx.y * tx_n + tx) * VEC;
   const bool live = c0 < C;
@@ -332,6 +363,8 @@ __global__ void __launch_bounds__(32 * kFinStripes) bn_finalize(
     float momentum, float* __restrict__ running_mean, float* __restrict__ running_var,
     float* __restrict__ out0, float* __restrict__ out1) {
   __shared__ double red[2][kFinStripes][33];
+  pdl_wait();                    // the partial sums are complete and visible
+  pdl_trigger();                 // the sweep may take its seats
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + tx;
   float a1[4] = {0.f, 0.f, 0.f, 0.f}, a2[4] = {0.f, 0.f, 0.f, 0.f};
@@ -442,6 +475,7 @@ template <int MODE, int VEC>
 __global__ void __launch_bounds__(kBlock) bn_sweep_nhwc(const float* a, const float* b, float* out,
                                                         SweepConst k, int C, size_t M, int tx_n,
                                                         int ty_n) {
+  pdl_wait();                    // the constants of the finalize kernel are complete and visible
   const int tx = threadIdx.x % tx_n, ty = threadIdx.x / tx_n;
   const int c0 = (blockIdx.y * tx_n + tx) * VEC;
   if (c0 >= C) return;
@@ -540,9 +574,9 @@ int run_sweep(const char* who, const mb_bn_desc* d, const Geometry& g, const flo
     dim3 grid(static_cast<unsigned>(want < cap ? want : cap), g.slabs);
     if (grid.x < 1) grid.x = 1;
     if (g.vec == 4)
-      bn_sweep_nhwc<MODE, 4><<<grid, kBlock, 0, st>>>(a, b, out, k, g.C, g.M, g.tx, g.ty);
+      launch_dependent(bn_sweep_nhwc<MODE, 4>, grid, dim3(kBlock), 0, st, a, b, out, k, g.C, g.M, g.tx, g.ty);
     else
-      bn_sweep_nhwc<MODE, 1><<<grid, kBlock, 0, st>>>(a, b, out, k, g.C, g.M, g.tx, g.ty);
+      launch_dependent(bn_sweep_nhwc<MODE, 1>, grid, dim3(kBlock), 0, st, a, b, out, k, g.C, g.M, g.tx, g.ty);
   } else {
     const size_t planes = static_cast<size_t>(g.N) * g.C;
     if (planes > 0x7fffffffULL) return fail(MB_ERR_UNSUPPORTED, "%s: N*C too large", who);
@@ -586,7 +620,7 @@ int bwd_common(const char* who, const float* dy, const float* v, const float* ga
   else
     rc = run_reduce<kBwd>("bn_bwd_reduce", d, g, dy, v, p0v, p1v, p1_is_gamma, ws, st);
   if (rc) return rc;
-  bn_finalize<kBwd><<<(g.C + 31) / 32, 32 * kFinStripes, 0, st>>>(ws, ws_const, nullptr, 0, g.C, g.M, g.S, 0.f,
+  launch_dependent(bn_finalize<kBwd>, dim3((g.C + 31) / 32), dim3(32 * kFinStripes), 0, st, ws, ws_const, nullptr, 0, g.C, g.M, g.S, 0.f,
                                                     0.f, nullptr, nullptr, dgamma, dbeta);
   rc = after_launch("bn_bwd_finalize");
   if (rc) return rc;
@@ -627,7 +661,7 @@ static int fwd_train_impl(const char* who, const float* x, const float* residual
   rc = run_reduce<kFwd>("bn_fwd_reduce", d, g, x, nullptr, nullptr, nullptr, 0, ws, st);
   if (rc) return rc;
   const size_t first_stride = d->layout == MB_NHWC ? 1 : static_cast<size_t>(d->HW);
-  bn_finalize<kFwd><<<(g.C + 31) / 32, 32 * kFinStripes, 0, st>>>(ws, nullptr, x, first_stride, g.C, g.M, g.S,
+  launch_dependent(bn_finalize<kFwd>, dim3((g.C + 31) / 32), dim3(32 * kFinStripes), 0, st, ws, nullptr, x, first_stride, g.C, g.M, g.S,
                                                     d->eps, d->momentum, running_mean,
                                                     running_var, save_mean, save_invstd);
   rc = after_launch("bn_fwd_finalize");
@@ -695,8 +729,7 @@ int mb_bn_act_fwd_train_partials(const float* x, const float* residual, int relu
   cudaStream_t st = as_stream(stream);
   // the statistics pass over x is replaced by the sums its producer left: finalize over
   // `partial_rows` rows of [2][rows][C], taken around `shift` (null: zero)
-  bn_finalize<kFwd><<<(g.C + 31) / 32, 32 * kFinStripes, 0, st>>>(
-      partials, nullptr, shift, 1, g.C, g.M, partial_rows, d->eps, d->momentum, running_mean,
+  launch_dependent(bn_finalize<kFwd>, dim3((g.C + 31) / 32), dim3(32 * kFinStripes), 0, st, partials, nullptr, shift, 1, g.C, g.M, partial_rows, d->eps, d->momentum, running_mean,
       running_var, save_mean, save_invstd);
   rc = after_launch("bn_fwd_finalize");
   if (rc) return rc;
@@ -727,7 +760,7 @@ int mb_bn_add_relu_bwd(const float* dy1, const float* dy2, const float* y, const
   rc = run_reduce<kBwdGate>("bn_add_relu_bwd_reduce", desc, g, dy1, x, save_mean, save_invstd, 0, ws,
                             st, nullptr, nullptr, dy2, y, d);
   if (rc) return rc;
-  bn_finalize<kBwd><<<(g.C + 31) / 32, 32 * kFinStripes, 0, st>>>(ws, ws_const, nullptr, 0, g.C, g.M, g.S, 0.f,
+  launch_dependent(bn_finalize<kBwd>, dim3((g.C + 31) / 32), dim3(32 * kFinStripes), 0, st, ws, ws_const, nullptr, 0, g.C, g.M, g.S, 0.f,
                                                     0.f, nullptr, nullptr, dgamma, dbeta);
   rc = after_launch("bn_bwd_finalize");
   if (rc) return rc;
