@@ -24,14 +24,20 @@ from .. import functional as F
 from .._lib import MB_CONV_DGRAD, MB_CONV_FPROP, MB_CONV_WGRAD
 from .base import OP, InputStorage, implements
 
-try:  # MONeT's global budget holder (an empty module at the root of a MONeT checkout)
-    import config as _monet_config
-except Exception:  # pragma: no cover - stand-alone use
-    _monet_config = None
+import sys
 
 
 def _budget_gb() -> float:
-    return float(getattr(_monet_config, "budget", float("inf"))) if _monet_config else float("inf")
+    """``config.budget`` in GB: MONeT's global budget holder is an empty module named ``config``
+    at the root of a checkout that the CLI fills in (schedule.py:379-380, read at
+    conv.py:140); no such module, or no value in it, means no limit."""
+    cfg = sys.modules.get("config")
+    if cfg is None:
+        try:
+            import config as cfg
+        except Exception:
+            return float("inf")
+    return float(getattr(cfg, "budget", float("inf")))
 
 
 class _ConvBase(OP):

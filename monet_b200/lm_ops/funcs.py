@@ -37,12 +37,11 @@ class AdaptiveAvgPool2D(OP):
 class _Add(OP):
     backward_storage = None
     params = None
-    inplace = False
 
     def forward(self, a, b, s):
         with torch.no_grad():
             self.params = s
-            return F.add(a, b, s, inplace=self.inplace)
+            return F.add(a, b, s, inplace=bool(getattr(self, "inplace", False)))
 
     def backward(self, grad_output, stored, nodel=False):
         assert len(stored) == 0
@@ -59,4 +58,6 @@ class Add(_Add):
 
 @implements(['aten::add_'], COMMON_MODES)
 class AddIP(_Add):
-    pass
+    # only the in-place spelling carries the attribute: SolverInfo.get_inplace_info offers the
+    # solver an in-place choice exactly for operators that have it (solver_info.py:442)
+    inplace = False

@@ -326,6 +326,12 @@ class Runner:
         self.input_requires_grad = input_requires_grad
         self.choices = [policy(self.nodes, n) for n in self.nodes]
         self.param_grads: Dict[str, torch.Tensor] = {}
+        self.on_param_grad: Optional[Callable[[str, torch.Tensor], None]] = None
+        self._param_uses: Dict[str, int] = {}
+        for n in self.nodes:
+            for a in n.args:
+                if a.kind == 'param':
+                    self._param_uses[a.value] = self._param_uses.get(a.value, 0) + 1
         self.shapes: Dict[int, tuple] = {}      # node id -> output shape, filled by forward()
         self._tensors = dict(model.state_dict(keep_vars=True))
         self._last_fwd_user = {n.id: (max(n.users) if n.users else -1) for n in self.nodes}
@@ -484,6 +490,7 @@ class Runner:
         # into its own pass).
         grads: Dict[int, List[torch.Tensor]] = {self.out_id: [grad_output]}
         self.param_grads = {}
+        pending_params: Dict[str, int] = {}      # parameter -> backward steps that still owe it a gradient
 
         def pending():
             for lst in grads.values():
@@ -559,12 +566,29 @@ class Runner:
                             self.param_grads[a.value] = self.param_grads[a.value] + gi
                         else:
                             self.param_grads[a.value] = gi
+                        pending_params[a.value] = pending_params.get(a.value, self._param_uses[a.value]) - 1
+                        if pending_params[a.value] == 0:
+                            del pending_params[a.value]
+                            self._finish_param(a.value)
                 del outs
-        for name, gi in self.param_grads.items():
-            p = self._tensors[name]
-            gi = gi.reshape(p.shape) if gi.shape != p.shape else gi
-            if p.dim() != 4:
-                gi = gi.contiguous()
+        for name in list(pending_params):
+            self._finish_param(name)
+        self._vals = {}
+        self._inter = {}
+
+    def _finish_param(self, name: str) -> None:
+        """The gradient of parameter `name` is complete: hand it to ``param.grad`` (accumulating,
+        like ``param.backward(grad)`` in schedule.py:304-306) and tell ``on_param_grad``, which
+        is how a data-parallel wrapper learns that a gradient bucket can be reduced while the
+        rest of the backward still runs."""
+        gi = self.param_grads[name]
+        p = self._tensors[name]
+        gi = gi.reshape(p.shape) if gi.shape != p.shape else gi
+        if p.dim() != 4:
+            gi = gi.contiguous()
+        if p.grad is not None:
+            p.grad.add_(gi)
+        else:
             if gi.stride() != p.stride():
                 # same strides as the parameter, so that foreach optimisers keep their fused
                 # path: a 1x1 filter is the same memory either way, anything else is copied
@@ -573,12 +597,9 @@ class Runner:
                     gi = gi.as_strided(p.shape, p.stride())
                 else:
                     gi = torch.empty_like(p).copy_(gi)
-            if p.grad is None:
-                p.grad = gi
-            else:
-                p.grad.add_(gi)
-        self._vals = {}
-        self._inter = {}
+            p.grad = gi
+        if self.on_param_grad is not None:
+            self.on_param_grad(name, p)
 
     def _release(self, node_id: int) -> None:
         """Called after the backward step of `node_id`: drop every value whose last backward
