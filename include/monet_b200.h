@@ -253,6 +253,18 @@ int mb_nhwc_to_nchw(const float* x, float* y, int N, int C, int H, int W, void* 
  * few-channel network input (C = 3) for the tensor-core convolution.         */
 int mb_nchw_to_nhwc_pad(const float* x, float* y, int N, int C, int H, int W, int Cp,
                         void* stream);
+/* Concatenation and its backward (cat.py:5-29: torch.cat forward, torch.split +
+ * one .contiguous() copy per piece backward) as ONE row-copy launch for all
+ * pieces.  With the extents before the concatenation axis folded into `rows`
+ * and the axis and everything after it into a row, piece i is `widths[i]`
+ * consecutive floats of every row of `whole`.  to_pieces = 0: pieces -> whole
+ * (forward); 1: whole -> pieces (the split of the gradient).  `pieces` and
+ * `widths` are HOST arrays of n_pieces (<= MB_CAT_MAX_PIECES) device pointers /
+ * widths in floats.  128-bit accesses when every width is a multiple of 4 and
+ * every pointer 16-byte aligned.                                              */
+#define MB_CAT_MAX_PIECES 8
+int mb_cat_rows(float* whole, float* const* pieces, const int* widths, int n_pieces, size_t rows,
+                int to_pieces, void* stream);
 /* Global average pool (adaptive_avg_pool2d to 1x1; funcs.py:7-21):
  * y[N,C] = mean over H*W; backward dx = dy / HW broadcast, written fully
  * (no zeros tensor as in funcs.py:20).                                       */

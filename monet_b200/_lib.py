@@ -37,6 +37,7 @@ class ConvDesc(C.Structure):
 
 
 MB_CONV_FPROP, MB_CONV_DGRAD, MB_CONV_WGRAD = 0, 1, 2
+MB_CAT_MAX_PIECES = 8
 
 
 # name -> (restype, argtypes); every symbol of include/monet_b200.h
@@ -98,6 +99,7 @@ PROTOTYPES = {
     "mb_conv2d_fprop_smallc": (C.c_int, [c_f, c_f, c_f, c_f, C.POINTER(ConvDesc), c_f]),
     "mb_conv_smallc_wgrad_workspace_bytes": (c_sz, [C.POINTER(ConvDesc), C.c_int]),
     "mb_conv2d_wgrad_smallc": (C.c_int, [c_f, c_f, c_f, c_f, C.POINTER(ConvDesc), C.c_int, c_f, c_sz, c_f]),
+    "mb_cat_rows": (C.c_int, [c_f, C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.c_int, c_sz, C.c_int, c_f]),
     "mb_global_avgpool_fwd": (C.c_int, [c_f, c_f, C.c_int, C.c_int, C.c_int, C.c_int, c_f]),
     "mb_global_avgpool_bwd": (C.c_int, [c_f, c_f, C.c_int, C.c_int, C.c_int, C.c_int, c_f]),
 }

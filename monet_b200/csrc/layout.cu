@@ -107,6 +107,42 @@ __global__ void __launch_bounds__(256) gap_bwd(const float* __restrict__ dy, flo
   }
 }
 
+// Concatenation along one axis, seen as a row copy: with everything before the axis folded
+// into `rows` and everything from the axis on into a row, piece i is the column range
+// [begin[i], begin[i+1]) of every row of the whole tensor.  One launch serves all pieces, in
+// either direction (forward: pieces -> whole; backward: whole -> pieces, the split of the
+// gradient).  V floats per thread per access.
+struct CatPieces {
+  float* ptr[MB_CAT_MAX_PIECES];
+  int begin[MB_CAT_MAX_PIECES + 1];
+  int n;
+};
+
+template <int V, bool kToPieces>
+__global__ void __launch_bounds__(256) cat_rows(float* __restrict__ whole, CatPieces P,
+                                                size_t rows, int width) {
+  const size_t wv = static_cast<size_t>(width / V), total = rows * wv;
+  for (size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
+       t += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t r = t / wv;
+    const int c = static_cast<int>(t - r * wv) * V;
+    int i = 0;
+#pragma unroll
+    for (int k = 1; k < MB_CAT_MAX_PIECES; ++k)
+      if (k < P.n && c >= P.begin[k]) i = k;
+    const int w = P.begin[i + 1] - P.begin[i];
+    float* piece = P.ptr[i] + r * w + (c - P.begin[i]);
+    float* big = whole + r * width + c;
+    if (V == 4) {
+      if (kToPieces) *reinterpret_cast<float4*>(piece) = __ldg(reinterpret_cast<const float4*>(big));
+      else *reinterpret_cast<float4*>(big) = __ldg(reinterpret_cast<const float4*>(piece));
+    } else {
+      if (kToPieces) *piece = __ldg(big);
+      else *big = __ldg(piece);
+    }
+  }
+}
+
 }  // namespace
 }  // namespace mb
 
@@ -133,6 +169,38 @@ int mb_nchw_to_nhwc_pad(const float* x, float* y, int N, int C, int H, int W, in
   const size_t HW = static_cast<size_t>(H) * W, total = HW * N;
   nchw_to_nhwc_pad<<<grid_for(total, 256, 8), 256, 0, as_stream(stream)>>>(x, y, C, Cp, HW, total);
   return after_launch("nchw_to_nhwc_pad");
+}
+
+int mb_cat_rows(float* whole, float* const* pieces, const int* widths, int n_pieces, size_t rows,
+                int to_pieces, void* stream) {
+  if (n_pieces < 1 || n_pieces > MB_CAT_MAX_PIECES || !pieces || !widths)
+    return fail(MB_ERR_INVALID_ARGUMENT, "mb_cat_rows: 1..%d pieces", MB_CAT_MAX_PIECES);
+  CatPieces P;
+  P.n = n_pieces;
+  P.begin[0] = 0;
+  bool vec = aligned(whole, 16);
+  for (int i = 0; i < n_pieces; ++i) {
+    if (widths[i] <= 0) return fail(MB_ERR_INVALID_ARGUMENT, "mb_cat_rows: empty piece %d", i);
+    if (rows && !pieces[i]) return fail(MB_ERR_INVALID_ARGUMENT, "mb_cat_rows: null piece %d", i);
+    P.ptr[i] = pieces[i];
+    P.begin[i + 1] = P.begin[i] + widths[i];
+    vec = vec && widths[i] % 4 == 0 && aligned(pieces[i], 16);
+  }
+  for (int i = n_pieces; i < MB_CAT_MAX_PIECES; ++i) { P.ptr[i] = nullptr; P.begin[i + 1] = P.begin[n_pieces]; }
+  if (rows == 0) return MB_OK;
+  if (!whole) return fail(MB_ERR_INVALID_ARGUMENT, "mb_cat_rows: null pointer");
+  const int width = P.begin[n_pieces];
+  cudaStream_t st = as_stream(stream);
+  const size_t items = rows * static_cast<size_t>(vec ? width / 4 : width);
+  const int grid = grid_for(items, 256, 8);
+  if (vec) {
+    if (to_pieces) cat_rows<4, true><<<grid, 256, 0, st>>>(whole, P, rows, width);
+    else cat_rows<4, false><<<grid, 256, 0, st>>>(whole, P, rows, width);
+  } else {
+    if (to_pieces) cat_rows<1, true><<<grid, 256, 0, st>>>(whole, P, rows, width);
+    else cat_rows<1, false><<<grid, 256, 0, st>>>(whole, P, rows, width);
+  }
+  return after_launch("cat_rows");
 }
 
 int mb_global_avgpool_fwd(const float* x, float* y, int N, int C, int HW, int layout,

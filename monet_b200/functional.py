@@ -571,6 +571,72 @@ def to_nchw(x: torch.Tensor) -> torch.Tensor:
     return y
 
 
+def _cat_geometry(shapes, dim: int, nhwc: bool):
+    """(rows, widths, physical-order flag) of a concatenation along logical axis `dim`."""
+    nd = len(shapes[0])
+    dim = dim % nd
+    order = (0, 2, 3, 1) if nhwc else tuple(range(nd))      # logical axes in physical order
+    pos = order.index(dim)
+    rows = 1
+    for a in order[:pos]:
+        rows *= int(shapes[0][a])
+    tail = 1
+    for a in order[pos + 1:]:
+        tail *= int(shapes[0][a])
+    for sh in shapes:
+        if len(sh) != nd or any(int(sh[a]) != int(shapes[0][a]) for a in range(nd) if a != dim):
+            raise RuntimeError("monet_b200.cat: shapes differ outside the concatenation axis")
+    return rows, [int(sh[dim]) * tail for sh in shapes], dim
+
+
+def _cat_call(whole, pieces, widths, rows, to_pieces):
+    n = len(pieces)
+    if n > _lib.MB_CAT_MAX_PIECES:
+        raise RuntimeError(f"monet_b200.cat: at most {_lib.MB_CAT_MAX_PIECES} tensors per call")
+    ptrs = (C.c_void_p * n)(*[p.data_ptr() for p in pieces])
+    ws = (C.c_int * n)(*widths)
+    check(lib().mb_cat_rows(whole.data_ptr(), ptrs, ws, n, rows, int(to_pieces), _stream()), "cat_rows")
+
+
+def cat(tensors, dim: int) -> torch.Tensor:
+    """torch.cat(tensors, dim) in one launch; the result has the first tensor's memory format."""
+    tensors = list(tensors)
+    _need_cuda(*tensors)
+    for t in tensors:
+        _f32(t, "cat input")
+    first = dense(tensors[0])
+    nhwc = is_nhwc(first)
+    parts = [first] + [like(first, t) if t.dim() == 4 else t.contiguous() for t in tensors[1:]]
+    rows, widths, dim = _cat_geometry([p.shape for p in parts], dim, nhwc)
+    shape = list(first.shape)
+    shape[dim] = sum(int(p.shape[dim]) for p in parts)
+    out = torch.empty(shape, dtype=first.dtype, device=first.device,
+                      memory_format=torch.channels_last if nhwc else torch.contiguous_format)
+    _cat_call(out, parts, widths, rows, False)
+    return out
+
+
+def cat_bwd(grad: torch.Tensor, sizes, dim: int):
+    """The gradient of a concatenation split back into dense pieces of `sizes` along `dim`
+    (torch.split + .contiguous() per piece in cat.py:20-29) in one launch."""
+    _need_cuda(grad); _f32(grad, "grad")
+    g = dense(grad)
+    nhwc = is_nhwc(g)
+    dim = dim % g.dim()
+    shapes = []
+    for sz in sizes:
+        sh = list(g.shape)
+        sh[dim] = int(sz)
+        shapes.append(sh)
+    if sum(int(s) for s in sizes) != int(g.shape[dim]):
+        raise RuntimeError("monet_b200.cat_bwd: sizes do not add up to the gradient's extent")
+    rows, widths, dim = _cat_geometry(shapes, dim, nhwc)
+    fmt = torch.channels_last if nhwc else torch.contiguous_format
+    pieces = [torch.empty(sh, dtype=g.dtype, device=g.device, memory_format=fmt) for sh in shapes]
+    _cat_call(g, pieces, widths, rows, True)
+    return pieces
+
+
 def global_avgpool(x: torch.Tensor) -> torch.Tensor:
     _need_cuda(x); _f32(x, "x")
     xd = dense(x)

@@ -1,8 +1,10 @@
-"""Concatenation (monet/lm_ops/cat.py:5-29)."""
+"""Concatenation (monet/lm_ops/cat.py:5-29): forward and the split of the gradient each run as
+one row-copy launch over all pieces."""
 from __future__ import annotations
 
 import torch
 
+from .. import functional as F
 from .base import COMMON_MODES, OP, implements
 
 
@@ -16,12 +18,12 @@ class Cat(OP):
         with torch.no_grad():
             if len(tensors) == 1:
                 return tensors[0]
-            return torch.cat(tensors, dim=dim)
+            return F.cat([t.detach() for t in tensors], dim)
 
-    def backward(self, *grad_output, nodel=False):
+    def backward(self, grad_output, stored=None, nodel=False):
+        # the executor calls backward(grad, stored) with an empty `stored` (no backward_storage)
         dim, sizes = self.params
         with torch.no_grad():
-            g = grad_output[0]
             if len(sizes) == 1:
-                return g
-            return [piece.contiguous() for piece in torch.split(g, sizes, dim=dim)]
+                return grad_output
+            return F.cat_bwd(grad_output, sizes, dim)

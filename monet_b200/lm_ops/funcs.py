@@ -9,10 +9,12 @@ from .base import COMMON_MODES, OP, implements
 
 @implements(['aten::adaptive_avg_pool2d'], COMMON_MODES)
 class AdaptiveAvgPool2D(OP):
-    """Global (1x1) pooling runs this library's kernels; other output sizes defer to torch
-    on the GPU.  The backward needs only the input's shape."""
+    """Global (1x1) pooling runs this library's kernels; other output sizes (the reference's
+    UNet uses the operator to up-sample, models/unet/unet_parts.py:47) run ATen's kernel on
+    the GPU, as the reference does (lrfuncs.cpp:11-14).  The backward needs only the input's
+    shape, which travels in ``params`` (the executor hands ``params``, not the object, to the
+    operator instance that runs the backward, schedule.py:247-251)."""
     params = None
-    grad_fn = None
 
     def forward(self, x, os):
         with torch.no_grad():
@@ -20,18 +22,17 @@ class AdaptiveAvgPool2D(OP):
             self.params = tuple(x.shape), F.is_nhwc(x), os
             if os == [1, 1] and x.dim() == 4:
                 return F.global_avgpool(x)
-        with torch.enable_grad():
-            r = torch._C._nn.adaptive_avg_pool2d(x.detach().requires_grad_(True), os)
-        self.grad_fn = r.grad_fn
-        return r.detach()
+            return torch._C._nn.adaptive_avg_pool2d(x.detach(), os)
 
     def backward(self, grad_output, stored, nodel=False):
         assert len(stored) == 0
         with torch.no_grad():
             shape, nhwc, os = self.params
-            if self.grad_fn is None:
+            if os == [1, 1] and len(shape) == 4:
                 return F.global_avgpool_bwd(grad_output, shape, nhwc)
-            return self.grad_fn(grad_output)
+            # ATen wants the forward input for its sizes only: a stride-0 view of one element
+            like = grad_output.new_empty(1).expand(shape)
+            return torch.ops.aten._adaptive_avg_pool2d_backward(grad_output.contiguous(), like)
 
 
 class _Add(OP):

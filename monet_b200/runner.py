@@ -536,10 +536,7 @@ class Runner:
                 if n.op in ('aten::_convolution', 'aten::addmm'):
                     variant = max(self.choices[n.id].algorithm, 0)
                     op.algorithm = 20 + variant          # weight and input gradients in one call
-                if n.op == 'aten::cat':
-                    outs = op.backward(g)
-                else:
-                    outs = op.backward(g, stored)
+                outs = op.backward(g, stored)
                 del stored, g
                 self._release(n.id)
                 if not isinstance(outs, (tuple, list)):

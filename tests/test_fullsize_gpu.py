@@ -88,3 +88,125 @@ def test_conv_linearity_and_adjointness_at_layer_size(cuda, geom):
     assert abs(lhs - float((x1.double() * dx.double()).sum())) < 2e-2 * abs(lhs) + 1e-3 * y1.numel() ** 0.5
     assert abs(lhs - float((w.double() * dw.double()).sum())) < 2e-2 * abs(lhs) + 1e-3 * y1.numel() ** 0.5
     assert F.conv_device_status() == 0
+
+
+# The 23 distinct convolution geometries of ResNet-50 (torchvision v1.5 layout) at 224 x 224:
+# (C, H, K, R, stride, pad); the GEMM shapes they give at batch 184 are M = 184 * P * Q from
+# 9 016 to 2 308 096.
+RESNET50_GEOMETRIES = [
+    (3, 224, 64, 7, 2, 3),
+    (64, 56, 64, 1, 1, 0), (64, 56, 64, 3, 1, 1), (64, 56, 256, 1, 1, 0), (256, 56, 64, 1, 1, 0),
+    (256, 56, 128, 1, 1, 0), (128, 56, 128, 3, 2, 1), (128, 28, 512, 1, 1, 0), (256, 56, 512, 1, 2, 0),
+    (512, 28, 128, 1, 1, 0), (128, 28, 128, 3, 1, 1),
+    (512, 28, 256, 1, 1, 0), (256, 28, 256, 3, 2, 1), (256, 14, 1024, 1, 1, 0), (512, 28, 1024, 1, 2, 0),
+    (1024, 14, 256, 1, 1, 0), (256, 14, 256, 3, 1, 1),
+    (1024, 14, 512, 1, 1, 0), (512, 14, 512, 3, 2, 1), (512, 7, 2048, 1, 1, 0), (1024, 14, 2048, 1, 2, 0),
+    (2048, 7, 512, 1, 1, 0), (512, 7, 512, 3, 1, 1),
+]
+SAMPLED = (0, 91, 183)
+
+
+@pytest.mark.parametrize("geom", RESNET50_GEOMETRIES, ids=lambda g: "c%d_h%d_k%d_r%d_s%d" % g[:5])
+def test_resnet50_convolutions_at_batch_184_against_the_oracle(cuda, geom):
+    """Every convolution geometry of the workload at its real batch, three passes, against the
+    fp32 CPU oracle at rtol 2e-2 of the tensor's scale.  The launches are the batch-184 ones
+    (tile widths, super-tiles and split counts are chosen from the problem size), the oracle
+    runs on three images:
+
+    * fprop and dgrad are independent per image: images 0, 91 and 183 of y and dx are compared
+      with the oracle applied to those images alone;
+    * wgrad sums over the batch: dy is zero outside the three images, so the batch-184 launch
+      (both variants) must reproduce the oracle's dw and db of the 3-image sub-batch."""
+    from monet_b200 import functional as F
+    from oracle import lm_ops_oracle as oracle
+    C, H, K, R, s, p = geom
+    N = 184
+    g = torch.Generator(device=cuda).manual_seed(7)
+    x = torch.randn(N, C, H, H, device=cuda, generator=g)
+    if C % 4 == 0:
+        x = x.contiguous(memory_format=torch.channels_last)
+    w = (torch.randn(K, C, R, R, device=cuda, generator=g) * (2.0 / (C * R * R)) ** 0.5)
+    idx = list(SAMPLED)
+    xs, ws = x[idx].cpu().contiguous(), w.cpu()
+
+    def err(a, ref):
+        return float((a - ref).abs().max() / ref.abs().max().clamp_min(1e-6))
+
+    y = F.conv2d_fprop(x, w, None, s, p, 1)
+    ref_y = oracle.conv_forward(xs, ws, None, s, p, 1)
+    assert tuple(y.shape) == (N,) + tuple(ref_y.shape[1:])
+    assert err(y[idx].cpu(), ref_y) < 2e-2, ("fprop", err(y[idx].cpu(), ref_y))
+
+    dy = torch.randn(y.shape, device=cuda, generator=g).contiguous(memory_format=torch.channels_last)
+    dys = dy[idx].cpu().contiguous()
+    ref_dx, ref_dw, ref_db = oracle.conv_backward(dys, xs, ws, s, p, 1)
+    dx = F.conv2d_dgrad(dy, w, x.shape, s, p, 1)
+    assert err(dx[idx].cpu(), ref_dx) < 2e-2, ("dgrad", err(dx[idx].cpu(), ref_dx))
+    del dx, y
+
+    mask = torch.zeros(N, 1, 1, 1, device=cuda)
+    mask[idx] = 1
+    dy_sparse = (dy * mask).contiguous(memory_format=torch.channels_last)
+    del dy
+    for variant in (0, 1):
+        dw, db = F.conv2d_wgrad(x, dy_sparse, w.shape, s, p, 1, variant=variant, need_bias=True)
+        assert err(dw.cpu(), ref_dw) < 2e-2, ("wgrad", variant, err(dw.cpu(), ref_dw))
+        assert torch.allclose(db.cpu(), ref_db, rtol=1e-4, atol=1e-3)
+    assert F.conv_device_status() == 0
+
+
+def test_stem_configuration_verbatim(cuda):
+    """The CPU-runnable configuration at its stated size: N = 4, 3 x 224 x 224, conv 7x7/2 ->
+    BN(train) -> ReLU (1-bit mask) -> max-pool 3x3/2 (4-bit indices), forward and backward through
+    the four operator classes; y, dx, dW, dgamma, dbeta against torch CPU, and all 401 408 mask
+    bytes and 401 408 index bytes bit-exact against the oracle applied to the tensors the
+    operators saw."""
+    import numpy as np
+    from monet_b200 import functional as F
+    from monet_b200 import lm_ops
+    from oracle import lm_ops_oracle as oracle
+    ref = oracle.stem_reference()                     # N=4, 224 x 224
+    mode = "conv_multiway_newnode"
+    conv = lm_ops.list_ops(mode, "aten::_convolution")[0]()
+    bn = lm_ops.list_ops(mode, "aten::batch_norm")[1]()
+    relu = lm_ops.list_ops(mode, "aten::relu")[2]()
+    pool = lm_ops.list_ops(mode, "aten::max_pool2d")[1]()
+    x = ref["x"].to(cuda).requires_grad_(True)
+    w = ref["w"].to(cuda).requires_grad_(True)
+    gamma, beta = ref["gamma"].to(cuda), ref["beta"].to(cuda)
+    rm, rv = torch.zeros(64, device=cuda), torch.ones(64, device=cuda)
+    c = conv.forward(x, w, None, [2, 2], [3, 3], [1, 1], False, [0, 0], 1)
+    b = bn.forward(c, gamma, beta, rm, rv, True, 0.1, 1e-5, True)
+    r, mask = relu.forward(b)
+    y, nib = pool.forward(r, [3, 3], [2, 2], [1, 1], [1, 1], False)
+    assert mask.numel() == 401408 and nib.numel() == 401408
+    cpu = lambda t: t.detach().cpu().contiguous()       # noqa: E731
+    b_cpu, r_cpu = cpu(b), cpu(r)
+    d_r = pool.backward(ref["dy"].to(cuda), [nib])
+    d_b = relu.backward(d_r.clone(), [mask])
+    d_c, dgamma, dbeta, _, _ = bn.backward(d_b, [gamma, beta, rm, rv, b])
+    conv.algorithm = 20
+    dx, dw = conv.backward(d_c, [x, w])
+    torch.cuda.synchronize()
+    assert F.conv_device_status() == 0
+
+    def rel(a, t):
+        return float((cpu(a) - t).abs().max() / t.abs().max().clamp_min(1e-12))
+
+    # packed formats: bit-exact on the operators' own inputs (NHWC physical order)
+    assert np.array_equal(mask.cpu().numpy(), oracle.relu_mask_bytes(b_cpu.permute(0, 2, 3, 1).contiguous()))
+    o_y, local = oracle.maxpool_forward(r_cpu, 3, 2, 1)
+    assert torch.equal(cpu(y), o_y)
+    assert np.array_equal(nib.cpu().numpy(), oracle.maxpool_nibbles(local, nhwc=True))
+    # against the all-fp32 torch CPU run of the whole stem: convolution tolerance (TF32 operands)
+    for name, got in (("y", y), ("dx", dx), ("dw", dw), ("dgamma", dgamma), ("dbeta", dbeta)):
+        assert rel(got, ref[name]) < 2e-2, (name, rel(got, ref[name]))
+    # the fp32 operators against the oracle on the same inputs: rtol 1e-5
+    o_b, _, o_inv, _, _ = oracle.bn_forward_train(cpu(c), ref["gamma"], ref["beta"], torch.zeros(64), torch.ones(64))
+    assert torch.allclose(b_cpu, o_b, rtol=1e-5, atol=1e-5)
+    o_dr = oracle.maxpool_backward_from_index(ref["dy"], local, tuple(r.shape), 3, 2, 1)
+    assert torch.allclose(cpu(d_r), o_dr, rtol=1e-5, atol=1e-6)
+    assert torch.equal(cpu(d_b), oracle.relu_backward(cpu(d_r), b_cpu))
+    o_dc, o_dg, o_db = oracle.bn_backward_from_output(cpu(d_b), b_cpu, ref["gamma"], ref["beta"], o_inv)
+    assert torch.allclose(cpu(d_c), o_dc, rtol=1e-5, atol=1e-5)
+    assert torch.allclose(cpu(dgamma), o_dg, rtol=1e-4, atol=1e-3) and torch.allclose(cpu(dbeta), o_db, rtol=1e-4, atol=1e-3)
