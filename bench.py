@@ -36,7 +36,12 @@ def parse():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--schedule", default="budget_10gb", choices=["low_memory", "store_all", "budget_10gb"])
+    ap.add_argument("--model", default="resnet50", choices=["resnet50", "mobilenet_v2", "unet", "vgg16_bn"],
+                    help="BASELINE configs[1..4]; batch, input and schedule default to the config's")
+    ap.add_argument("--schedule", default=None, choices=["low_memory", "store_all", "budget_10gb"])
+    ap.add_argument("--buckets", type=int, default=4, help="gradient buckets of the data-parallel all-reduce")
+    ap.add_argument("--no-comparators", action="store_true",
+                    help="skip the unfused-graph and stock-PyTorch-on-this-GPU runs (N = 1 only)")
     ap.add_argument("--no-fuse", action="store_true",
                     help="run batch norm, residual add and ReLU as separate operators, as the "
                          "reference's graph does")
@@ -46,8 +51,9 @@ def parse():
     ap.add_argument("--no-cuda-graph", action="store_true",
                     help="time the Python executor's eager launches only (the default also captures "
                          "the step as a CUDA graph and reports the replayed step as `value`)")
-    ap.add_argument("--batch", type=int, default=184)
-    ap.add_argument("--cpu-batch", type=int, default=16, help="images per step of the CPU sample")
+    ap.add_argument("--batch", type=int, default=None, help="per-GPU batch (default: the config's)")
+    ap.add_argument("--cpu-batch", type=int, default=None,
+                    help="images per step of the CPU arm (default: the full batch; an override is echoed in config)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--micro", default=None, choices=sorted(MICRO),
                     help="time ONE operator on one ResNet-50 layer's tensors (for ncu captures)")
@@ -159,14 +165,18 @@ def run_reference(args):
     if rank != 0:
         return
     from oracle import cpu_baseline
-    steps = max(1, min(args.steps, 5))
-    ips, ms, threads = cpu_baseline.resnet50_train_steps(args.cpu_batch, steps, warmup=1)
-    sample = f"{steps} eager steps of batch {args.cpu_batch} (of 184) on {threads} host threads"
+    steps = max(1, min(args.steps, 4))
+    batch = args.cpu_batch or args.batch or 184
+    ips, ms, threads = cpu_baseline.resnet50_train_steps(batch, steps, warmup=1)
+    sample = f"{steps} eager steps of batch {batch} (of 184) on {threads} host threads"
+    cfg = {"workload": WORKLOAD, "sample": sample}
+    if batch != 184:
+        cfg["cpu_batch_override"] = batch
     line = {
         "impl": "reference", "metric": METRIC, "value": ips, "unit": "images/s", "n_gpus": args.gpus,
         "steps": steps, "warmup": 1, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample": sample},
+        "config": cfg,
         "cpu_baseline": {"value": ips, "unit": "images/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": ips, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -257,11 +267,23 @@ def family_costs(runner_obj, batch_shape):
         if n.op == 'aten::_convolution':
             w = runner_obj._tensors[n.args[1].value]
             e_w = float(w.numel())
+            byts = 4 * (e_in + e_w + e_out)
+            if n.args[8].value > 1:                     # depthwise: bandwidth kernels, no tensor cores
+                add("mb_depthwise_fprop", byts)
+                add("mb_depthwise_wgrad", byts)
+                add("mb_depthwise_dgrad", byts)
+                continue
+            if n.args[6].value:                         # transposed: forward = dgrad kernel, backward-data = fprop kernel
+                fl = 2.0 * e_in * w.shape[1] * w.shape[2] * w.shape[3]
+                add("mb_conv2d_dgrad", byts, fl)
+                add("mb_conv2d_fprop", byts, fl)
+                add("mb_conv2d_wgrad", byts, fl)
+                continue
             fl = 2.0 * e_out * w.shape[1] * w.shape[2] * w.shape[3]
-            add("mb_conv2d_fprop_bnstats" if emits_sums(n) else "mb_conv2d_fprop", 4 * (e_in + e_w + e_out), fl)
-            add("mb_conv2d_wgrad", 4 * (e_in + e_w + e_out), fl)
+            add("mb_conv2d_fprop_bnstats" if emits_sums(n) else "mb_conv2d_fprop", byts, fl)
+            add("mb_conv2d_wgrad", byts, fl)
             if a0.kind == 'node':
-                add("mb_conv2d_dgrad", 4 * (e_in + e_w + e_out), fl)
+                add("mb_conv2d_dgrad", byts, fl)
         elif n.op == 'aten::batch_norm':
             src = runner_obj.nodes[n.sums_from] if getattr(n, "sums_from", -1) >= 0 else None
             if src is not None and emits_sums(src):
@@ -292,6 +314,11 @@ def family_costs(runner_obj, batch_shape):
             add("mb_relu_bwd_act", 12 * e_out)
         elif n.op in ('aten::add', 'aten::add_'):
             add("mb_add_fwd", 12 * e_out)
+        elif n.op in ('aten::hardtanh', 'aten::hardtanh_'):
+            add("mb_hardtanh_fwd", 8 * e_out * (2 if ch.recompute else 1))
+            add("mb_hardtanh_bwd", 12 * e_out)
+        elif n.op == 'aten::cat':
+            add("mb_cat_rows", 16 * e_out)              # forward and backward: read + write each
         elif n.op == 'aten::max_pool2d':
             add("mb_maxpool2d_fwd", 4 * e_in + 4.5 * e_out)
             add("mb_maxpool2d_bwd", 4 * e_in + 4.5 * e_out)
@@ -314,81 +341,230 @@ TRAFFIC_RATIO = {
 }
 
 
+# -------------------------------------------------------------------------- workloads
+def _unet(n_classes=2, base=64):
+    """UNet of BASELINE configs[3]: 4 down / 4 up levels, double 3x3 conv + BN + ReLU per level,
+    2x2 max-pool down, 2x2 stride-2 transposed convolution up, skip concatenation."""
+    import torch
+    nn = torch.nn
+
+    def double(cin, cout):
+        return nn.Sequential(nn.Conv2d(cin, cout, 3, padding=1, bias=False), nn.BatchNorm2d(cout), nn.ReLU(inplace=True),
+                             nn.Conv2d(cout, cout, 3, padding=1, bias=False), nn.BatchNorm2d(cout), nn.ReLU(inplace=True))
+
+    class UNet(nn.Module):
+        def __init__(self):
+            super().__init__()
+            c = [base, base * 2, base * 4, base * 8, base * 16]
+            self.inc = double(3, c[0])
+            self.pool1 = nn.MaxPool2d(2); self.down1 = double(c[0], c[1])
+            self.pool2 = nn.MaxPool2d(2); self.down2 = double(c[1], c[2])
+            self.pool3 = nn.MaxPool2d(2); self.down3 = double(c[2], c[3])
+            self.pool4 = nn.MaxPool2d(2); self.down4 = double(c[3], c[4])
+            self.up1 = nn.ConvTranspose2d(c[4], c[3], 2, stride=2); self.conv1 = double(c[4], c[3])
+            self.up2 = nn.ConvTranspose2d(c[3], c[2], 2, stride=2); self.conv2 = double(c[3], c[2])
+            self.up3 = nn.ConvTranspose2d(c[2], c[1], 2, stride=2); self.conv3 = double(c[2], c[1])
+            self.up4 = nn.ConvTranspose2d(c[1], c[0], 2, stride=2); self.conv4 = double(c[1], c[0])
+            self.outc = nn.Conv2d(c[0], n_classes, 1)
+
+        def forward(self, x):
+            x1 = self.inc(x)
+            x2 = self.down1(self.pool1(x1))
+            x3 = self.down2(self.pool2(x2))
+            x4 = self.down3(self.pool3(x3))
+            x5 = self.down4(self.pool4(x4))
+            y = self.conv1(torch.cat([x4, self.up1(x5)], 1))
+            y = self.conv2(torch.cat([x3, self.up2(y)], 1))
+            y = self.conv3(torch.cat([x2, self.up3(y)], 1))
+            y = self.conv4(torch.cat([x1, self.up4(y)], 1))
+            return self.outc(y)
+
+    return UNet()
+
+
+# name -> (constructor, batch, input shape, classes, default schedule, description)
+def workloads():
+    import torchvision
+    return {
+        "resnet50": (torchvision.models.resnet50, 184, (3, 224, 224), 1000, "budget_10gb",
+                     "ResNet-50 v1.5, batch 184 per GPU, 3x224x224 fp32, CE + SGD momentum (BASELINE configs[1])"),
+        "mobilenet_v2": (torchvision.models.mobilenet_v2, 272, (3, 224, 224), 1000, "low_memory",
+                         "MobileNetV2 1.0, batch 272 per GPU, 3x224x224 fp32, CE + SGD momentum (BASELINE configs[2])"),
+        "unet": (_unet, 11, (3, 416, 608), 2, "low_memory",
+                 "UNet 4+4 levels base 64, transposed-conv up, batch 11 per GPU, 3x416x608 fp32, per-pixel 2-class CE + SGD momentum (BASELINE configs[3])"),
+        "vgg16_bn": (torchvision.models.vgg16_bn, 176, (3, 224, 224), 1000, "low_memory",
+                     "VGG-16-BN, batch 176 per GPU, 3x224x224 fp32, CE + SGD momentum (BASELINE configs[4])"),
+    }
+
+
+def measure_tf32_peak(dev, seconds=0.6):
+    """Sustained dense TF32 rate of this GPU right now: cuBLAS 8192^3 fp32 matmul with TF32
+    allowed, repeated for about `seconds`, CUDA events.  The denominator of the convolutions'
+    tensor-pipe fraction (no TF32 figure is in MEASURED_PEAKS.json)."""
+    import torch
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        n = 8192
+        a = torch.randn(n, n, device=dev)
+        b = torch.randn(n, n, device=dev)
+        c = torch.empty(n, n, device=dev)
+        for _ in range(3):
+            torch.matmul(a, b, out=c)
+        torch.cuda.synchronize()
+        flop = 2.0 * n ** 3
+        reps, best = 20, 0.0
+        t_end = time.perf_counter() + seconds
+        while True:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                torch.matmul(a, b, out=c)
+            e1.record()
+            torch.cuda.synchronize()
+            best = flop * reps / (e0.elapsed_time(e1) * 1e-3) / 1e12     # last window = sustained
+            if time.perf_counter() > t_end:
+                break
+        return best
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+
+
+def torch_gpu_baseline(make_model, x, y, steps, warmup, pixelwise):
+    """Stock PyTorch on the same GPU: eager, channels_last, cuDNN TF32 + benchmark mode, same
+    batch, CE + SGD momentum -- what the reference compares itself with
+    (examples/check_runtime_original.py:32-56).  Returns (ms per step, peak bytes)."""
+    import torch
+    old = (torch.backends.cudnn.allow_tf32, torch.backends.cudnn.benchmark, torch.backends.cuda.matmul.allow_tf32)
+    torch.backends.cudnn.allow_tf32 = True
+    torch.backends.cudnn.benchmark = True
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        torch.manual_seed(0)
+        model = make_model().to(x.device).train().to(memory_format=torch.channels_last)
+        opt = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9)
+        xc = x.contiguous(memory_format=torch.channels_last)
+        crit = torch.nn.CrossEntropyLoss()
+
+        def step():
+            opt.zero_grad(set_to_none=True)
+            loss = crit(model(xc), y)
+            loss.backward()
+            opt.step()
+            return loss
+
+        for _ in range(max(warmup, 3)):
+            step()
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms, peak = e0.elapsed_time(e1) / steps, torch.cuda.max_memory_allocated()
+        del model, opt
+        torch.cuda.empty_cache()
+        return ms, peak
+    finally:
+        torch.backends.cudnn.allow_tf32, torch.backends.cudnn.benchmark, torch.backends.cuda.matmul.allow_tf32 = old
+
+
+def _stats(ms_list):
+    return {"min": min(ms_list), "median": statistics.median(ms_list), "max": max(ms_list)}
+
+
 # ----------------------------------------------------------------------------- ours
 def run_ours(args):
+    import math
+
     import torch
     import torch.distributed as dist
-    import torchvision
 
     from monet_b200 import _lib, build, runner
+    from monet_b200 import dist as mbdist
+    from monet_b200 import functional as F
     from monet_b200.lm_ops.softmax import SoftmaxCrossEntropy
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the operators)")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
-    if not _lib.LIB_PATH.exists():
-        build.build()
+    rank, world = mbdist.init_from_env(dev)
+    import shutil
+    if shutil.which("nvcc") or not _lib.LIB_PATH.exists():
+        build.build()                      # incremental: never time a library older than its sources
     api = _lib.lib()
 
+    make_model, default_batch, in_shape, classes, default_schedule, workload = workloads()[args.model]
+    B = args.batch or default_batch
+    schedule = args.schedule or default_schedule
+    pixelwise = args.model == "unet"
+    metric = METRIC if args.model == "resnet50" and B == 184 else f"{args.model}_bs{B}_train_images_per_s"
+
     torch.manual_seed(0)
-    model = torchvision.models.resnet50().to(dev).train()
+    ctor = (lambda: make_model()) if args.model == "unet" else (lambda: make_model(num_classes=classes))
+    model = ctor().to(dev).train()
     model = model.to(memory_format=torch.channels_last)       # filters as [K][R][S][C]
     params = [p for p in model.parameters()]
     opt = torch.optim.SGD(params, lr=0.1, momentum=0.9)
-    flat, views = None, None
-    if world > 1:                      # one flat bucket for the NCCL all-reduce of the gradients
-        flat = torch.zeros(sum(p.numel() for p in params), device=dev)
-        views, off = [], 0
-        for p in params:
-            views.append(flat[off:off + p.numel()].view(p.shape))
-            off += p.numel()
-    policy = getattr(runner, args.schedule)
-    run = runner.Runner(model, policy, fuse=not args.no_fuse, channel_sums=not args.no_channel_sums)
+
+    def make_runner(fuse, policy_name):
+        policy = getattr(runner, policy_name)
+        if not fuse and policy_name == "budget_10gb":
+            policy = runner.low_memory            # the block-output rule needs the fused block nodes
+        return runner.Runner(model, policy, fuse=fuse, channel_sums=not args.no_channel_sums)
+
+    run = make_runner(not args.no_fuse, schedule)
+    buckets = None
+    if world > 1:
+        buckets = mbdist.GradientBuckets(list(model.named_parameters()), n_buckets=args.buckets)
+        buckets.install(run)
     ce = SoftmaxCrossEntropy()
 
-    B = args.batch
     g = torch.Generator(device="cpu").manual_seed(1 + rank)
-    x_host = torch.randn(B, 3, 224, 224, generator=g).pin_memory()
-    y_host = torch.randint(0, 1000, (B,), generator=g).pin_memory()
+    x_host = torch.randn(B, *in_shape, generator=g).pin_memory()
+    label_shape = (B,) + (tuple(in_shape[1:]) if pixelwise else ())
+    y_host = torch.randint(0, classes, label_shape, generator=g).pin_memory()
     x_dev = x_host.to(dev)
     y_dev = y_host.to(dev)
+    fixed_bytes = sum(p.numel() * 4 for p in params) * 3 + x_dev.numel() * 4 + y_dev.numel() * 8
 
-    def fwd_bwd(x, y):
-        for p in params:
-            p.grad = None              # the backward hands over freshly written gradients
-        out = run.forward(x)
-        loss = ce.forward(out, y)
-        run.backward(ce.backward())
-        if world > 1:
-            torch._foreach_copy_(views, [p.grad for p in params])
-        return loss
+    def make_step(run_):
+        def step(x, y):
+            for p in params:
+                p.grad = None              # the backward hands over freshly written gradients
+            out = run_.forward(x)
+            loss = ce.forward(out, y)
+            run_.backward(ce.backward())
+            if buckets is not None:
+                buckets.wait()             # every bucket was all-reduced on the comm stream meanwhile
+            opt.step()
+            return loss
+        return step
 
-    def reduce_grads():
-        dist.all_reduce(flat)
-        flat.div_(world)
-        for p, v in zip(params, views):
-            p.grad = v
-
-    def step(x, y):
-        loss = fwd_bwd(x, y)
-        if world > 1:
-            reduce_grads()
-        opt.step()
-        return loss
+    step = make_step(run)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- warm-up (first step also autotunes nothing: variants are fixed) + survey of families
+    def timed(fn, n):
+        """n calls of fn(), one CUDA event per step boundary: (mean ms, per-step ms list)."""
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(n + 1)]
+        barrier()
+        evs[0].record()
+        for i in range(n):
+            fn()
+            evs[i + 1].record()
+        barrier()
+        per = [evs[i].elapsed_time(evs[i + 1]) for i in range(n)]
+        return evs[0].elapsed_time(evs[n]) / n, per
+
+    # ---- warm-up, then a survey of every entry-point family over `survey_steps` eager steps
     fam_events = {}
     stream = torch.cuda.current_stream()
     watch = None
@@ -405,59 +581,53 @@ def run_ours(args):
             ev.record(stream)
             fam_events[name][-1][1] = ev
 
-    for i in range(max(args.warmup, 3)):
-        if i == max(args.warmup, 3) - 1:
-            _lib.set_probe(before, after)            # survey: every family, one untimed step
+    W = max(args.warmup, 3)
+    for _ in range(W):
+        loss = step(x_dev, y_dev)
+    torch.cuda.synchronize()
+    survey_steps = 2
+    _lib.set_probe(before, after)
+    for _ in range(survey_steps):
         loss = step(x_dev, y_dev)
     torch.cuda.synchronize()
     _lib.set_probe()
-    survey = {k: sum(a.elapsed_time(b) for a, b in v) for k, v in fam_events.items()}
-    costs = family_costs(run, (B, 3, 224, 224))
+    survey = {k: sum(a.elapsed_time(b) for a, b in v) / survey_steps for k, v in fam_events.items()}
+    survey_calls = {k: len(v) / survey_steps for k, v in fam_events.items()}
+    costs = family_costs(run, (B,) + tuple(in_shape))
     dominant = max((k for k in survey if k in costs), key=lambda k: survey[k])
     fam_events.clear()
     watch = {dominant}
 
-    # ---- timed region 1: batch resident in HBM
+    # ---- timed region 1: eager launches, batch resident in HBM
     sampler = ClockSampler(local)
     sampler.start()
     torch.cuda.reset_peak_memory_stats()
     launches0 = api.mb_launch_count()
     _lib.set_probe(before, after)
-    barrier()
-    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for _ in range(args.steps):
-        loss = step(x_dev, y_dev)
-    t1.record()
-    barrier()
+    ms_eager, per_eager = timed(lambda: step(x_dev, y_dev), args.steps)
     _lib.set_probe()
     launches = api.mb_launch_count() - launches0
-    # host time to enqueue one step, taken on an idle GPU so that a full launch queue does not
-    # hold the host back (untimed extra step)
     h0 = time.perf_counter()
-    loss = step(x_dev, y_dev)
+    loss = step(x_dev, y_dev)              # host time to enqueue one step on an idle GPU
     host_ms = (time.perf_counter() - h0) * 1e3
     barrier()
-    ms_dev = t0.elapsed_time(t1) / args.steps
-    ms_eager = ms_dev
+    ms_dev, per_step = ms_eager, per_eager
     peak = torch.cuda.max_memory_allocated()
+    dom_ms = sum(a.elapsed_time(b) for a, b in fam_events[dominant]) / args.steps
+    dom_calls = len(fam_events[dominant]) / args.steps
 
-    # ---- timed region 1g: the same step replayed from a CUDA graph (forward, loss, backward and,
-    # on one GPU, the optimiser; with several GPUs the NCCL all-reduce and the optimiser stay
-    # outside the capture).  The executor is a Python loop that enqueues a step in ~12 ms; the
-    # replay is one host call.  The eager region above stays: its CUDA events time the dominant
-    # entry point for the roofline, and a captured step launches exactly what it launched.
+    # ---- timed region 1g: the whole step (forward, loss, backward, bucketed all-reduce,
+    # optimiser) replayed from one CUDA graph.  The executor is a Python loop that enqueues a
+    # step in ~12 ms; the replay is one host call and launches exactly what the eager step did.
     graph, graph_err, host_replay_ms = None, None, None
     x_st, y_st = x_dev.clone(), y_dev.clone()
     if not args.no_cuda_graph:
         try:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                loss_st = fwd_bwd(x_st, y_st)
-                if world == 1:
-                    opt.step()
+                loss_st = step(x_st, y_st)
         except Exception as exc:          # capture refused: keep the eager numbers
-            graph, graph_err = None, f"{type(exc).__name__}: {exc}"[:200]
+            graph, graph_err = None, f"{type(exc).__name__}: {exc}"[:300]
             torch.cuda.synchronize()
 
     def gstep(x, y):
@@ -465,31 +635,19 @@ def run_ours(args):
             x_st.copy_(x, non_blocking=True)
             y_st.copy_(y, non_blocking=True)
         graph.replay()
-        if world > 1:
-            reduce_grads()
-            opt.step()
         return loss_st
 
     if graph is not None:
         for _ in range(3):
             loss = gstep(x_st, y_st)
-        barrier()
-        g0 = torch.cuda.Event(enable_timing=True); g1 = torch.cuda.Event(enable_timing=True)
-        g0.record()
-        for _ in range(args.steps):
-            loss = gstep(x_st, y_st)
-        g1.record()
-        barrier()
-        ms_dev = g0.elapsed_time(g1) / args.steps
+        ms_dev, per_step = timed(lambda: gstep(x_st, y_st), args.steps)
         h0 = time.perf_counter()
         loss = gstep(x_st, y_st)
         host_replay_ms = (time.perf_counter() - h0) * 1e3
         barrier()
     run_step = gstep if graph is not None else step
-    dom_ms = sum(a.elapsed_time(b) for a, b in fam_events[dominant]) / args.steps
-    dom_calls = len(fam_events[dominant]) / args.steps
 
-    # ---- timed region 2: end to end from pinned host memory, loss read back every step
+    # ---- timed region 2: end to end from pinned host memory, loss read back every step.
     # Inputs are double-buffered: the batch of step i+1 crosses PCIe on a copy stream while
     # step i computes; every step's batch is copied inside the timed region.
     copy_stream = torch.cuda.Stream()
@@ -531,58 +689,131 @@ def run_ours(args):
     barrier()
     ms_e2e = max(e0.elapsed_time(e1), (time.perf_counter() - w0) * 1e3) / args.steps
     clocks = sampler.stop()
+    conv_status = F.conv_device_status()
 
     if world > 1:
-        t = torch.tensor([ms_dev, ms_e2e], device=dev)
+        t = torch.tensor([ms_dev, ms_e2e, ms_eager], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_dev, ms_e2e = float(t[0]), float(t[1])
+        ms_dev, ms_e2e, ms_eager = float(t[0]), float(t[1]), float(t[2])
+
+    # ---- comparators, rank 0 at N = 1 only (they are about one GPU): the reference's node set
+    # (no fused nodes) through the same executor, and stock PyTorch on this GPU
+    extras = {}
+    if rank == 0 and world == 1 and not args.no_comparators:
+        del graph
+        graph = None
+        torch.cuda.empty_cache()
+        if not args.no_fuse:
+            run_u = make_runner(False, schedule)
+            step_u = make_step(run_u)
+            for _ in range(3):
+                step_u(x_dev, y_dev)
+            torch.cuda.synchronize()
+            torch.cuda.reset_peak_memory_stats()
+            ms_u_eager, _ = timed(lambda: step_u(x_dev, y_dev), args.steps)
+            peak_u = torch.cuda.max_memory_allocated()
+            ms_u = ms_u_eager
+            try:
+                gu = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gu):
+                    step_u(x_st, y_st)
+                for _ in range(2):
+                    gu.replay()
+                ms_u, _ = timed(gu.replay, args.steps)
+                del gu
+            except Exception:
+                torch.cuda.synchronize()
+            extras["unfused"] = {"ms_per_step": ms_u, "eager_ms_per_step": ms_u_eager, "peak_gb": peak_u / 2 ** 30,
+                                 "what": "the reference's node set (batch norm, add, ReLU as separate operators), "
+                                         "same schedule family, same executor"}
+            del run_u, step_u
+            for p in params:
+                p.grad = None
+            torch.cuda.empty_cache()
+        tms, tpeak = torch_gpu_baseline(ctor, x_dev, y_dev, args.steps, W, pixelwise)
+        extras["torch_gpu"] = {"ms_per_step": tms, "images_per_s": B / (tms * 1e-3), "peak_gb": tpeak / 2 ** 30,
+                               "what": "stock PyTorch eager, channels_last, cuDNN TF32 + benchmark, same batch, CE + SGD"}
+        extras["overhead_vs_torch_gpu"] = ms_dev / tms - 1.0
+        if "unfused" in extras:
+            extras["unfused"]["overhead_vs_torch_gpu"] = extras["unfused"]["ms_per_step"] / tms - 1.0
+    tf32_measured = measure_tf32_peak(dev) if rank == 0 else None
 
     if rank == 0:
         peaks_file = ROOT / "MEASURED_PEAKS.json"
         if peaks_file.exists():
             mp = json.loads(peaks_file.read_text())
-            hbm, tf32, which = mp["hbm_gbs"], mp["bf16_tflops_sustained"] / 2, "measured"
+            hbm, which = mp["hbm_gbs"], "measured"
         else:
-            hbm, tf32, which = 6650.0, 1590.0 / 2, "fallback"
+            hbm, which = 6650.0, "fallback"
+        tf32 = tf32_measured
+
+        def roof_of(b, f, ms):
+            t_hbm, t_tc = b / (hbm * 1e9), f / (tf32 * 1e12)
+            if t_hbm >= t_tc:
+                r = {"bound": "hbm", "achieved": b / (ms * 1e-3) / 1e9, "peak": hbm, "unit": "GB/s"}
+            else:
+                r = {"bound": "tensor", "achieved": f / (ms * 1e-3) / 1e12, "peak": tf32, "unit": "TFLOP/s"}
+            r["frac"] = r["achieved"] / r["peak"]
+            return r
+
         b, f = costs[dominant]
-        t_hbm, t_tc = b / (hbm * 1e9), f / (tf32 * 1e12)
-        if t_hbm >= t_tc:
-            roof = {"bound": "hbm", "achieved": b / (dom_ms * 1e-3) / 1e9, "peak": hbm, "unit": "GB/s"}
-        else:
-            roof = {"bound": "tensor", "achieved": f / (dom_ms * 1e-3) / 1e12, "peak": tf32, "unit": "TFLOP/s"}
-        roof["frac"] = roof["achieved"] / roof["peak"]
+        roof = roof_of(b, f, dom_ms)
         ratio = TRAFFIC_RATIO.get(dominant)
         roof.update({"traffic": (ratio * b / dom_calls / 1e9) if ratio else None, "traffic_unit": "GB per launch (ncu ratio x algorithmic bytes)",
                      "algorithmic_gb_per_launch": b / dom_calls / 1e9, "kernel": dominant, "launches_per_step": dom_calls,
                      "ms_per_step": dom_ms, "peak_source": which,
                      "note": "entry point timed with CUDA events inside the eager timed region (the graphed "
-                             "region replays the same launches); tensor peak = measured sustained bf16 / 2 (TF32)"})
+                             "region replays the same launches); tensor peak = cuBLAS TF32 8192^3 sustained, measured in this run"})
+        families = {}
+        for k, ms in sorted(survey.items(), key=lambda kv: -kv[1]):
+            if k not in costs or ms <= 0:
+                continue
+            fb, ff = costs[k]
+            r = roof_of(fb, ff, ms)
+            families[k] = {"ms_per_step": round(ms, 3), "calls_per_step": survey_calls[k], "algorithmic_gb": round(fb / 1e9, 3),
+                           "gflop": round(ff / 1e9, 1), "bound": r["bound"], "achieved": round(r["achieved"], 1),
+                           "unit": r["unit"], "frac": round(r["frac"], 3)}
+        conv_ms = sum(v["ms_per_step"] for k, v in families.items() if k.startswith("mb_conv2d"))
+        conv_fl = sum(costs[k][1] for k in families if k.startswith("mb_conv2d"))
         line = {
-            "metric": METRIC, "value": B * world / (ms_dev * 1e-3), "unit": "images/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_dev,
+            "metric": metric, "value": B * world / (ms_dev * 1e-3), "unit": "images/s",
+            "n_gpus": world, "steps": args.steps, "warmup": W, "ms_per_step": ms_dev,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32(tf32 conv)",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD, "schedule": args.schedule,
+            "config": {"workload": workload, "schedule": schedule,
                        "fused_bn_add_relu": not args.no_fuse, "global_batch": B * world,
                        "parallelism": f"dp{world}", "l2": "inputs and activations exceed L2 (126 MB) many times over"},
-            "peak_gb": peak / 2 ** 30, "loss": last,
+            "peak_gb": peak / 2 ** 30, "activation_peak_gb": (peak - fixed_bytes) / 2 ** 30,
+            "loss": last, "loss_finite": math.isfinite(last), "conv_device_status": conv_status,
             "e2e": {"value": B * world / (ms_e2e * 1e-3), "unit": "images/s",
                     "h2d_bytes_per_step": x_host.numel() * 4 + y_host.numel() * 8, "d2h_bytes_per_step": 4},
-            "cuda_graph": graph is not None, "eager_ms_per_step": ms_eager,
+            "cuda_graph": graph_err is None and not args.no_cuda_graph, "eager_ms_per_step": ms_eager,
+            "ms_per_step_stats": _stats(per_step), "eager_ms_per_step_stats": _stats(per_eager),
             "host_enqueue_ms": host_ms, "host_replay_ms": host_replay_ms,
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
-            "family_ms_survey": {k: round(v, 3) for k, v in sorted(survey.items(), key=lambda kv: -kv[1])[:12]},
+            "tf32_peak_measured_tflops": tf32,
+            "roofline_families": families,
+            "conv_total": {"ms_per_step": round(conv_ms, 3), "tflops": round(conv_fl / (conv_ms * 1e-3) / 1e12, 1) if conv_ms else None,
+                           "frac_of_measured_tf32": round(conv_fl / (conv_ms * 1e-3) / 1e12 / tf32, 3) if conv_ms else None},
         }
+        if buckets is not None:
+            line["gradient_buckets"] = {"count": len(buckets.buckets), "mb": [round(fl.numel() * 4 / 2 ** 20, 1) for fl in buckets.flat],
+                                        "overlap": "all-reduce (mean) per bucket on a communication stream during backward, inside the captured step"}
+        line.update(extras)
         if graph_err:
             line["cuda_graph_error"] = graph_err
-        if not args.no_cpu_baseline and world >= 1:
+        if not args.no_cpu_baseline and world == 1 and args.model == "resnet50":
             from oracle import cpu_baseline
-            ips, ms, threads = cpu_baseline.resnet50_train_steps(args.cpu_batch, 2, warmup=1)
+            cb = args.cpu_batch or B
+            ips, ms, threads = cpu_baseline.resnet50_train_steps(cb, 2, warmup=1)
             line["cpu_baseline"] = {"value": ips, "unit": "images/s", "cores": threads, "kind": "port",
-                                    "sample": f"2 eager steps of batch {args.cpu_batch} (of 184), PyTorch CPU"}
+                                    "sample": f"2 eager steps of batch {cb} (of {B}), PyTorch CPU"}
         print(json.dumps(line), flush=True)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
+    if conv_status != 0 or not math.isfinite(last):
+        raise SystemExit(f"invalid run: conv_device_status={conv_status}, loss={last}")
 
 
 def main():

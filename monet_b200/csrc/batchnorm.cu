@@ -72,7 +72,7 @@ Geometry make_geometry(const mb_bn_desc* d) {
     size_t rows_per_cta_min = static_cast<size_t>(g.ty) * 8;
     size_t want = (g.M + rows_per_cta_min - 1) / rows_per_cta_min;
     // one wave: 4 CTAs of 256 threads are resident per SM at the kernels' register use
-    size_t cap = static_cast<size_t>(kNumSMs) * 4 / g.slabs;
+    size_t cap = static_cast<size_t>(num_sms()) * 4 / g.slabs;
     if (cap < 1) cap = 1;
     g.S = static_cast<int>(want < cap ? want : cap);   // at most 592 partials per channel
   } else {
@@ -80,7 +80,7 @@ Geometry make_geometry(const mb_bn_desc* d) {
     g.tx = g.ty = 0;
     g.slabs = 1;
     size_t want = (g.M + 4095) / 4096;
-    size_t cap = static_cast<size_t>(kNumSMs) * 8 / (d->C > 0 ? d->C : 1);
+    size_t cap = static_cast<size_t>(num_sms()) * 8 / (d->C > 0 ? d->C : 1);
     if (cap < 1) cap = 1;
     g.S = static_cast<int>(want < cap ? want : cap);
   }
@@ -115,10 +115,8 @@ cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-  // MB_NO_PDL=1 in the environment launches the chain with plain stream order (for A/B timing)
-  static const bool plain = std::getenv("MB_NO_PDL") != nullptr;
   cfg.attrs = attr;
-  cfg.numAttrs = plain ? 0 : 1;
+  cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
@@ -569,7 +567,7 @@ int run_sweep(const char* who, const mb_bn_desc* d, const Geometry& g, const flo
               const float* b, float* out, const SweepConst& k, cudaStream_t st) {
   if (d->layout == MB_NHWC) {
     size_t want = (g.M + static_cast<size_t>(g.ty) * 4 - 1) / (static_cast<size_t>(g.ty) * 4);
-    size_t cap = static_cast<size_t>(kNumSMs) * 8 / g.slabs;
+    size_t cap = static_cast<size_t>(num_sms()) * 8 / g.slabs;
     if (cap < 1) cap = 1;
     dim3 grid(static_cast<unsigned>(want < cap ? want : cap), g.slabs);
     if (grid.x < 1) grid.x = 1;

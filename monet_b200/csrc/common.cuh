@@ -7,8 +7,10 @@
 
 namespace mb {
 
-// B200: 148 SMs.  Grids of grid-stride kernels are sized as a multiple of it.
-constexpr int kNumSMs = 148;
+// SM count of the current device (cudaDevAttrMultiProcessorCount, cached per device; 148 on a
+// B200, which is also the answer when no device can be queried, e.g. a workspace-size call on a
+// machine without a GPU).  Grids of grid-stride and persistent kernels are sized from it.
+int num_sms();
 
 // Records a printf-style message for mb_last_error() and returns `code`.
 int fail(int code, const char* fmt, ...);
@@ -23,7 +25,7 @@ inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_
 // at a time: enough CTAs to cover the work, capped at `waves` CTAs per SM.
 inline int grid_for(size_t work_items, size_t per_block, int ctas_per_sm) {
   size_t need = (work_items + per_block - 1) / per_block;
-  size_t cap = static_cast<size_t>(kNumSMs) * ctas_per_sm;
+  size_t cap = static_cast<size_t>(num_sms()) * ctas_per_sm;
   if (need < 1) need = 1;
   return static_cast<int>(need < cap ? need : cap);
 }

@@ -17,6 +17,7 @@
 #include "conv_wgrad_halo.cuh"
 
 #include <cstring>
+#include <atomic>
 #include <mutex>
 
 namespace mb {
@@ -146,7 +147,7 @@ void pick_bn_stages(int kout, long long m_tiles, int* BN, int* stages, size_t* s
   // more than one wave the wide tile wins even when the last wave is half empty (measured:
   // 3x3/2 512->512 at 14x14, 184 wide tiles on 148 SMs 0.13 ms, 736 narrow ones 0.27 ms).
   auto tiles = [&](int b) { return m_tiles * ((kout + b - 1) / b); };
-  while (bn > 64 && bn % 64 == 0 && tiles(bn / 2) <= kNumSMs) bn /= 2;
+  while (bn > 64 && bn % 64 == 0 && tiles(bn / 2) <= num_sms()) bn /= 2;
   const size_t stage = kAStageBytes + static_cast<size_t>(bn) * 128;
   const size_t staging = 2 * kAStageBytes;            // TMA-store epilogue buffers
   int st = static_cast<int>((220 * 1024 - 2048 - staging - extra_bytes) / stage);
@@ -168,16 +169,27 @@ struct GemmLaunch {
   int grid;
 };
 
+// Opt a kernel in to 227 KB of dynamic shared memory.  Function attributes belong to a device,
+// so what is remembered is one bit per (kernel, device): a process that drives several GPUs sets
+// the attribute on each, and a failed attempt is not remembered.
+template <class Kernel>
+int raise_smem_limit(const char* who, Kernel kernel, std::atomic<unsigned long long>& done) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess)
+    return fail(MB_ERR_LAUNCH, "%s: no current CUDA device", who);
+  const unsigned long long bit = dev < 64 ? (1ull << dev) : 0ull;
+  if (bit && (done.load(std::memory_order_acquire) & bit)) return MB_OK;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (e != cudaSuccess)
+    return fail(MB_ERR_LAUNCH, "%s: cannot raise the shared-memory limit: %s", who, cudaGetErrorString(e));
+  if (bit) done.fetch_or(bit, std::memory_order_release);
+  return MB_OK;
+}
+
 int launch_gemm(const char* who, GemmLaunch& L, cudaStream_t st) {
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(conv_gemm_kmajor<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (attr_err == cudaSuccess)
-      attr_err = cudaFuncSetAttribute(conv_gemm_kmajor<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-  });
-  if (attr_err != cudaSuccess)
-    return fail(MB_ERR_LAUNCH, "%s: cannot raise the shared-memory limit: %s", who, cudaGetErrorString(attr_err));
+  static std::atomic<unsigned long long> done_plain{0}, done_stats{0};
+  if (int rc = raise_smem_limit(who, conv_gemm_kmajor<false>, done_plain)) return rc;
+  if (int rc = raise_smem_limit(who, conv_gemm_kmajor<true>, done_stats)) return rc;
   // output view {Kout, Q, P, N} with the tile's box: the epilogue stores whole tiles with TMA
   {
     GemmParams& p = L.p;
@@ -202,14 +214,6 @@ int launch_gemm(const char* who, GemmLaunch& L, cudaStream_t st) {
   else
     conv_gemm_kmajor<false><<<L.grid, 192, L.smem, st>>>(L.a[0], L.a[1], L.a[2], L.a[3], L.b, L.out, L.p);
   return after_launch(who);
-}
-
-template <class Kernel>
-int raise_smem_limit(const char* who, Kernel kernel) {
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-  if (e != cudaSuccess)
-    return fail(MB_ERR_LAUNCH, "%s: cannot raise the shared-memory limit: %s", who, cudaGetErrorString(e));
-  return MB_OK;
 }
 
 
@@ -271,9 +275,9 @@ int run_halo(const char* who, const float* in, int Cin, int Win, int Hin, const 
     // 128-column tiles when they fill the SMs' rounds better: an M = 128 MMA takes about 140
     // cycles with 256 columns and 86 with 128 in this kernel, and a round costs its MMAs
     const long long pix_items = static_cast<long long>(p.tiles_h) * ((N + p.bn - 1) / p.bn);
-    const long long rounds256 = (pix_items * p.tiles_c + kNumSMs - 1) / kNumSMs;
+    const long long rounds256 = (pix_items * p.tiles_c + num_sms() - 1) / num_sms();
     const int tiles128 = (Kout + 127) / 128;
-    const long long rounds128 = (pix_items * tiles128 + kNumSMs - 1) / kNumSMs;
+    const long long rounds128 = (pix_items * tiles128 + num_sms() - 1) / num_sms();
     if (rounds128 * 86 < rounds256 * 140) {
       p.BN = 128;
       p.tiles_c = tiles128;
@@ -311,9 +315,9 @@ int run_halo(const char* who, const float* in, int Cin, int Win, int Hin, const 
   if (rc) return rc;
   rc = encode_act(who, &mo, out, Kout, Qo, Po, N, K4, K4 * Qo, K4 * Qo * Po, p.Wh, p.Hout, p.bn);
   if (rc) return rc;
-  static const int attr_rc = raise_smem_limit(who, conv_gemm_halo);
-  if (attr_rc) return attr_rc;
-  const int grid = p.num_items < kNumSMs ? p.num_items : kNumSMs;
+  static std::atomic<unsigned long long> smem_done{0};
+  if (int rc = raise_smem_limit(who, conv_gemm_halo, smem_done)) return rc;
+  const int grid = p.num_items < num_sms() ? p.num_items : num_sms();
   conv_gemm_halo<<<grid, 192, smem, st>>>(ma, mb_, mo, p);
   return after_launch("conv_gemm_halo");
 }
@@ -404,7 +408,7 @@ int wgrad_finish(const char* who, int variant, int splits, const float* dy, floa
       return fail(MB_ERR_LAUNCH, "%s: memset failed", who);
     const size_t pixels = static_cast<size_t>(d->N) * d->P * d->Q;
     int chunks = static_cast<int>((pixels + 2047) / 2048);
-    const int cap = 4 * kNumSMs / ((d->K + 31) / 32) + 1;
+    const int cap = 4 * num_sms() / ((d->K + 31) / 32) + 1;
     if (chunks > cap) chunks = cap;
     dim3 grid((d->K + 31) / 32, chunks);
     bias_grad_kernel<<<grid, 256, 0, st>>>(dy, dbias, pixels, d->K);
@@ -421,8 +425,8 @@ int wgrad_launch(const char* who, wg::Plan& pl, const CUtensorMap& mdy, const CU
   int rc = wgrad_prepare(who, variant, p.splits, p.ntaps >= p.T, dw, dw_elems, workspace,
                          workspace_bytes, st, &p.out, &p.split_stride);
   if (rc) return rc;
-  static const int attr_rc = raise_smem_limit(who, conv_wgrad_tcgen05);
-  if (attr_rc) return attr_rc;
+  static std::atomic<unsigned long long> smem_done{0};
+  if (int rc = raise_smem_limit(who, conv_wgrad_tcgen05, smem_done)) return rc;
   p.prof = g_conv_prof;
   conv_wgrad_tcgen05<<<pl.grid, 192, pl.smem, st>>>(mdy, mx[0], mx[1], mx[2], mx[3], p);
   rc = after_launch("conv_wgrad_tcgen05");
@@ -444,8 +448,8 @@ int wgrad_run_halo(const char* who, wgh::Launches& hl, const float* x, const flo
   int rc = wgrad_prepare(who, variant, hl.plan[0].p.splits, covered >= d->R * d->S, dw, dw_elems, workspace,
                          workspace_bytes, st, &out, &split_stride);
   if (rc) return rc;
-  static const int attr_rc = raise_smem_limit(who, conv_wgrad_halo_tcgen05);
-  if (attr_rc) return attr_rc;
+  static std::atomic<unsigned long long> smem_done{0};
+  if (int rc = raise_smem_limit(who, conv_wgrad_halo_tcgen05, smem_done)) return rc;
   const long long K4 = static_cast<long long>(d->K) * 4, C4 = static_cast<long long>(d->C) * 4;
   for (int i = 0; i < hl.n; ++i) {
     WgHaloParams& p = hl.plan[i].p;
@@ -707,7 +711,7 @@ static int fprop_impl(const char* who, const float* x, const float* w, const flo
   p.num_tiles = static_cast<int>(tiles);
   rc = encode_filter(who, &L.b, w, d->C, d->R * d->S, d->K, p.BN);
   if (rc) return rc;
-  L.grid = p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs;
+  L.grid = p.num_tiles < num_sms() ? p.num_tiles : num_sms();
   p.stats = stats;
   p.stats_shift = stats_shift;
   if (stats_rows) *stats_rows = L.grid;
@@ -723,7 +727,7 @@ int mb_conv2d_fprop(const float* x, const float* w, const float* bias, float* y,
 
 size_t mb_conv_bnstats_bytes(const mb_conv_desc* d) {
   if (!d || d->K <= 0) return 0;
-  return static_cast<size_t>(2) * kNumSMs * d->K * sizeof(float);
+  return static_cast<size_t>(2) * num_sms() * d->K * sizeof(float);
 }
 
 int mb_conv2d_fprop_bnstats(const float* x, const float* w, const float* bias, float* y,
@@ -857,7 +861,7 @@ int mb_conv2d_dgrad(const float* dy, const float* w, float* dx, const mb_conv_de
       rc = filter_mn ? encode_filter_mn(who, &L.b, wt, d->K, T, d->C, p.BN)
                      : encode_filter(who, &L.b, wt, d->K, T, d->C, p.BN);
       if (rc) return rc;
-      L.grid = p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs;
+      L.grid = p.num_tiles < num_sms() ? p.num_tiles : num_sms();
       rc = launch_gemm("conv_dgrad_tcgen05", L, st);
       if (rc) return rc;
     }
@@ -938,7 +942,7 @@ int mb_conv2d_fprop_smallc(const float* xp, const float* wp, const float* bias, 
   p.num_tiles = static_cast<int>(tiles);
   rc = encode_filter(who, &L.b, wp, 32, d->R, d->K, p.BN);
   if (rc) return rc;
-  L.grid = p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs;
+  L.grid = p.num_tiles < num_sms() ? p.num_tiles : num_sms();
   return launch_gemm("conv_fprop_smallc_tcgen05", L, as_stream(stream));
 }
 

@@ -467,7 +467,7 @@ inline bool make_plan(const mb_conv_desc* d, int variant, Plan* pl, bool smallc 
   // splits: one wave of CTAs (every extra CTA adds a full tile of atomics / partials to
   // combine), at least 4 pixel tiles per split
   const int items = p.k_tiles * p.groups;
-  int splits = kNumSMs / items;
+  int splits = num_sms() / items;
   const int max_splits = (p.pix_tiles + 3) / 4;
   if (splits > max_splits) splits = max_splits;
   if (splits < 1) splits = 1;

@@ -334,7 +334,7 @@ inline bool plan_launch(int K, int C, int T, int N, int P, int Q, const Tap* tap
   const int items = p.k_tiles * p.cchunks;
   // one wave of CTAs: the kernel is bound by MMA issue, a second wave would only repeat the
   // set-up and double the number of partial results to combine
-  int splits = kNumSMs / items;
+  int splits = num_sms() / items;
   const int max_splits = (p.pix_tiles + 3) / 4;
   if (splits > max_splits) splits = max_splits;
   if (splits < 1) splits = 1;

@@ -412,7 +412,7 @@ int mb_depthwise_wgrad(const float* x, const float* dy, float* dw_tc, float* dbi
   const int slabs = (groups + tx - 1) / tx;
   const size_t pixels = static_cast<size_t>(p.N) * p.P * p.Q;
   int chunks = static_cast<int>((pixels + ty * 8 - 1) / (static_cast<size_t>(ty) * 8));
-  const int cap = kNumSMs * 4 / slabs > 0 ? kNumSMs * 4 / slabs : 1;
+  const int cap = num_sms() * 4 / slabs > 0 ? num_sms() * 4 / slabs : 1;
   if (chunks > cap) chunks = cap;
   if (chunks < 1) chunks = 1;
   const size_t smem = 256 * sizeof(float4);

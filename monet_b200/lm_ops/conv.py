@@ -12,7 +12,9 @@ reference, in who picks the variant ("algorithm"):
 
 A variant that cannot run raises ``RuntimeError``; like the reference (conv.py:279-283) the
 operator then retries with the default variant.  Depthwise convolutions (groups == C) run the
-bandwidth-bound depthwise kernels.  Outputs are channels_last tensors.
+bandwidth-bound depthwise kernels.  Transposed convolutions, which the reference refuses
+(conv.py:269), run the same tensor-core kernels with the passes exchanged.  Outputs are
+channels_last tensors.
 """
 from __future__ import annotations
 
@@ -102,12 +104,65 @@ class _ConvBase(OP):
                 raise
             return F.conv2d_wgrad(x, dy, w_shape, stride, padding, dilation, groups, 0, need_bias)
 
-    def _remember(self, input_, weight, bias, stride, padding, dilation, groups):
+    def _remember(self, input_, weight, bias, stride, padding, dilation, groups, transposed=False,
+                  output_padding=(0, 0)):
         self.params = (stride, padding, dilation, groups, tuple(input_.shape), tuple(weight.shape),
                        [input_.requires_grad, weight.requires_grad,
-                        bias is not None and bias.requires_grad])
+                        bias is not None and bias.requires_grad], bool(transposed),
+                       tuple(int(v) for v in output_padding))
+
+    # -- transposed convolution -------------------------------------------------------------
+    # Beyond the reference, whose operators assert `not transposed` (conv.py:269): a transposed
+    # convolution with filter W[C_in][C_out][R][S] is, pass for pass, the ordinary convolution
+    # C_out -> C_in with the same filter read as [K = C_in][C = C_out][R][S], run backwards:
+    #   forward          y  = dgrad(dy := x, W)          (output extent (H-1)*s - 2p + d(R-1) + op + 1)
+    #   backward-data    dx = fprop(x := dy, W)
+    #   backward-filter  dW = wgrad(x := dy, dy := x)
+    # so it runs on the same tcgen05 kernels (a 2x2 stride-2 up-convolution is four 1x1 phase
+    # GEMMs).  The bias is added by the element-wise kernel, db is a plain reduction.
+    def _transposed_out_shape(self, x, w):
+        stride, padding, dilation, groups = self.params[:4]
+        op = self.params[8]
+        sh, sw = F._pair(stride); ph, pw = F._pair(padding); dh, dw = F._pair(dilation)
+        N, _, H, W = (int(v) for v in x.shape)
+        R, S = int(w.shape[2]), int(w.shape[3])
+        return (N, int(w.shape[1]), (H - 1) * sh - 2 * ph + dh * (R - 1) + op[0] + 1,
+                (W - 1) * sw - 2 * pw + dw * (S - 1) + op[1] + 1)
+
+    def _forward_transposed(self, x, w, bias, variant):
+        stride, padding, dilation, groups = self.params[:4]
+        if groups != 1:
+            raise NotImplementedError("grouped transposed convolution")
+        y = F.conv2d_dgrad(x, w, self._transposed_out_shape(x, w), stride, padding, dilation, 1, 0)
+        if bias is not None:
+            y = F.add_channel_bias(y, bias.detach())
+        return y
+
+    def _backward_transposed(self, grad_output, stored, nodel, convtype):
+        with torch.no_grad():
+            input_, weight = stored
+            stride, padding, dilation = self.params[:3]
+            do_grad = self.params[6]
+            if not nodel:
+                del stored[1]
+                del stored[0]
+            di = dw = db = None
+            if convtype in (0, 2) and input_ is not None:
+                if do_grad[1]:
+                    dw, _ = F.conv2d_wgrad(grad_output, input_.detach(), tuple(self.params[5]), stride,
+                                           padding, dilation, 1, 0, False)
+                if do_grad[2]:
+                    db = grad_output.sum((0, 2, 3))
+            del input_
+            if convtype in (1, 2) and weight is not None and do_grad[0]:
+                di = F.conv2d_fprop(grad_output, weight.detach(), None, stride, padding, dilation, 1, 0)
+            if do_grad[2]:
+                return di, dw, db
+            return di, dw
 
     def _backward(self, grad_output, stored, nodel, convtype, wt_variant, ip_variant):
+        if len(self.params) > 7 and self.params[7]:
+            return self._backward_transposed(grad_output, stored, nodel, convtype)
         with torch.no_grad():
             input_, weight = stored
             groups, do_grad = self.params[3], self.params[6]
@@ -137,10 +192,10 @@ class PytorchConvolution(_ConvBase):
 
     def forward(self, input_, weight, bias, stride, padding, dilation, transposed,
                 output_padding, groups, *args, **kwargs):
-        if transposed:
-            raise NotImplementedError("transposed convolution")
         with torch.no_grad():
-            self._remember(input_, weight, bias, stride, padding, dilation, groups)
+            self._remember(input_, weight, bias, stride, padding, dilation, groups, transposed, output_padding)
+            if transposed:
+                return self._forward_transposed(input_.detach(), weight.detach(), bias, 0)
             return self._fprop(input_.detach(), weight.detach(), bias, 0)
 
     def backward(self, grad_output, stored, nodel=False):
@@ -178,11 +233,11 @@ class GreedyAlgoConvolution(_ConvBase):
 
     def forward(self, input_, weight, bias, stride, padding, dilation, transposed,
                 output_padding, groups, *args, **kwargs):
-        if transposed:
-            raise NotImplementedError("transposed convolution")
         with torch.no_grad():
-            self._remember(input_, weight, bias, stride, padding, dilation, groups)
+            self._remember(input_, weight, bias, stride, padding, dilation, groups, transposed, output_padding)
             x, w = input_.detach(), weight.detach()
+            if transposed:
+                return self._forward_transposed(x, w, bias, 0)
             if self.is_depthwise or groups != 1:
                 return self._fprop(x, w, bias, 0)
             if self.fwd_algo == -1:
@@ -191,7 +246,7 @@ class GreedyAlgoConvolution(_ConvBase):
 
     def backward(self, grad_output, stored, nodel=False):
         convtype = self.algorithm // 10 if self.algorithm >= 0 else 2
-        if not (self.is_depthwise or self.params[3] != 1):
+        if not (self.is_depthwise or self.params[3] != 1 or self.params[7]):
             x, w = stored
             do_grad = self.params[6]
             with torch.no_grad():
@@ -212,10 +267,10 @@ class SpecificAlgoConvolution(_ConvBase):
 
     def forward(self, input_, weight, bias, stride, padding, dilation, transposed,
                 output_padding, groups, *args, **kwargs):
-        if transposed:
-            raise NotImplementedError("transposed convolution")
         with torch.no_grad():
-            self._remember(input_, weight, bias, stride, padding, dilation, groups)
+            self._remember(input_, weight, bias, stride, padding, dilation, groups, transposed, output_padding)
+            if transposed:
+                return self._forward_transposed(input_.detach(), weight.detach(), bias, self.algorithm)
             return self._fprop(input_.detach(), weight.detach(), bias, self.algorithm)
 
     def backward(self, grad_output, stored, nodel=False):

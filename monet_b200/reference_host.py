@@ -237,14 +237,15 @@ def wrap_mobilenet(model):
 
 
 def build_solver_info(model, batch: int, model_name: str, mode: str, input_shape=(3, 224, 224),
-                      workdir=None, profile: bool = True, costs=None):
+                      workdir=None, profile: bool = True, costs=None, profiler: str = "reference"):
     """(graph, solver_info) for ``model`` through MONeT's own ``Graph.create`` and
     ``SolverInfo.extract`` (solver_info.py:103-155).
 
     ``profile=True`` is MONeT's behaviour: every implementation of every operator is run on
     the current CUDA device by ``meminfo`` / ``computeinfo`` (meminfo.py) to fill the
-    workspace-memory and run-time tables; ``model`` must then live on that device.  With
-    ``profile=False`` the tables are filled by ``costs(si, graph)`` instead (default:
+    workspace-memory and run-time tables; ``model`` must then live on that device
+    (``profiler="events"`` substitutes ``monet_b200.profiler``'s functions of the same
+    signature: CUDA-event timing on channels_last activations).  With ``profile=False`` the tables are filled by ``costs(si, graph)`` instead (default:
     ``monet_b200.solver.estimate_costs``, a bytes-and-flops model), which needs no GPU.
     """
     ref = activate()
@@ -261,7 +262,15 @@ def build_solver_info(model, batch: int, model_name: str, mode: str, input_shape
             if dev.type != "cuda":
                 raise RuntimeError("profiling the cost tables needs the model on a CUDA device")
             x = torch.randn((batch,) + tuple(input_shape), device=dev)
-            si.extract(graph, x, *list(m.state_dict(keep_vars=True).values()))
+            from . import profiler as own
+            if profiler == "events":
+                own.install(ref)
+            elif profiler != "reference":
+                raise ValueError(f"unknown profiler {profiler!r}")
+            try:
+                si.extract(graph, x, *list(m.state_dict(keep_vars=True).values()))
+            finally:
+                own.uninstall(ref)
         else:
             if costs is None:
                 from .solver import estimate_costs as costs

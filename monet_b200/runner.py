@@ -98,6 +98,13 @@ def extract_graph(model: nn.Module) -> Tuple[List[Node], int]:
                      [x, P('weight'), bias, Arg('const', _as_list(m.stride)),
                       Arg('const', _as_list(m.padding)), Arg('const', _as_list(m.dilation)),
                       Arg('const', False), Arg('const', [0, 0]), Arg('const', m.groups)], fn.target)
+            elif isinstance(m, nn.ConvTranspose2d):
+                bias = P('bias') if m.bias is not None else Arg('const', None)
+                emit(fn, 'aten::_convolution',
+                     [x, P('weight'), bias, Arg('const', _as_list(m.stride)),
+                      Arg('const', _as_list(m.padding)), Arg('const', _as_list(m.dilation)),
+                      Arg('const', True), Arg('const', _as_list(m.output_padding)),
+                      Arg('const', m.groups)], fn.target)
             elif isinstance(m, nn.BatchNorm2d):
                 emit(fn, 'aten::batch_norm',
                      [x, P('weight'), P('bias'), P('running_mean'), P('running_var'),
@@ -240,7 +247,8 @@ def link_channel_sums(nodes: List[Node]) -> None:
         if n.op not in _BN_LIKE or not n.args[5].value or n.args[0].kind != 'node':
             continue
         src = nodes[n.args[0].value]
-        if src.op == 'aten::_convolution' and src.users == [n.id] and src.args[8].value == 1:
+        if (src.op == 'aten::_convolution' and src.users == [n.id] and src.args[8].value == 1
+                and not src.args[6].value):
             n.sums_from = src.id
 
 

@@ -722,3 +722,72 @@ def hand_solution(si, kind: str = "store_all"):
             rf[i + 1 - V, ci, c0] = 1
     fwd, bwd = _expected_cost(tb, r, m, rf, ip)
     return _solution_class()(r, s, m, rf, ip, p, 0.0, fwd, bwd, fwd + bwd)
+
+
+# ------------------------------------------------------------------------------- CLI
+def main(argv=None):
+    """``python -m monet_b200.solver MODEL BS BUDGET MODE [--time_limit S] [--costs ...]``: the
+    command line of monet/cvxpy_solver.py:336-384 (positionals model, batch size, budget in GB,
+    mode) with HiGHS as the only backend.  Writes ``solution_<model>_<bs>_<mode>_<budget>.pkl``
+    (the reference's file name, cvxpy_solver.py:323) under ``--out`` and prints one JSON line."""
+    import argparse
+    import json
+    from pathlib import Path
+
+    import torch
+    import torchvision
+
+    from . import reference_host as rh
+
+    ap = argparse.ArgumentParser(prog="python -m monet_b200.solver")
+    ap.add_argument("model", help='e.g. "resnet50", or an expression like torchvision.models.vgg16_bn()')
+    ap.add_argument("bs", type=int)
+    ap.add_argument("budget", type=float, help="GB, in the ILP's accounting (activations + parameters + gradients)")
+    ap.add_argument("mode", nargs="?", default="inplace_conv_multiway_newnode")
+    ap.add_argument("--time_limit", type=float, default=3600.0)
+    ap.add_argument("--gap", type=float, default=0.01)
+    ap.add_argument("--costs", default="estimate", choices=["estimate", "reference", "events"],
+                    help="cost tables: bytes-and-flops model (no GPU), MONeT's profiler, or the CUDA-event profiler")
+    ap.add_argument("--cost_file", default=None, help="a cost_*.pkl written by an earlier profiling run")
+    ap.add_argument("--height", type=int, default=224)
+    ap.add_argument("--width", type=int, default=224)
+    ap.add_argument("--out", default=None, help="directory for the solution pickle (default: <MONeT root>/data)")
+    ap.add_argument("--verbose", action="store_true")
+    args = ap.parse_args(argv)
+
+    ref = rh.activate()
+    if "(" in args.model:
+        model = eval(args.model, {"torch": torch, "torchvision": torchvision})      # as cvxpy_solver.py:369
+        name = args.model.split(".")[-1].split("(")[0]
+    else:
+        name = args.model
+        model = getattr(torchvision.models, name)()
+    shape = (3, args.height, args.width)
+    out_dir = Path(args.out) if args.out else ref.root / "data"
+    workdir = out_dir.parent if out_dir.name == "data" else out_dir
+    if args.cost_file:
+        import shutil
+        (workdir / "data").mkdir(parents=True, exist_ok=True)
+        si_probe = ref.solver_info.SolverInfo(args.bs, name, args.mode)
+        shutil.copyfile(args.cost_file, workdir / "data" / f"cost_{si_probe.data_path}.pkl")
+    profile = args.costs != "estimate" or bool(args.cost_file)
+    if profile and not args.cost_file:
+        model = model.cuda()
+    graph, si = rh.build_solver_info(model, args.bs, name, args.mode, shape, workdir=workdir,
+                                     profile=profile, profiler="events" if args.costs == "events" else "reference")
+    base = check_solution(si, hand_solution(si, "store_all"))
+    sol = solve(si, args.budget, time_limit=args.time_limit, mip_rel_gap=args.gap, verbose=args.verbose)
+    chk = check_solution(si, sol, args.budget)
+    path = out_dir / ("solution_%s_%4.2f.pkl" % (si.data_path, args.budget))
+    rh.save_solution(si, sol, path)
+    print(json.dumps({"solution": str(path), "budget_gb": args.budget, "ilp_peak_gb": chk["peak_gb"],
+                      "violations": chk["violations"], "expected_cost": sol.runtime_expected,
+                      "store_all_cost": base["cost"], "store_all_ilp_peak_gb": base["peak_gb"],
+                      "overhead_expected": sol.runtime_expected / base["cost"] - 1.0,
+                      "recomputations": int(sol.r[1:].sum()), "in_place": int(sol.ip.sum()),
+                      "solve_time_s": sol.solve_time, "mip_gap": sol.mip_gap, "size": sol.size,
+                      "costs": args.cost_file or args.costs}))
+
+
+if __name__ == "__main__":
+    main()

@@ -162,6 +162,7 @@ _FAKES = {
     "linear_fwd": lambda x, w, b: torch.addmm(b, x, w.t()),
     "linear_wgrad": lambda x, dy: dy.t().mm(x),
     "linear_dgrad": lambda dy, w: dy.mm(w),
+    "add_channel_bias": lambda y, b: y.add_(b.view(1, -1, 1, 1)),
     "cat": lambda ts, dim: torch.cat(list(ts), dim),
     "cat_bwd": lambda g, sizes, dim: [p.contiguous() for p in torch.split(g, sizes, dim=dim)],
 }

@@ -179,3 +179,37 @@ def test_oracle_against_golden_vectors():
     assert np.allclose(s["y"].numpy(), z["stem_y"], atol=1e-5)
     assert np.array_equal(s["mask"], z["stem_mask"]) and np.array_equal(s["nibbles"], z["stem_nibbles"])
     assert np.allclose(s["dw"].numpy(), z["stem_dw"], atol=1e-4)
+
+
+def test_unet_with_transposed_convolution_through_the_runner_on_cpu():
+    """Host logic of the transposed convolution (forward = backward-data kernel, backward-data =
+    forward kernel, backward-filter with operands exchanged), concatenation and per-pixel
+    cross-entropy: a small UNet through the executor on the CPU stand-in of the tensor-level
+    functions, against autograd."""
+    import copy
+    import sys
+    from pathlib import Path
+    sys.path.insert(0, str(Path(__file__).resolve().parent))
+    import cpu_functional
+    import bench
+    from monet_b200 import runner
+    from monet_b200.lm_ops.softmax import SoftmaxCrossEntropy
+    torch.manual_seed(0)
+    model = bench._unet(n_classes=2, base=4).train()
+    x = torch.randn(2, 3, 32, 48)
+    y = torch.randint(0, 2, (2, 32, 48))
+    ref = copy.deepcopy(model)
+    loss_ref = torch.nn.functional.cross_entropy(ref(x), y)
+    loss_ref.backward()
+    for policy in (runner.store_all, runner.low_memory):
+        m = copy.deepcopy(model)
+        run = runner.Runner(m, policy)
+        ce = SoftmaxCrossEntropy()
+        with cpu_functional.patched():
+            loss = ce.forward(run.forward(x), y)
+            run.backward(ce.backward())
+        assert abs(float(loss) - float(loss_ref.detach())) < 1e-5
+        top = max(float(p.grad.abs().max()) for p in ref.parameters())
+        for (k, p), (_, q) in zip(m.named_parameters(), ref.named_parameters()):
+            err = float((p.grad - q.grad).abs().max())
+            assert err < 2e-3 * float(q.grad.abs().max()) + 1e-4 * top, (k, err)

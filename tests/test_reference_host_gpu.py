@@ -114,7 +114,8 @@ class _Tiny(torch.nn.Module):
         return self.fc(torch.flatten(self.avg(x), 1))
 
 
-def test_reference_profiler_fills_the_cost_tables(cuda, tmp_path):
+@pytest.mark.parametrize("profiler", ["reference", "events"])
+def test_reference_profiler_fills_the_cost_tables(cuda, tmp_path, profiler):
     """SolverInfo.extract with MONeT's own meminfo / computeinfo (meminfo.py:6-396,
     solver_info.py:338-427) over every implementation and convolution variant; then the ILP on
     those measured tables and a step under the resulting schedule."""
@@ -126,7 +127,8 @@ def test_reference_profiler_fills_the_cost_tables(cuda, tmp_path):
     torch.manual_seed(0)
     model = _Tiny().to(cuda).train()
     batch = 32
-    graph, si = rh.build_solver_info(model, batch, "tiny", MODE, (3, 32, 32), workdir=tmp_path, profile=True)
+    graph, si = rh.build_solver_info(model, batch, "tiny", MODE, (3, 32, 32), workdir=tmp_path, profile=True,
+                                     profiler=profiler)
     assert (tmp_path / "data" / f"cost_tiny_{batch}_{MODE}.pkl").exists()     # solver_info.py:425-427
     BwdNode = ref.solver_info.BwdNode
     n_conv = 0
