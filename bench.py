@@ -471,6 +471,59 @@ def torch_gpu_baseline(make_model, x, y, steps, warmup, pixelwise):
         torch.backends.cudnn.allow_tf32, torch.backends.cudnn.benchmark, torch.backends.cuda.matmul.allow_tf32 = old
 
 
+SOLVED_10GB = ROOT / "monet_b200" / "schedules" / "solution_resnet50_184_inplace_conv_multiway_newnode_10.00.pkl"
+
+
+def reference_executor_block(model, params, x, y, B, in_shape, args, timed):
+    """The drop-in measured: MONeT's own MONeTWrapper / Schedule (installed under baseline/_ref)
+    executing its own solver's solution over these kernels, eagerly and as one captured CUDA
+    graph.  Uses the committed 10 GB ILP solution when batch and model match it, else a
+    hand-made low-memory solution."""
+    import tempfile
+
+    import torch
+    try:
+        from monet_b200 import graphed, reference_host as rh, solver
+        ref = rh.activate()
+        with tempfile.TemporaryDirectory() as tmp:
+            if SOLVED_10GB.exists() and B == 184:
+                sol_file, what = str(SOLVED_10GB), "ILP solution, 10 GB budget (scipy/HiGHS), " + SOLVED_10GB.name
+            else:
+                graph, si = rh.build_solver_info(model, B, "resnet50", "inplace_conv_multiway_newnode",
+                                                 tuple(in_shape), workdir=tmp, profile=False)
+                sol_file = str(rh.save_solution(si, solver.hand_solution(si, "low_memory"), tmp + "/solution.pkl"))
+                what = "hand-made low-memory solution"
+            wrapped = ref.monet_wrapper.MONeTWrapper(model, sol_file, tuple(in_shape))
+            opt = torch.optim.SGD(params, lr=0.1, momentum=0.9)
+            step = graphed.training_step(wrapped, torch.nn.CrossEntropyLoss(), opt)
+            xs = x.clone()
+            for _ in range(2):
+                step(xs, y)
+            torch.cuda.synchronize()
+            torch.cuda.reset_peak_memory_stats()
+            n = max(2, min(args.steps, 5))
+            ms_eager, _ = timed(lambda: step(xs, y), n)
+            peak = torch.cuda.max_memory_allocated()
+            out = {"solution": what, "eager_ms_per_step": ms_eager, "peak_gb": peak / 2 ** 30,
+                   "what": "monet_wrapper.MONeTWrapper + schedule.Schedule from the reference, unmodified, "
+                           "the reference's node set (no fused nodes), loss by torch"}
+            try:
+                cap = graphed.CapturedStep(step, [xs, y], warmup=1)
+                for _ in range(2):
+                    cap(xs, y)
+                ms_g, _ = timed(lambda: cap(xs, y), args.steps)
+                out["graphed_ms_per_step"] = ms_g
+                out["graphed_images_per_s"] = B / (ms_g * 1e-3)
+                del cap
+            except Exception as exc:      # noqa: BLE001
+                out["graph_error"] = f"{type(exc).__name__}: {exc}"[:200]
+                torch.cuda.synchronize()
+            del wrapped, step, opt
+            return out
+    except Exception as exc:              # noqa: BLE001 - the comparator must not take the bench line down
+        return {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+
+
 def _stats(ms_list):
     return {"min": min(ms_list), "median": statistics.median(ms_list), "max": max(ms_list)}
 
@@ -624,7 +677,9 @@ def run_ours(args):
     if not args.no_cuda_graph:
         try:
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            # with NCCL in the step its watchdog thread polls events while this thread captures
+            mode = {"capture_error_mode": "thread_local"} if world > 1 else {}
+            with torch.cuda.graph(graph, **mode):
                 loss_st = step(x_st, y_st)
         except Exception as exc:          # capture refused: keep the eager numbers
             graph, graph_err = None, f"{type(exc).__name__}: {exc}"[:300]
@@ -736,6 +791,11 @@ def run_ours(args):
         extras["overhead_vs_torch_gpu"] = ms_dev / tms - 1.0
         if "unfused" in extras:
             extras["unfused"]["overhead_vs_torch_gpu"] = extras["unfused"]["ms_per_step"] / tms - 1.0
+        if args.model == "resnet50" and not args.no_fuse:
+            extras["reference_executor"] = reference_executor_block(model, params, x_dev, y_dev, B, in_shape, args, timed)
+            for p in params:
+                p.grad = None
+            torch.cuda.empty_cache()
     tf32_measured = measure_tf32_peak(dev) if rank == 0 else None
 
     if rank == 0:

@@ -879,6 +879,41 @@ def conv2d_wgrad(x, dy, w_shape, stride, padding, dilation, groups=1, variant: i
     return dw, db
 
 
+# ------------------------------------------------------------------ fully connected
+# A fully connected layer is a 1x1 convolution over a 1x1 map: x [N, C] is the NHWC activation
+# [N, C, 1, 1] and W [K, C] the filter [K][1][1][C], byte for byte.  The three passes therefore run
+# on the same tcgen05 kernels (TF32 operands, fp32 accumulation) as the pointwise convolutions,
+# instead of the fp32 SIMT library GEMM the reference calls (linear.py:38,52-60).
+
+def linear_fwd(x: torch.Tensor, w: torch.Tensor, bias) -> torch.Tensor:
+    """x @ w.T + bias for x [N, C], w [K, C]."""
+    _need_cuda(x, w, bias); _f32(x, "x"); _f32(w, "w")
+    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
+        raise RuntimeError("monet_b200.linear_fwd expects x [N, C] and w [K, C]")
+    N, Cc, K = int(x.shape[0]), int(x.shape[1]), int(w.shape[0])
+    y = conv2d_fprop(x.detach().contiguous().view(N, Cc, 1, 1), w.detach().contiguous().view(K, Cc, 1, 1),
+                     bias, 1, 0, 1)
+    return y.reshape(N, K)
+
+
+def linear_dgrad(dy: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """dy @ w for dy [N, K], w [K, C]."""
+    _need_cuda(dy, w); _f32(dy, "dy"); _f32(w, "w")
+    N, K, Cc = int(dy.shape[0]), int(w.shape[0]), int(w.shape[1])
+    dx = conv2d_dgrad(dy.contiguous().view(N, K, 1, 1), w.detach().contiguous().view(K, Cc, 1, 1),
+                      (N, Cc, 1, 1), 1, 0, 1)
+    return dx.reshape(N, Cc)
+
+
+def linear_wgrad(x: torch.Tensor, dy: torch.Tensor, need_bias: bool = False):
+    """(dy.T @ x, dy.sum(0) or None) for x [N, C], dy [N, K]."""
+    _need_cuda(x, dy); _f32(x, "x"); _f32(dy, "dy")
+    N, Cc, K = int(x.shape[0]), int(x.shape[1]), int(dy.shape[1])
+    dw, db = conv2d_wgrad(x.detach().contiguous().view(N, Cc, 1, 1), dy.contiguous().view(N, K, 1, 1),
+                          (K, Cc, 1, 1), 1, 0, 1, 1, 0, need_bias)
+    return dw.reshape(K, Cc), db
+
+
 def conv_device_status(reset: bool = True) -> int:
     """0 when no tensor-core kernel has reported a pipeline time-out (synchronises)."""
     return lib().mb_conv_device_status(int(reset))

@@ -160,7 +160,7 @@ _FAKES = {
     "softmax": lambda x, dim, log=False: oracle.softmax_forward(x, dim, log),
     "softmax_bwd": lambda dy, y, dim, log=False: oracle.softmax_backward(dy, y, dim, log),
     "linear_fwd": lambda x, w, b: torch.addmm(b, x, w.t()),
-    "linear_wgrad": lambda x, dy: dy.t().mm(x),
+    "linear_wgrad": lambda x, dy, need_bias=False: (dy.t().mm(x), dy.sum(0) if need_bias else None),
     "linear_dgrad": lambda dy, w: dy.mm(w),
     "add_channel_bias": lambda y, b: y.add_(b.view(1, -1, 1, 1)),
     "cat": lambda ts, dim: torch.cat(list(ts), dim),

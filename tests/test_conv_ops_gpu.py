@@ -152,3 +152,36 @@ def test_cat_forward_and_backward(cuda, shapes, dim, nhwc):
     for a, b in zip(grads, want_g):
         assert torch.equal(a.cpu(), b)
         assert a.is_contiguous() or a.is_contiguous(memory_format=torch.channels_last)
+
+
+@pytest.mark.parametrize("N,C,K", [(184, 2048, 1000), (8, 512, 10), (176, 25088, 4096), (3, 100, 36)])
+def test_addmm_runs_on_the_tensor_core_kernels(cuda, N, C, K):
+    """LowMemAddMM (linear.py:25-61): forward, the weight/bias step (algorithm 0), the input
+    step (algorithm 10) and both (20), against fp32 CPU matmuls at the convolution tolerance.
+    Includes the classifier of ResNet-50 and the 25088 x 4096 layer of VGG-16."""
+    from monet_b200 import functional as F
+    from monet_b200 import lm_ops
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(N, C, generator=g)
+    w = torch.randn(K, C, generator=g) * C ** -0.5
+    b = torch.randn(K, generator=g)
+    dy = torch.randn(N, K, generator=g)
+    op = lm_ops.list_ops("conv_multiway_newnode", "aten::addmm")[0]()
+    xg, wg, bg = (t.to(cuda).requires_grad_(True) for t in (x, w, b))
+    y = op.forward(bg, xg, wg, 1, 1)
+    assert tuple(y.shape) == (N, K)
+    assert _rel(y, torch.addmm(b, x, w.t())) < 2e-2
+    op.algorithm = 0
+    db, di, dw = op.backward(dy.to(cuda), [xg, wg], nodel=True)
+    assert di is None
+    assert _rel(dw, dy.t().mm(x)) < 2e-2
+    assert torch.allclose(db.cpu(), dy.sum(0), rtol=1e-4, atol=1e-3)
+    op.algorithm = 10
+    db, di, dw = op.backward(dy.to(cuda), [None, wg], nodel=True)
+    assert dw is None and db is None
+    assert _rel(di, dy.mm(w)) < 2e-2
+    op.algorithm = 20
+    stored = [xg, wg]
+    db, di, dw = op.backward(dy.to(cuda), stored)
+    assert stored == [] and di is not None and dw is not None
+    assert F.conv_device_status() == 0
