@@ -516,7 +516,8 @@ def reference_executor_block(model, params, x, y, B, in_shape, args, timed):
                 out["graphed_images_per_s"] = B / (ms_g * 1e-3)
                 del cap
             except Exception as exc:      # noqa: BLE001
-                out["graph_error"] = f"{type(exc).__name__}: {exc}"[:200]
+                out["graph_error"] = f"{type(exc).__name__}: {exc}"[:300]
+                print("reference executor: capture failed:", out["graph_error"], file=sys.stderr, flush=True)
                 torch.cuda.synchronize()
             del wrapped, step, opt
             return out
@@ -599,6 +600,8 @@ def run_ours(args):
         return step
 
     step = make_step(run)
+    # measured before any graph capture (a capture that fails leaves the CUDA generator unusable)
+    tf32_measured = measure_tf32_peak(dev) if rank == 0 else None
 
     def barrier():
         if world > 1:
@@ -796,8 +799,6 @@ def run_ours(args):
             for p in params:
                 p.grad = None
             torch.cuda.empty_cache()
-    tf32_measured = measure_tf32_peak(dev) if rank == 0 else None
-
     if rank == 0:
         peaks_file = ROOT / "MEASURED_PEAKS.json"
         if peaks_file.exists():

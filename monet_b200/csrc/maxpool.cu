@@ -147,100 +147,14 @@ __global__ void __launch_bounds__(256) maxpool_bwd_nhwc8(const float* __restrict
 }
 
 // ------------------------------------------- NHWC, 3x3 window, stride 2, pad 1
-// The pooling of the ResNet stem.  Windows overlap by one row and one column, so a thread
-// that owns a 2x2 block of outputs (forward) or of inputs (backward) shares the loads its
-// four pixels have in common:
-//   forward : 2x2 outputs x 8 channels read a 5x5 input patch once (25 loads instead of 36);
-//   backward: a 2x2 input quad (rows 2a, 2a+1; columns 2b, 2b+1) is covered by the windows
-//             (a, a+1) x (b, b+1) only, so four (gradient, nibble-word) loads serve four
-//             pixels (1 load per pixel instead of 2.25) and the stores are two 64-byte runs.
-// Taps are visited in increasing (i, j) order for every output, so ties resolve exactly as
-// in the one-output-per-thread kernel.
-__global__ void __launch_bounds__(256) maxpool_fwd_3x3s2p1_quad(const float* __restrict__ x,
-                                                                float* __restrict__ y,
-                                                                uint32_t* __restrict__ nib,
-                                                                PoolP p, size_t total) {
-  const int cg = p.C / 8, P2 = (p.P + 1) / 2, Q2 = (p.Q + 1) / 2;
-  for (size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
-       t += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const int g = static_cast<int>(t % cg);
-    size_t r = t / cg;
-    const int b = static_cast<int>(r % Q2);
-    r /= Q2;
-    const int a = static_cast<int>(r % P2);
-    const int n = static_cast<int>(r / P2);
-    const int h0 = 4 * a - 1, w0 = 4 * b - 1;          // origin of the 5x5 patch
-    float best[2][2][8];
-    uint32_t idx[2][2][8];
-#pragma unroll
-    for (int u = 0; u < 2; ++u)
-#pragma unroll
-      for (int v = 0; v < 2; ++v) {
-        // index of the first in-bounds tap: what an all -inf window keeps
-        const uint32_t first = ((h0 + 2 * u < 0) ? 3u : 0u) + ((w0 + 2 * v < 0) ? 1u : 0u);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          best[u][v][k] = -INFINITY;
-          idx[u][v][k] = first;
-        }
-      }
-    const float* xn = x + static_cast<size_t>(n) * p.H * p.W * p.C + g * 8;
-#pragma unroll
-    for (int rr = 0; rr < 5; ++rr) {
-      const int h = h0 + rr;
-      if (h < 0 || h >= p.H) continue;
-#pragma unroll
-      for (int cc = 0; cc < 5; ++cc) {
-        const int w = w0 + cc;
-        if (w < 0 || w >= p.W) continue;
-        const float4* src =
-            reinterpret_cast<const float4*>(xn + (static_cast<size_t>(h) * p.W + w) * p.C);
-        const float4 fa = __ldg(src), fb = __ldg(src + 1);
-        const float val[8] = {fa.x, fa.y, fa.z, fa.w, fb.x, fb.y, fb.z, fb.w};
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int i = rr - 2 * u;
-          if (i < 0 || i > 2) continue;
-#pragma unroll
-          for (int v = 0; v < 2; ++v) {
-            const int j = cc - 2 * v;
-            if (j < 0 || j > 2) continue;
-            const uint32_t local = i * 3 + j;
-#pragma unroll
-            for (int k = 0; k < 8; ++k)
-              if (better(val[k], best[u][v][k])) {
-                best[u][v][k] = val[k];
-                idx[u][v][k] = local;
-              }
-          }
-        }
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int pp = 2 * a + u;
-      if (pp >= p.P) continue;
-#pragma unroll
-      for (int v = 0; v < 2; ++v) {
-        const int q = 2 * b + v;
-        if (q >= p.Q) continue;
-        const size_t o = ((static_cast<size_t>(n) * p.P + pp) * p.Q + q) * cg + g;
-        f8 out;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) out.v[k] = best[u][v][k];
-        st8(y + o * 8, out);
-        if (nib) {
-          uint32_t w32 = 0;
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            w32 |= (((idx[u][v][2 * k] << 4) | idx[u][v][2 * k + 1]) & 0xffu) << (8 * k);
-          nib[o] = w32;
-        }
-      }
-    }
-  }
-}
-
+// The pooling of the ResNet stem, backward.  Windows overlap by one row and one column: a 2x2
+// input quad (rows 2a, 2a+1; columns 2b, 2b+1) is covered by the windows (a, a+1) x (b, b+1)
+// only, so a thread that owns a quad serves four pixels with four (gradient, nibble-word)
+// loads (1 load per pixel instead of 2.25) and its stores are two 64-byte runs: 0.26 -> 0.13 ms
+// on 184 x 64 x 112 x 112.  (The same sharing in the forward -- 2x2 outputs from one 5x5 patch,
+// with 8 or with 4 channels per thread -- measured slower than one output per thread, 0.26 and
+// 0.24 against 0.19 ms: the forward is read-dominated and L2 already absorbs the overlap, while
+// the quad's registers cost occupancy.)
 __global__ void __launch_bounds__(256) maxpool_bwd_3x3s2p1_quad(const float* __restrict__ dy,
                                                                 const uint32_t* __restrict__ nib,
                                                                 float* __restrict__ dx, PoolP p,
@@ -452,11 +366,6 @@ int mb_maxpool2d_fwd(const float* x, float* y, uint8_t* nibbles, const mb_pool_d
     uint32_t* nw = reinterpret_cast<uint32_t*>(nibbles);
     const int grid = grid_for(total, 256, 8);
     const bool unit_dil = p.dh == 1 && p.dw == 1;
-    if (unit_dil && p.kh == 3 && p.kw == 3 && p.sh == 2 && p.sw == 2 && p.ph == 1 && p.pw == 1) {
-      const size_t quads = static_cast<size_t>(p.N) * ((p.P + 1) / 2) * ((p.Q + 1) / 2) * (p.C / 8);
-      maxpool_fwd_3x3s2p1_quad<<<grid_for(quads, 256, 4), 256, 0, as_stream(stream)>>>(x, y, nw, p, quads);
-      return after_launch("maxpool_fwd_3x3s2p1_quad");
-    }
     if (unit_dil && p.kh == 3 && p.kw == 3)
       maxpool_fwd_nhwc8<3, 3><<<grid, 256, 0, as_stream(stream)>>>(x, y, nw, p, total);
     else if (unit_dil && p.kh == 2 && p.kw == 2)

@@ -31,7 +31,7 @@ class CapturedStep:
         if not all(t.is_cuda for t in example_inputs):
             raise RuntimeError("CapturedStep needs CUDA tensors")
         self.step_fn = step_fn
-        self.static = [t.clone() for t in example_inputs]
+        self.static = [t.detach().clone() for t in example_inputs]
         # warm-up on a side stream: first calls tune, fill caches, create optimiser state and
         # raise shared-memory limits -- none of that may happen during capture
         side = torch.cuda.Stream()
@@ -47,9 +47,10 @@ class CapturedStep:
             self.output = step_fn(*self.static)
 
     def __call__(self, *inputs: torch.Tensor) -> torch.Tensor:
-        for dst, src in zip(self.static, inputs):
-            if src is not dst:
-                dst.copy_(src, non_blocking=True)
+        with torch.no_grad():          # a module may have marked its input as requiring grad
+            for dst, src in zip(self.static, inputs):
+                if src is not dst:
+                    dst.copy_(src, non_blocking=True)
         self.graph.replay()
         return self.output
 

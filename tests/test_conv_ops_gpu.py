@@ -116,8 +116,42 @@ def test_pytorch_convolution_default_variant(cuda):
     ref_dx, ref_dw, ref_db = oracle.conv_backward(dy, x, w, 1, 1, 1)
     assert _rel(di, ref_dx) < 2e-2 and _rel(dw, ref_dw) < 2e-2
     assert torch.allclose(db.cpu(), ref_db, rtol=1e-4, atol=1e-3)
-    with pytest.raises(NotImplementedError):
-        op.forward(xg, wg, None, [1, 1], [1, 1], [1, 1], True, [0, 0], 1)
+
+
+@pytest.mark.parametrize("geom", [
+    # N, C_in, H, W, C_out, R, stride, pad, output_padding
+    (3, 64, 13, 19, 32, 2, 2, 0, 0),      # UNet's 2x2 stride-2 up-convolution
+    (2, 128, 7, 7, 64, 2, 2, 0, 0),
+    (2, 32, 9, 9, 16, 3, 2, 1, 1),        # 3x3 stride 2 with output padding (doubles the extent)
+    (2, 16, 10, 12, 24, 3, 1, 1, 0),      # stride 1
+    (2, 64, 6, 6, 2, 2, 2, 0, 0),         # two output channels (padded to 4 inside)
+])
+def test_transposed_convolution_on_the_convolution_kernels(cuda, geom):
+    """Beyond the reference (conv.py:269 asserts `not transposed`): forward = backward-data
+    kernel, backward-data = forward kernel, backward-filter with the operands exchanged.  Against
+    torch's CPU conv_transpose2d and autograd at the convolution tolerance."""
+    from monet_b200 import functional as F
+    from monet_b200 import lm_ops
+    N, Ci, H, W, Co, R, s, p, op_ = geom
+    g = torch.Generator().manual_seed(13)
+    x = torch.randn(N, Ci, H, W, generator=g)
+    w = torch.randn(Ci, Co, R, R, generator=g) * (Ci * R * R) ** -0.5
+    b = torch.randn(Co, generator=g)
+    xr, wr, br = (t.clone().requires_grad_(True) for t in (x, w, b))
+    ref = torch.nn.functional.conv_transpose2d(xr, wr, br, s, p, op_)
+    dy = torch.randn(ref.shape, generator=g)
+    ref.backward(dy)
+    op = lm_ops.list_ops("conv_multiway_newnode", "aten::_convolution")[0]()
+    xg, wg, bg = (t.to(cuda).requires_grad_(True) for t in (x, w, b))
+    y = op.forward(xg, wg, bg, [s, s], [p, p], [1, 1], True, [op_, op_], 1)
+    assert tuple(y.shape) == tuple(ref.shape)
+    assert _rel(y, ref.detach()) < 2e-2
+    op.algorithm = 20
+    di, dw, db = op.backward(dy.to(cuda), [xg, wg])
+    assert _rel(di, xr.grad) < 2e-2, _rel(di, xr.grad)
+    assert _rel(dw, wr.grad) < 2e-2, _rel(dw, wr.grad)
+    assert torch.allclose(db.cpu(), br.grad, rtol=1e-4, atol=1e-3)
+    assert F.conv_device_status() == 0
 
 
 @pytest.mark.parametrize("nhwc", [False, True])

@@ -198,9 +198,23 @@ def test_stem_configuration_verbatim(cuda):
     o_y, local = oracle.maxpool_forward(r_cpu, 3, 2, 1)
     assert torch.equal(cpu(y), o_y)
     assert np.array_equal(nib.cpu().numpy(), oracle.maxpool_nibbles(local, nhwc=True))
-    # against the all-fp32 torch CPU run of the whole stem: convolution tolerance (TF32 operands)
+    # against the all-fp32 torch CPU run of the whole stem.  The chain contains discrete decisions
+    # (the ReLU gate and the pooling argmax): where TF32 rounding of the convolution flips one,
+    # a gradient is routed to a different pixel, so single elements of dx can differ by their
+    # whole size.  The chain is therefore compared in the L2 norm at the convolution tolerance,
+    # and the number of flipped decisions is bounded; every operator is held to its own
+    # element-wise tolerance on the same inputs below.
+    def rel2(a, t):
+        return float((cpu(a) - t).norm() / t.norm().clamp_min(1e-12))
     for name, got in (("y", y), ("dx", dx), ("dw", dw), ("dgamma", dgamma), ("dbeta", dbeta)):
-        assert rel(got, ref[name]) < 2e-2, (name, rel(got, ref[name]))
+        assert rel2(got, ref[name]) < 2e-2, (name, rel2(got, ref[name]))
+    assert rel(y, ref["y"]) < 2e-2
+    flipped_gate = float(((b_cpu > 0) != (ref["bn"] > 0)).float().mean())
+    flipped_argmax = float((local != ref["local_idx"]).mean())
+    assert flipped_gate < 2e-3 and flipped_argmax < 2e-3, (flipped_gate, flipped_argmax)
+    # the convolution's own backward-data and backward-filter on the gradient the GPU chain produced
+    o_dx, o_dw, _ = oracle.conv_backward(cpu(d_c), ref["x"], ref["w"], 2, 3)
+    assert rel(dx, o_dx) < 2e-2 and rel(dw, o_dw) < 2e-2, (rel(dx, o_dx), rel(dw, o_dw))
     # the fp32 operators against the oracle on the same inputs: rtol 1e-5
     o_b, _, o_inv, _, _ = oracle.bn_forward_train(cpu(c), ref["gamma"], ref["beta"], torch.zeros(64), torch.ones(64))
     assert torch.allclose(b_cpu, o_b, rtol=1e-5, atol=1e-5)

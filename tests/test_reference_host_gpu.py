@@ -139,7 +139,8 @@ def test_reference_profiler_fills_the_cost_tables(cuda, tmp_path, profiler):
             want = F.conv_num_variants(MB_CONV_WGRAD) if node.bwd_op == "param_grad" else 1
             assert len(node.workspace_compute) == want
             assert all(t > 0 for t in node.workspace_compute)          # every variant ran (none is -1)
-            if node.bwd_op == "param_grad":
+            c_in = graph.nodes[node.fwd_node.args[0].index].shape[1]
+            if node.bwd_op == "param_grad" and c_in > 4:      # (few-channel inputs take their own kernels)
                 # the deterministic variant's scratch shows up in the allocator peak the profiler
                 # reads, and is what mb_conv_workspace_bytes declares for it
                 shape = [batch if s == -1 else s for s in graph.nodes[node.fwd_node.args[0].index].shape]
@@ -149,7 +150,8 @@ def test_reference_profiler_fills_the_cost_tables(cuda, tmp_path, profiler):
                 d = F._padded_desc(d)
                 declared = F.conv_workspace_bytes(MB_CONV_WGRAD, 1, d) - F.conv_workspace_bytes(MB_CONV_WGRAD, 0, d)
                 measured = (node.workspace_mem[1] - node.workspace_mem[0]) * 2 ** 20
-                assert abs(measured - declared) <= max(0.02 * declared, 4096), (measured, declared)
+                assert declared > 0
+                assert 0.98 * declared <= measured <= declared + 2 ** 20, (measured, declared)
     assert n_conv == 4            # two convolutions x (param_grad, ip_grad)
     for i in range(si.loss):
         node = si.nodes[i]
