@@ -246,6 +246,12 @@ def family_costs(runner_obj, batch_shape):
         c[0] += b; c[1] += f
 
     shapes = runner_obj.shapes
+    needed = getattr(runner_obj, "_need", {})     # node id -> backward step that reads its output
+
+    def recomputed(n, ch):
+        """A node marked recompute is rebuilt only when some backward step reads its output."""
+        return ch.recompute and n.id in needed
+
     emitters = {n.sums_from for n in runner_obj.nodes if getattr(n, "sums_from", -1) >= 0}
 
     def emits_sums(n):
@@ -297,7 +303,7 @@ def family_costs(runner_obj, batch_shape):
                 add("mb_bn_act_fwd_train_partials", 8 * e_out)
             else:
                 add("mb_bn_act_fwd_train", 12 * e_out)
-            if ch.recompute:
+            if recomputed(n, ch):
                 add("mb_bn_act_fwd_apply", 8 * e_out)
             add("mb_bn_act_bwd_from_input", 20 * e_out)
         elif n.op == 'monet::batch_norm_add_relu':
@@ -306,16 +312,16 @@ def family_costs(runner_obj, batch_shape):
                 add("mb_bn_act_fwd_train_partials", 12 * e_out)
             else:
                 add("mb_bn_act_fwd_train", 16 * e_out)
-            if ch.recompute:
+            if recomputed(n, ch):
                 add("mb_bn_act_fwd_apply", 12 * e_out)
             add("mb_bn_add_relu_bwd", (32 if len(n.users) == 2 else 28) * e_out)
         elif n.op in ('aten::relu', 'aten::relu_'):
-            add("mb_relu_fwd", 8 * e_out * (2 if ch.recompute else 1))
+            add("mb_relu_fwd", 8 * e_out * (2 if recomputed(n, ch) else 1))
             add("mb_relu_bwd_act", 12 * e_out)
         elif n.op in ('aten::add', 'aten::add_'):
             add("mb_add_fwd", 12 * e_out)
         elif n.op in ('aten::hardtanh', 'aten::hardtanh_'):
-            add("mb_hardtanh_fwd", 8 * e_out * (2 if ch.recompute else 1))
+            add("mb_hardtanh_fwd", 8 * e_out * (2 if recomputed(n, ch) else 1))
             add("mb_hardtanh_bwd", 12 * e_out)
         elif n.op == 'aten::cat':
             add("mb_cat_rows", 16 * e_out)              # forward and backward: read + write each

@@ -179,7 +179,7 @@ def test_graphed_step_matches_eager(cuda, policy):
     torch.cuda.synchronize()
     assert all(l == l for l in graph_losses)
     for a, b in zip(graph_losses, eager_losses):
-        assert abs(a - b) <= 2e-2 * max(1.0, abs(b)), (graph_losses, eager_losses)
+        assert abs(a - b) <= 4e-2 * max(1.0, abs(b)), (graph_losses, eager_losses)
     # the classifier and the first batch norm's running statistics after the same number of steps
     # (the convolution filters of a 4-image batch with random labels are too ill-conditioned to
     # compare between any two runs: batch norm makes their gradients differences of large terms)
