@@ -550,8 +550,8 @@ def check_solution(si, sol, budget_gb: Optional[float] = None) -> dict:
     ``budget_gb`` is given, memory rows above it."""
     tb = _Tables(si)
     V, T, ram = tb.V, tb.T, tb.ram
-    R, S, M, IP, P = sol.r, sol.s, sol.m, sol.ip, sol.p
-    rf = sol.rf
+    # (stored schedules keep their 0/1 arrays as uint8: evaluate in floating point)
+    R, S, M, IP, P, rf = (np.asarray(a, dtype=np.float64) for a in (sol.r, sol.s, sol.m, sol.ip, sol.p, sol.rf))
     bad: List[str] = []
     inpl = si.do_inplace
     conv_list = dict(si.conv_list) if si.select_conv_algo else {}

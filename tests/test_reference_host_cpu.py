@@ -145,3 +145,23 @@ def test_inplace_table_names_the_overwritten_input(host, tmp_path):
     for v in adds:
         assert si.inplace_list[v] == si.nodes[v].args[0][0]
         assert si.nodes[si.inplace_list[v]].last_used == v
+
+
+def test_shipped_schedule_is_valid(host, tmp_path):
+    """The committed 10 GB ResNet-50 schedule still matches the graph this PyTorch traces, and
+    satisfies every row of the reference's ILP literally (no budget row above 10 GB)."""
+    from monet_b200 import solver
+    rh, ref = host
+    path = Path(rh.__file__).resolve().parent / "schedules" / "solution_resnet50_184_inplace_conv_multiway_newnode_10.00.pkl"
+    si, sol = ref.schedule.load_solution(str(path))
+    chk = solver.check_solution(si, sol, 10.0)
+    assert chk["violations"] == [] and chk["peak_gb"] <= 10.0
+    graph, fresh = rh.build_solver_info(torchvision.models.resnet50(), 184, "resnet50", MODE, (3, 224, 224),
+                                        workdir=tmp_path, profile=False)
+    assert len(fresh.nodes) == len(si.nodes) and fresh.loss == si.loss
+    assert [n.op for n in fresh.nodes.values()] == [n.op for n in si.nodes.values()]
+    assert dict(fresh.inplace_list) == dict(si.inplace_list) and dict(fresh.conv_list) == dict(si.conv_list)
+    sched = rh.make_schedule(graph, si, sol)            # init_schedule consumes the uint8 arrays
+    assert len(sched._bwd_op) == len(si.nodes) - si.loss
+    store_all = solver.check_solution(si, solver.hand_solution(si, "store_all"))
+    assert chk["cost"] <= 1.05 * store_all["cost"]
