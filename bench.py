@@ -876,11 +876,19 @@ def run_ours(args):
             line["cpu_baseline"] = {"value": ips, "unit": "images/s", "cores": threads, "kind": "port",
                                     "sample": f"2 eager steps of batch {cb} (of {B}), PyTorch CPU"}
         print(json.dumps(line), flush=True)
+    bad = conv_status != 0 or not math.isfinite(last)
+    if bad:
+        print(f"invalid run: conv_device_status={conv_status}, loss={last}", file=sys.stderr, flush=True)
     if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
-    if conv_status != 0 or not math.isfinite(last):
-        raise SystemExit(f"invalid run: conv_device_status={conv_status}, loss={last}")
+        # Leave without tearing NCCL down: destroying a communicator whose collectives live in a
+        # captured graph was seen to block at exit.  Every rank has passed the max-reduction of
+        # the timings above, so nobody waits for a peer any more.
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(1 if bad else 0)
+    if bad:
+        raise SystemExit(1)
 
 
 def main():
