@@ -58,6 +58,8 @@ def parse():
     ap.add_argument("--micro", default=None, choices=sorted(MICRO),
                     help="time ONE operator on one ResNet-50 layer's tensors (for ncu captures)")
     ap.add_argument("--micro-batch", type=int, default=184)
+    ap.add_argument("--cudnn", action="store_true",
+                    help="with --micro on a convolution pass: also time cuDNN (TF32, benchmark mode) on the same tensors")
     return ap.parse_args()
 
 
@@ -81,6 +83,16 @@ MICRO = {
     "bn_relu_bwd": ("bn_relu_bwd", 256, 56, 0, 0, 0, 0), "relu_bwd2": ("relu_bwd2", 256, 56, 0, 0, 0, 0),
     "bn_add_relu_bwd": ("bn_add_relu_bwd", 256, 56, 0, 0, 0, 0),
     "maxpool_fwd": ("maxpool_fwd", 64, 112, 0, 0, 0, 0), "maxpool_bwd": ("maxpool_bwd", 64, 112, 0, 0, 0, 0),
+    "relu_bwd_mask": ("relu_bwd_mask", 256, 56, 0, 0, 0, 0),
+    # not ResNet-50 layers: a MobileNetV2 depthwise layer (use --micro-batch 272), UNet's skip
+    # concatenation (--micro-batch 11), VGG-16's first classifier layer (--micro-batch 176), and the
+    # fused softmax + cross-entropy on 65 536 rows of 1000 classes (ResNet's own 184 rows are 0.7 MB)
+    "dw3x3_fprop": ("dw_fprop", 144, 56, 144, 3, 1, 1), "dw3x3_dgrad": ("dw_dgrad", 144, 56, 144, 3, 1, 1),
+    "dw3x3_wgrad": ("dw_wgrad", 144, 56, 144, 3, 1, 1),
+    "cat_bwd": ("cat_bwd", 128, 208, 0, 0, 0, 0), "cat_fwd": ("cat_fwd", 128, 208, 0, 0, 0, 0),
+    "fc_fwd": ("fc_fwd", 25088, 1, 4096, 1, 1, 0), "fc_dgrad": ("fc_dgrad", 25088, 1, 4096, 1, 1, 0),
+    "fc_wgrad": ("fc_wgrad", 25088, 1, 4096, 1, 1, 0),
+    "softmax_ce": ("softmax_ce", 1000, 1, 0, 0, 0, 0),
 }
 
 
@@ -93,9 +105,41 @@ def run_micro(args):
     N = args.micro_batch
     torch.manual_seed(0)
     cl = torch.channels_last
-    x = torch.randn(N, Cc, H, H, device=dev)
-    x = x.contiguous(memory_format=cl) if Cc % 4 == 0 else x
-    if kind in ("fprop", "dgrad", "wgrad", "fprop_sums"):
+    if kind == "softmax_ce":
+        rows = 65536
+        logits = torch.randn(rows, Cc, device=dev)
+        labels = torch.randint(0, Cc, (rows,), device=dev)
+        flops, nbytes = 0.0, 8.0 * rows * Cc + 12.0 * rows
+        fn = lambda: F.cross_entropy_fwd_bwd(logits, labels, 1.0 / rows)      # noqa: E731
+    elif kind.startswith("fc_"):
+        xf = torch.randn(N, Cc, device=dev)
+        wf = torch.randn(K, Cc, device=dev) * Cc ** -0.5
+        bf = torch.randn(K, device=dev)
+        dyf = torch.randn(N, K, device=dev)
+        flops, nbytes = 2.0 * N * Cc * K, 4.0 * (N * Cc + K * Cc + N * K)
+        fn = {"fc_fwd": lambda: F.linear_fwd(xf, wf, bf), "fc_dgrad": lambda: F.linear_dgrad(dyf, wf),
+              "fc_wgrad": lambda: F.linear_wgrad(xf, dyf, True)}[kind]
+    elif kind.startswith("cat_"):
+        W = H * 304 // 208
+        parts = [torch.randn(N, Cc // 2, H, W, device=dev).contiguous(memory_format=cl) for _ in range(2)]
+        whole = F.cat(parts, 1)
+        flops, nbytes = 0.0, 8.0 * whole.numel()
+        fn = (lambda: F.cat(parts, 1)) if kind == "cat_fwd" else (lambda: F.cat_bwd(whole, [Cc // 2, Cc // 2], 1))
+    elif kind.startswith("dw_"):
+        xd = torch.randn(N, Cc, H, H, device=dev).contiguous(memory_format=cl)
+        wd = torch.randn(Cc, 1, R, R, device=dev) * 0.2
+        yd = F.depthwise_fprop(xd, wd, None, s, p, 1, Cc)
+        dyd = torch.randn_like(yd)
+        flops, nbytes = 0.0, 4.0 * (xd.numel() + yd.numel())
+        fn = {"dw_fprop": lambda: F.depthwise_fprop(xd, wd, None, s, p, 1, Cc),
+              "dw_dgrad": lambda: F.depthwise_bwd(dyd, xd, wd, s, p, 1, Cc, need=(True, False, False)),
+              "dw_wgrad": lambda: F.depthwise_bwd(dyd, xd, wd, s, p, 1, Cc, need=(False, True, False))}[kind]
+    else:
+        x = torch.randn(N, Cc, H, H, device=dev)
+        x = x.contiguous(memory_format=cl) if Cc % 4 == 0 else x
+    if kind in ("softmax_ce",) or kind.startswith(("fc_", "cat_", "dw_")):
+        pass
+    elif kind in ("fprop", "dgrad", "wgrad", "fprop_sums"):
         w = (torch.randn(K, Cc, R, R, device=dev) * 0.05).contiguous(memory_format=cl)
         y = F.conv2d_fprop(x, w, None, s, p, 1)
         dy = torch.randn_like(y)
@@ -136,6 +180,9 @@ def run_micro(args):
             nbytes, fn = 8.125 * E, lambda: F.relu_mask(x)
         elif kind == "relu_bwd":
             nbytes, fn = 12 * E, lambda: F.relu_bwd_act(dy, x, 0.0, inplace=False)
+        elif kind == "relu_bwd_mask":
+            _, rmask = F.relu_mask(x)
+            nbytes, fn = 8.125 * E, lambda: F.relu_bwd_mask(dy, rmask, inplace=False)
         elif kind == "add":
             nbytes, fn = 12 * E, lambda: F.add(x, dy, 1.0)
         elif kind == "maxpool_fwd":
@@ -145,18 +192,32 @@ def run_micro(args):
             yp, nib, d = F.maxpool2d(x, 3, 2, 1, 1, False)
             dyp = torch.randn_like(yp)
             nbytes, fn = 4 * E + 4.5 * yp.numel(), lambda: F.maxpool2d_bwd(dyp, nib, d)
-    for _ in range(max(args.warmup, 1)):
-        fn()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        fn()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / args.steps
-    print(json.dumps({"micro": args.micro, "batch": N, "ms": ms, "algorithmic_GBps": nbytes / ms / 1e6,
-                      "TFLOPps": flops / ms / 1e9, "conv_status": F.conv_device_status()}), flush=True)
+    def clock(f):
+        for _ in range(max(args.warmup, 1)):
+            f()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            f()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.steps
+
+    ms = clock(fn)
+    line = {"micro": args.micro, "batch": N, "ms": ms, "algorithmic_GBps": nbytes / ms / 1e6,
+            "TFLOPps": flops / ms / 1e9, "conv_status": F.conv_device_status()}
+    if args.cudnn and kind in ("fprop", "dgrad", "wgrad"):
+        # the library op this pass replaces, on the same tensors: cuDNN, TF32, benchmark mode
+        torch.backends.cudnn.allow_tf32 = True
+        torch.backends.cudnn.benchmark = True
+        xc = x.contiguous(memory_format=cl)
+        mask = {"dgrad": [True, False, False], "wgrad": [False, True, False]}.get(kind)
+        lib_fn = ((lambda: torch.nn.functional.conv2d(xc, w, None, s, p)) if kind == "fprop" else
+                  (lambda: torch.ops.aten.convolution_backward(dy, xc, w, None, [s, s], [p, p], [1, 1], False,
+                                                                [0, 0], 1, mask)))
+        line["cudnn_ms"] = clock(lib_fn)
+    print(json.dumps(line), flush=True)
 
 
 # ------------------------------------------------------------------ reference arm (CPU)

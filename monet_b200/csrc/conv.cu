@@ -235,46 +235,80 @@ int run_halo(const char* who, const float* in, int Cin, int Win, int Hin, const 
     if (taps[t].dw > max_dw) max_dw = taps[t].dw;
   }
   const int halo_h = max_dh - min_dh, halo_w = max_dw - min_dw;
+  // Geometry of one candidate: the map cut into `tw` column tiles.  Returns the fraction of MMA
+  // rows that are real output pixels, or 0 when the candidate does not fit (TMA box limits, two
+  // accumulators, shared memory).
+  const size_t budget = 222 * 1024 - 2048;
+  auto plan = [&](int tw, HaloParams& p) -> double {
+    std::memset(&p, 0, sizeof(p));
+    const int rows_cap = 2 * kTileM;
+    p.tiles_w = tw;
+    p.bw = (Qo + tw - 1) / tw;
+    p.Wh = p.bw + halo_w;
+    p.row_stores = tw > 1 ? 1 : 0;
+    p.Po = Po;
+    if (p.Wh > 256) return 0.0;
+    if (tw == 1 && (Po + halo_h) * p.Wh <= rows_cap) {        // whole (padded) images, several per super-tile
+      p.Hb = Po + halo_h;
+      p.bn = rows_cap / (p.Hb * p.Wh);
+      if (p.bn > N) p.bn = N;
+      p.bh = Po;
+      p.tiles_h = 1;
+      p.Hout = p.bn > 1 ? p.Hb : p.bh;
+    } else {
+      p.bn = 1;
+      const int bh_max = rows_cap / p.Wh;
+      if (bh_max < 1) return 0.0;
+      p.tiles_h = (Po + bh_max - 1) / bh_max;
+      p.bh = (Po + p.tiles_h - 1) / p.tiles_h;
+      p.Hb = p.bh + halo_h;
+      p.Hout = p.bh;
+    }
+    if (p.Hb > 256) return 0.0;
+    p.tiles_n = (N + p.bn - 1) / p.bn;
+    p.box_rows = p.Wh * p.Hb * p.bn;
+    p.out_rows = p.Wh * p.Hout * p.bn;
+    const int span = ((p.bn - 1) * p.Hb + p.bh) * p.Wh;
+    p.MT = ((span > p.out_rows ? span : p.out_rows) + kTileM - 1) / kTileM;
+    if (p.MT > 2) return 0.0;
+    const int max_off = halo_h * p.Wh + halo_w;
+    int need_rows = p.MT * kTileM + max_off;
+    if (need_rows < p.box_rows) need_rows = p.box_rows;
+    p.a_rows_alloc = (need_rows + 7) / 8 * 8;
+    p.BN = Kout >= 256 ? 256 : round_up(Kout, 32);
+    const size_t a_slot = static_cast<size_t>(p.a_rows_alloc) * 128;
+    const size_t staging = (static_cast<size_t>(p.out_rows) * 128 + 1023) / 1024 * 1024;
+    if (2 * a_slot + staging + 2 * static_cast<size_t>(p.BN) * 128 > budget) {
+      if (p.BN != 256 || 2 * a_slot + staging + 2 * static_cast<size_t>(128) * 128 > budget) return 0.0;
+      p.BN = 128;                                   // narrower filter tiles leave room for the halo box
+    }
+    return static_cast<double>(Qo) * Po * N /
+           (static_cast<double>(p.tiles_w) * p.tiles_h * p.tiles_n * p.MT * kTileM);
+  };
+  // One column tile (the whole row in the box) unless that does not fit or wastes more than 30 %
+  // of the MMA rows and a tiling recovers at least 15 points: maps wider than a TMA box (256
+  // pixels), and wide maps whose single output row already spills into a second accumulator.
   HaloParams p;
-  std::memset(&p, 0, sizeof(p));
-  p.Wh = Qo + halo_w;
-  if (p.Wh > 256) return MB_ERR_UNSUPPORTED;
-  const int rows_cap = 2 * kTileM;
-  if ((Po + halo_h) * p.Wh <= rows_cap) {        // whole (padded) images, several per super-tile
-    p.Hb = Po + halo_h;
-    p.bn = rows_cap / (p.Hb * p.Wh);
-    if (p.bn > N) p.bn = N;
-    p.bh = Po;
-    p.tiles_h = 1;
-    p.Hout = p.bn > 1 ? p.Hb : p.bh;
-  } else {
-    p.bn = 1;
-    const int bh_max = rows_cap / p.Wh;
-    if (bh_max < 1) return MB_ERR_UNSUPPORTED;
-    p.tiles_h = (Po + bh_max - 1) / bh_max;
-    p.bh = (Po + p.tiles_h - 1) / p.tiles_h;
-    p.Hb = p.bh + halo_h;
-    p.Hout = p.bh;
+  double eff = plan(1, p);
+  if (eff < 0.7) {
+    HaloParams q;
+    double best = eff;
+    int best_tw = 1;
+    for (int tw = 2; tw <= (Qo + 7) / 8; ++tw) {
+      const double e = plan(tw, q);
+      if (e > best + 1e-9) { best = e; best_tw = tw; }
+    }
+    if (best_tw > 1 && (eff == 0.0 || best >= eff + 0.15)) eff = plan(best_tw, p);
+    else if (eff > 0.0) eff = plan(1, p);
   }
-  if (p.Hb > 256) return MB_ERR_UNSUPPORTED;
-  p.tiles_n = (N + p.bn - 1) / p.bn;
-  p.box_rows = p.Wh * p.Hb * p.bn;
-  p.out_rows = p.Wh * p.Hout * p.bn;
-  const int span = ((p.bn - 1) * p.Hb + p.bh) * p.Wh;
-  p.MT = ((span > p.out_rows ? span : p.out_rows) + kTileM - 1) / kTileM;
-  if (p.MT > 2) return MB_ERR_UNSUPPORTED;
-  const int max_off = halo_h * p.Wh + halo_w;
-  int need_rows = p.MT * kTileM + max_off;
-  if (need_rows < p.box_rows) need_rows = p.box_rows;
-  p.a_rows_alloc = (need_rows + 7) / 8 * 8;
+  if (eff == 0.0) return MB_ERR_UNSUPPORTED;
   p.bias = bias;
   p.Kout = Kout;
-  p.BN = Kout >= 256 ? 256 : round_up(Kout, 32);
   p.tiles_c = (Kout + p.BN - 1) / p.BN;
   if (p.BN == 256) {
     // 128-column tiles when they fill the SMs' rounds better: an M = 128 MMA takes about 140
     // cycles with 256 columns and 86 with 128 in this kernel, and a round costs its MMAs
-    const long long pix_items = static_cast<long long>(p.tiles_h) * ((N + p.bn - 1) / p.bn);
+    const long long pix_items = static_cast<long long>(p.tiles_h) * p.tiles_w * p.tiles_n;
     const long long rounds256 = (pix_items * p.tiles_c + num_sms() - 1) / num_sms();
     const int tiles128 = (Kout + 127) / 128;
     const long long rounds128 = (pix_items * tiles128 + num_sms() - 1) / num_sms();
@@ -295,12 +329,11 @@ int run_halo(const char* who, const float* in, int Cin, int Win, int Hin, const 
   p.a_stages = 2;
   const size_t a_slot = static_cast<size_t>(p.a_rows_alloc) * 128, b_slot = static_cast<size_t>(p.BN) * 128;
   const size_t staging = (static_cast<size_t>(p.out_rows) * 128 + 1023) / 1024 * 1024;
-  const size_t budget = 222 * 1024 - 2048;
   if (2 * a_slot + staging + 2 * b_slot > budget) return MB_ERR_UNSUPPORTED;
   int bs = static_cast<int>((budget - 2 * a_slot - staging) / b_slot);
   if (bs > 16) bs = 16;
   p.b_stages = bs;
-  const long long items = static_cast<long long>(p.tiles_h) * p.tiles_n * p.tiles_c;
+  const long long items = static_cast<long long>(p.tiles_h) * p.tiles_w * p.tiles_n * p.tiles_c;
   if (items > 0x7fffffffLL) return MB_ERR_UNSUPPORTED;
   p.num_items = static_cast<int>(items);
   const size_t smem = 512 + 1024 + 2 * a_slot + bs * b_slot + staging;
@@ -313,7 +346,8 @@ int run_halo(const char* who, const float* in, int Cin, int Win, int Hin, const 
   rc = filter_mn ? encode_filter_mn(who, &mb_, filt, Cin, T, Kout, p.BN)
                  : encode_filter(who, &mb_, filt, Cin, T, Kout, p.BN);
   if (rc) return rc;
-  rc = encode_act(who, &mo, out, Kout, Qo, Po, N, K4, K4 * Qo, K4 * Qo * Po, p.Wh, p.Hout, p.bn);
+  rc = p.row_stores ? encode_act(who, &mo, out, Kout, Qo, Po, N, K4, K4 * Qo, K4 * Qo * Po, p.bw, 1, 1)
+                    : encode_act(who, &mo, out, Kout, Qo, Po, N, K4, K4 * Qo, K4 * Qo * Po, p.Wh, p.Hout, p.bn);
   if (rc) return rc;
   static std::atomic<unsigned long long> smem_done{0};
   if (int rc = raise_smem_limit(who, conv_gemm_halo, smem_done)) return rc;

@@ -35,6 +35,9 @@ struct HaloParams {
   int Hout;                  // height of the store box (bh, or Hb when bn > 1)
   int bh;                    // output rows per super-tile
   int tiles_h, tiles_n;      // super-tiles along h and n
+  int tiles_w, bw;           // super-tiles along w and their output width (tiles_w == 1: bw == Q)
+  int row_stores;            // 1: the store box is one output row of bw pixels (w-tiled maps)
+  int Po;                    // output height (row stores skip rows past it)
   int num_items;             // super-tiles * tiles_c
   int org_w, org_h;          // input coordinates of the box origin relative to the output pixel
   int a_stages, b_stages;
@@ -96,12 +99,15 @@ conv_gemm_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     acc_cycles += clock64() - t0;
     return r;
   };
-  auto decode = [&](int item, int& c0, int& p0, int& n0) {
+  auto decode = [&](int item, int& c0, int& w0, int& p0, int& n0) {
     const int ct = item % p.tiles_c;
     int r = item / p.tiles_c;
+    const int wt = r % p.tiles_w;
+    r /= p.tiles_w;
     const int ht = r % p.tiles_h;
     const int nt = r / p.tiles_h;
     c0 = ct * p.BN;
+    w0 = wt * p.bw;
     p0 = ht * p.bh;
     n0 = nt * p.bn;
   };
@@ -117,14 +123,14 @@ conv_gemm_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       bool ok = true;
       long long w_ae = 0, w_be = 0;
       for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
-        int c0, p0, n0;
-        decode(item, c0, p0, n0);
+        int c0, w0, p0, n0;
+        decode(item, c0, w0, p0, n0);
         for (int kc = 0; ok && kc < p.kchunks; ++kc) {
           if (!timed_wait(&a_empty[ra.stage], ra.phase ^ 1u, w_ae)) { ok = false; break; }
           mbar_arrive_expect_tx(&a_full[ra.stage], static_cast<uint32_t>(p.box_rows) * 128u);
           armed_a[ra.stage] = 1u + ra.phase;
           tma_load_4d(&mapA, base_ptr + static_cast<size_t>(ra.stage) * a_slot_bytes, &a_full[ra.stage],
-                      kc * kChunkK, p.org_w, p0 + p.org_h, n0);
+                      kc * kChunkK, w0 + p.org_w, p0 + p.org_h, n0);
           ra.advance();
           for (int t = 0; t < p.num_taps; ++t) {
             if (!timed_wait(&b_empty[rb.stage], rb.phase ^ 1u, w_be)) { ok = false; break; }
@@ -273,8 +279,8 @@ conv_gemm_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++it) {
       const int acc = p.acc_bufs == 2 ? (it & 1) : 0;
       const uint32_t acc_phase = p.acc_bufs == 2 ? ((it >> 1) & 1u) : (it & 1u);
-      int c0, p0, n0;
-      decode(item, c0, p0, n0);
+      int c0, w0, p0, n0;
+      decode(item, c0, w0, p0, n0);
       const bool got = timed_wait(&acc_full[acc], acc_phase, w_full);
       const long long t_e0 = prof ? clock64() : 0;
       const bool warp_ok = __all_sync(0xffffffffu, got);
@@ -309,7 +315,15 @@ conv_gemm_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         fence_async_smem();
         named_barrier(1, 128);
         if (threadIdx.x == 0) {
-          tma_store_4d(&mapOut, stage_out, c0 + col, 0, p0, n0);
+          if (!p.row_stores) {
+            tma_store_4d(&mapOut, stage_out, c0 + col, 0, p0, n0);
+          } else {
+            // w-tiled map: the halo columns of this tile are real pixels of the next one, so
+            // only the bw pixels the tile owns are stored, one output row at a time (the
+            // staging rows keep the halo pitch Wh; the tensor map clips the ragged last tile)
+            for (int h = 0; h < p.bh && p0 + h < p.Po; ++h)
+              tma_store_4d(&mapOut, stage_out + static_cast<size_t>(h) * p.Wh * 128, c0 + col, w0, p0 + h, n0);
+          }
           tma_store_commit();
         }
       }

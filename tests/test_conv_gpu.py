@@ -29,6 +29,9 @@ CASES = [
     (2, 4, 18, 18, 24, 3, 2, 1, 1),      # four input channels
     (2, 16, 9, 9, 2, 1, 1, 0, 1),        # K = 2 padded to 4
     (1, 260, 5, 5, 36, 1, 1, 0, 1),      # C spans several 32-channel chunks with a tail
+    (1, 32, 7, 300, 64, 3, 1, 1, 1),     # map wider than a TMA box: column-tiled halo kernel
+    (2, 64, 5, 610, 32, 3, 1, 1, 1),     # UNet's 608-wide maps, ragged last column tile
+    (1, 32, 9, 257, 40, 5, 1, 2, 1),     # 5x5 on a wide map, odd width
 ]
 
 
