@@ -362,6 +362,16 @@ int mb_conv_smallc_geometry(const mb_conv_desc* d, int* Hp, int* Wp);
 int mb_conv_smallc_pack_input(const float* x_nchw, float* xp, const mb_conv_desc* d, void* stream);
 int mb_conv2d_fprop_smallc(const float* xp, const float* wp, const float* bias, float* y,
                            const mb_conv_desc* d, void* stream);
+/* The same first layer when its stride is 2 (3 <= R <= 8): both row phases of the padded input
+ * in one buffer xp2[N][Hp2][Wp][2][4] (N*Hp2*Wp*32 bytes, the caller's; extents from
+ * mb_conv_smallc2_geometry) and the filter as wp2[K][ceil(R/2)][64] with
+ * wp2[k][dh][(s/4)*32 + (s%4)*8 + (r%2)*4 + c] = w[k][c][r = 2*dh + r%2][s], zero elsewhere.
+ * The forward then runs on the many-tap kernel with ceil(R/2) row taps, which fetches every
+ * input window once per tile instead of once per filter row.                                  */
+int mb_conv_smallc2_geometry(const mb_conv_desc* d, int* Hp2, int* Wp);
+int mb_conv_smallc2_pack_input(const float* x_nchw, float* xp2, const mb_conv_desc* d, void* stream);
+int mb_conv2d_fprop_smallc2(const float* xp2, const float* wp2, const float* bias, float* y,
+                            const mb_conv_desc* d, void* stream);
 size_t mb_conv_smallc_wgrad_workspace_bytes(const mb_conv_desc* d, int variant);
 int mb_conv2d_wgrad_smallc(const float* xp, const float* dy, float* dwp, float* dbias,
                            const mb_conv_desc* d, int variant, void* workspace,

@@ -97,6 +97,9 @@ PROTOTYPES = {
     "mb_conv_smallc_geometry": (C.c_int, [C.POINTER(ConvDesc), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "mb_conv_smallc_pack_input": (C.c_int, [c_f, c_f, C.POINTER(ConvDesc), c_f]),
     "mb_conv2d_fprop_smallc": (C.c_int, [c_f, c_f, c_f, c_f, C.POINTER(ConvDesc), c_f]),
+    "mb_conv_smallc2_geometry": (C.c_int, [C.POINTER(ConvDesc), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "mb_conv_smallc2_pack_input": (C.c_int, [c_f, c_f, C.POINTER(ConvDesc), c_f]),
+    "mb_conv2d_fprop_smallc2": (C.c_int, [c_f, c_f, c_f, c_f, C.POINTER(ConvDesc), c_f]),
     "mb_conv_smallc_wgrad_workspace_bytes": (c_sz, [C.POINTER(ConvDesc), C.c_int]),
     "mb_conv2d_wgrad_smallc": (C.c_int, [c_f, c_f, c_f, c_f, C.POINTER(ConvDesc), C.c_int, c_f, c_sz, c_f]),
     "mb_cat_rows": (C.c_int, [c_f, C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.c_int, c_sz, C.c_int, c_f]),

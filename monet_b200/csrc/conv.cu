@@ -225,7 +225,10 @@ struct HaloTap { int dh, dw, btap; };
 // geometry does not fit, so that the caller can fall back to the per-tap kernel.
 int run_halo(const char* who, const float* in, int Cin, int Win, int Hin, const float* filt, int T,
              float* out, int Kout, int Qo, int Po, int N, const HaloTap* taps, int ntaps,
-             const float* bias, cudaStream_t st, bool filter_mn = false) {
+             const float* bias, cudaStream_t st, bool filter_mn = false,
+             const long long* in_strides = nullptr) {
+  // in_strides: byte strides {pixel, row, image} of `in` when it is not a dense NHWC tensor (the
+  // overlapping-window view of a few-channel input); Cin is then the length of a window
   if (ntaps < 2 || ntaps > kMaxTaps) return MB_ERR_UNSUPPORTED;
   int min_dh = taps[0].dh, max_dh = taps[0].dh, min_dw = taps[0].dw, max_dw = taps[0].dw;
   for (int t = 1; t < ntaps; ++t) {
@@ -245,7 +248,7 @@ int run_halo(const char* who, const float* in, int Cin, int Win, int Hin, const 
     p.tiles_w = tw;
     p.bw = (Qo + tw - 1) / tw;
     p.Wh = p.bw + halo_w;
-    p.row_stores = tw > 1 ? 1 : 0;
+    p.row_stores = (tw > 1 && halo_w > 0) ? 1 : 0;     // without a column halo the tile is the store box
     p.Po = Po;
     if (p.Wh > 256) return 0.0;
     if (tw == 1 && (Po + halo_h) * p.Wh <= rows_cap) {        // whole (padded) images, several per super-tile
@@ -290,7 +293,20 @@ int run_halo(const char* who, const float* in, int Cin, int Win, int Hin, const 
   // pixels), and wide maps whose single output row already spills into a second accumulator.
   HaloParams p;
   double eff = plan(1, p);
-  if (eff < 0.7) {
+  if (halo_w == 0) {
+    // taps that differ in their row only: column tiles cost nothing (no halo columns), and a
+    // narrow tile can be tall, which is what saves input traffic (bh + halo_h rows are fetched
+    // for bh rows of output).  Take the tiling with the most useful work per fetched row.
+    HaloParams q;
+    double best = eff > 0.0 ? eff * p.bh / (p.bh + halo_h) : 0.0;
+    int best_tw = 1;
+    for (int tw = 2; tw <= (Qo + 7) / 8; ++tw) {
+      const double e = plan(tw, q);
+      const double score = e > 0.0 ? e * q.bh / (q.bh + halo_h) : 0.0;
+      if (score > best + 1e-9) { best = score; best_tw = tw; }
+    }
+    eff = plan(best_tw, p);
+  } else if (eff < 0.7) {
     HaloParams q;
     double best = eff;
     int best_tw = 1;
@@ -340,7 +356,9 @@ int run_halo(const char* who, const float* in, int Cin, int Win, int Hin, const 
 
   CUtensorMap ma, mb_, mo;
   const long long C4 = static_cast<long long>(Cin) * 4, K4 = static_cast<long long>(Kout) * 4;
-  int rc = encode_act(who, &ma, in, Cin, Win, Hin, N, C4, C4 * Win, C4 * Win * Hin, p.Wh, p.Hb, p.bn);
+  int rc = in_strides ? encode_act(who, &ma, in, Cin, Win, Hin, N, in_strides[0], in_strides[1], in_strides[2],
+                                   p.Wh, p.Hb, p.bn)
+                      : encode_act(who, &ma, in, Cin, Win, Hin, N, C4, C4 * Win, C4 * Win * Hin, p.Wh, p.Hb, p.bn);
   if (rc) return rc;
   p.b_mn = filter_mn ? 1 : 0;
   rc = filter_mn ? encode_filter_mn(who, &mb_, filt, Cin, T, Kout, p.BN)
@@ -609,6 +627,37 @@ __global__ void __launch_bounds__(256) smallc_pack_input(const float* __restrict
       if (C > 3) v.w = __ldg(src + 3 * plane);
     }
     reinterpret_cast<float4*>(xp)[t] = v;
+  }
+}
+
+// one thread per (image, phase-row, padded column): both row phases of up to 4 channels
+__global__ void __launch_bounds__(256) smallc2_pack_input(const float* __restrict__ x,
+                                                          float* __restrict__ xp2, int C, int H, int W,
+                                                          int ph, int pw, int Hp2, int Wp,
+                                                          size_t total) {
+  for (size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
+       t += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const int wq = static_cast<int>(t % Wp);
+    size_t r = t / Wp;
+    const int hh = static_cast<int>(r % Hp2);
+    const size_t n = r / Hp2;
+    const int w = wq - pw;
+    const size_t plane = static_cast<size_t>(H) * W;
+    float4 v[2];
+#pragma unroll
+    for (int phase = 0; phase < 2; ++phase) {
+      const int h = 2 * hh + phase - ph;
+      v[phase] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (h >= 0 && h < H && w >= 0 && w < W) {
+        const float* src = x + (n * C * H + h) * static_cast<size_t>(W) + w;
+        v[phase].x = __ldg(src);
+        if (C > 1) v[phase].y = __ldg(src + plane);
+        if (C > 2) v[phase].z = __ldg(src + 2 * plane);
+        if (C > 3) v[phase].w = __ldg(src + 3 * plane);
+      }
+    }
+    reinterpret_cast<float4*>(xp2)[2 * t] = v[0];
+    reinterpret_cast<float4*>(xp2)[2 * t + 1] = v[1];
   }
 }
 
@@ -978,6 +1027,57 @@ int mb_conv2d_fprop_smallc(const float* xp, const float* wp, const float* bias, 
   if (rc) return rc;
   L.grid = p.num_tiles < num_sms() ? p.num_tiles : num_sms();
   return launch_gemm("conv_fprop_smallc_tcgen05", L, as_stream(stream));
+}
+
+// ---- few-channel input, stride 2: both row phases in one buffer, forward on the halo kernel.
+// xp2[N][Hp2][Wp][2][4]: padded pixel (2*hh + phase, w) of image n, channel c, at float
+// ((n*Hp2 + hh)*Wp + w)*8 + phase*4 + c.  The 64 floats that start at pixel (hh, 2q) are the
+// window of output column q for filter rows 2*dh and 2*dh + 1 (dh = hh - p): 8 input columns x
+// 2 phases x 4 channels, i.e. two 32-float operand chunks.  The GEMM therefore has
+// ceil(R/2) "taps" that differ only in their row and 2 chunks each, which is the halo
+// kernel's interface: the window rows a tile needs are fetched once (bh + ceil(R/2) - 1 rows
+// for bh output rows) instead of once per filter row, and the filter tiles are 8 per tile
+// instead of one per filter row and tile.
+int mb_conv_smallc2_geometry(const mb_conv_desc* d, int* Hp2, int* Wp) {
+  if (!smallc_ok(d) || d->stride_h != 2 || d->stride_w != 2 || d->R > 8 || d->R < 3)
+    return MB_ERR_UNSUPPORTED;
+  const int taps = (d->R + 1) / 2;
+  int hp = (d->H + 2 * d->pad_h + 1) / 2;
+  if (hp < d->P + taps - 1) hp = d->P + taps - 1;
+  int wp = 2 * (d->Q - 1) + 8;
+  if (wp < d->W + 2 * d->pad_w) wp = d->W + 2 * d->pad_w;
+  if (Hp2) *Hp2 = hp;
+  if (Wp) *Wp = (wp + 1) / 2 * 2;
+  return MB_OK;
+}
+
+int mb_conv_smallc2_pack_input(const float* x_nchw, float* xp2, const mb_conv_desc* d, void* stream) {
+  const char* who = "mb_conv_smallc2_pack_input";
+  int Hp2, Wp;
+  if (mb_conv_smallc2_geometry(d, &Hp2, &Wp)) return fail(MB_ERR_UNSUPPORTED, "%s: not a stride-2 few-channel geometry", who);
+  if (!x_nchw || !xp2 || !aligned(xp2, 32)) return fail(MB_ERR_INVALID_ARGUMENT, "%s: bad pointer", who);
+  const size_t total = static_cast<size_t>(d->N) * Hp2 * Wp;
+  smallc2_pack_input<<<grid_for(total, 256, 8), 256, 0, as_stream(stream)>>>(
+      x_nchw, xp2, d->C, d->H, d->W, d->pad_h, d->pad_w, Hp2, Wp, total);
+  return after_launch("conv_smallc2_pack_input");
+}
+
+int mb_conv2d_fprop_smallc2(const float* xp2, const float* wp2, const float* bias, float* y,
+                            const mb_conv_desc* d, void* stream) {
+  const char* who = "mb_conv2d_fprop_smallc2";
+  int Hp2, Wp;
+  if (mb_conv_smallc2_geometry(d, &Hp2, &Wp)) return fail(MB_ERR_UNSUPPORTED, "%s: not a stride-2 few-channel geometry", who);
+  if (!xp2 || !wp2 || !y) return fail(MB_ERR_INVALID_ARGUMENT, "%s: null pointer", who);
+  if (!aligned(xp2, 16) || !aligned(wp2, 16) || !aligned(y, 16) || !aligned(bias, 16))
+    return fail(MB_ERR_INVALID_ARGUMENT, "%s: pointers must be 16-byte aligned", who);
+  const int T = (d->R + 1) / 2;
+  HaloTap taps[4];
+  for (int t = 0; t < T; ++t) taps[t] = HaloTap{t, 0, t};
+  const long long strides[3] = {64LL, 32LL * Wp, 32LL * Wp * Hp2};
+  int rc = run_halo(who, xp2, 64, d->Q, Hp2, wp2, T, y, d->K, d->Q, d->P, d->N, taps, T, bias, as_stream(stream),
+                    false, strides);
+  if (rc == MB_ERR_UNSUPPORTED) return fail(MB_ERR_UNSUPPORTED, "%s: geometry does not fit the halo kernel", who);
+  return rc;
 }
 
 size_t mb_conv_smallc_wgrad_workspace_bytes(const mb_conv_desc* d, int variant) {

@@ -316,7 +316,7 @@ conv_gemm_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         named_barrier(1, 128);
         if (threadIdx.x == 0) {
           if (!p.row_stores) {
-            tma_store_4d(&mapOut, stage_out, c0 + col, 0, p0, n0);
+            tma_store_4d(&mapOut, stage_out, c0 + col, w0, p0, n0);
           } else {
             // w-tiled map: the halo columns of this tile are real pixels of the next one, so
             // only the bw pixels the tile owns are stored, one output row at a time (the

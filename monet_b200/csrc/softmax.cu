@@ -55,9 +55,15 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) softmax_rows(
       mx = warp_max(mx);
       float sum = 0.f;
       if (IN_REGS) {
+        // softmax and the fused loss keep exp(x - max) in the register that held x: one expf
+        // per element instead of two (log-softmax needs x itself again)
 #pragma unroll
         for (int k = 0; k < kRegCols; ++k)
-          if (k * 32 + lane < classes) sum += expf(va[k] - mx);
+          if (k * 32 + lane < classes) {
+            const float e = expf(va[k] - mx);
+            if (KIND != 1) va[k] = e;
+            sum += e;
+          }
       } else {
         for (int k = 0; k < ncols; ++k)
           if (k * 32 + lane < classes) sum += expf(A(k, k * 32 + lane) - mx);
@@ -75,10 +81,11 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) softmax_rows(
       }
       auto emit = [&](int k, int i) {
         const float x = A(k, i);
+        const float e = (IN_REGS && KIND != 1) ? x : expf(x - mx);     // x already holds the exponential
         float o;
-        if (KIND == 0) o = expf(x - mx) * inv;
+        if (KIND == 0) o = e * inv;
         else if (KIND == 1) o = x - lse;
-        else o = (expf(x - mx) * inv - (i == label ? 1.f : 0.f)) * grad_scale;
+        else o = (e * inv - (i == label ? 1.f : 0.f)) * grad_scale;
         outr[i] = o;
       };
       if (IN_REGS) {

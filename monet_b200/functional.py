@@ -802,6 +802,25 @@ def conv2d_fprop(x, w, bias, stride, padding, dilation, groups=1, variant: int =
     if geom is not None:
         if variant != 0:
             raise RuntimeError("monet_b200.conv2d_fprop: no variant %d for a few-channel input" % variant)
+        hp2, wp2 = C.c_int(0), C.c_int(0)
+        if lib().mb_conv_smallc2_geometry(C.byref(d0), C.byref(hp2), C.byref(wp2)) == 0:
+            # stride 2: both row phases in one buffer, forward on the many-tap kernel
+            xc = x.detach().contiguous()
+            xp2 = torch.empty((d0.N, hp2.value, wp2.value, 8), dtype=x.dtype, device=x.device)
+            check(lib().mb_conv_smallc2_pack_input(xc.data_ptr(), xp2.data_ptr(), C.byref(d0), _stream()),
+                  "conv_smallc2_pack_input")
+            T = (d0.R + 1) // 2
+            wpad = torch.zeros((d0.K, 4, 2 * T, 8), dtype=w.dtype, device=w.device)
+            wpad[:, :d0.C, :d0.R, :d0.S] = w.detach()
+            # (k, c, dh, phase, chunk, s%4) -> (k, dh, chunk, s%4, phase, c)
+            wq = wpad.view(d0.K, 4, T, 2, 2, 4).permute(0, 2, 4, 5, 3, 1).contiguous()
+            y = torch.empty((d0.N, d0.K, d0.P, d0.Q), dtype=x.dtype, device=x.device,
+                            memory_format=torch.channels_last)
+            b = bias.detach().contiguous() if bias is not None else None
+            check(lib().mb_conv2d_fprop_smallc2(xp2.data_ptr(), wq.data_ptr(),
+                                                b.data_ptr() if b is not None else None, y.data_ptr(),
+                                                C.byref(d0), _stream()), "conv2d_fprop_smallc2")
+            return y
         xp = _smallc_input(x, d0, geom)
         wp = torch.zeros((d0.K, d0.R, 8, 4), dtype=w.dtype, device=w.device)
         wp[:, :, :d0.S, :d0.C] = w.detach().permute(0, 2, 3, 1)
