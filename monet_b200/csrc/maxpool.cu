@@ -50,28 +50,65 @@ __global__ void __launch_bounds__(256) maxpool_fwd_nhwc8(const float* __restrict
       idx[k] = 0;
     }
     const float* xn = x + static_cast<size_t>(n) * p.H * p.W * p.C + g * 8;
+    if (KH > 0 && KW > 0) {
+      // Compile-time window: every tap is loaded first, from a clamped (always valid) address,
+      // and only then compared.  With the loads behind the bounds tests the compiler issued
+      // them one by one and the kernel waited on each (long-scoreboard stalls, 0.6 of the HBM
+      // roofline); issued together they overlap.
+      float4 va[KH * KW > 0 ? KH * KW : 1], vb[KH * KW > 0 ? KH * KW : 1];
+      bool ok[KH * KW > 0 ? KH * KW : 1];
 #pragma unroll
-    for (int i = 0; i < kh; ++i) {
-      const int h = h0 + i * dh;
-      if (h < 0 || h >= p.H) continue;
+      for (int i = 0; i < KH; ++i) {
+        const int h = h0 + i;
+        const int hc = h < 0 ? 0 : (h >= p.H ? p.H - 1 : h);
 #pragma unroll
-      for (int j = 0; j < kw; ++j) {
-        const int w = w0 + j * dw;
-        if (w < 0 || w >= p.W) continue;
-        const uint32_t local = i * kw + j;
-        const float4* src =
-            reinterpret_cast<const float4*>(xn + (static_cast<size_t>(h) * p.W + w) * p.C);
-        const float4 a = __ldg(src), b = __ldg(src + 1);
+        for (int j = 0; j < KW; ++j) {
+          const int w = w0 + j;
+          const int wc = w < 0 ? 0 : (w >= p.W ? p.W - 1 : w);
+          const float4* src =
+              reinterpret_cast<const float4*>(xn + (static_cast<size_t>(hc) * p.W + wc) * p.C);
+          va[i * KW + j] = __ldg(src);
+          vb[i * KW + j] = __ldg(src + 1);
+          ok[i * KW + j] = h == hc && w == wc;
+        }
+      }
+#pragma unroll
+      for (int tap = 0; tap < KH * KW; ++tap) {
+        if (!ok[tap]) continue;
+        const float4 a = va[tap], b = vb[tap];
         const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          if (first) idx[k] = local;
+          if (first) idx[k] = tap;
           if (better(v[k], best[k])) {
             best[k] = v[k];
-            idx[k] = local;
+            idx[k] = tap;
           }
         }
         first = false;
+      }
+    } else {
+      for (int i = 0; i < kh; ++i) {
+        const int h = h0 + i * dh;
+        if (h < 0 || h >= p.H) continue;
+        for (int j = 0; j < kw; ++j) {
+          const int w = w0 + j * dw;
+          if (w < 0 || w >= p.W) continue;
+          const uint32_t local = i * kw + j;
+          const float4* src =
+              reinterpret_cast<const float4*>(xn + (static_cast<size_t>(h) * p.W + w) * p.C);
+          const float4 a = __ldg(src), b = __ldg(src + 1);
+          const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            if (first) idx[k] = local;
+            if (better(v[k], best[k])) {
+              best[k] = v[k];
+              idx[k] = local;
+            }
+          }
+          first = false;
+        }
       }
     }
     f8 out;

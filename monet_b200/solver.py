@@ -753,6 +753,9 @@ def main(argv=None):
     ap.add_argument("--width", type=int, default=224)
     ap.add_argument("--out", default=None, help="directory for the solution pickle (default: <MONeT root>/data)")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--profile_only", action="store_true",
+                    help="stop after the cost tables are written (cost_<model>_<bs>_<mode>.pkl under --out): "
+                         "profile on the GPU machine, solve anywhere with --cost_file")
     args = ap.parse_args(argv)
 
     ref = rh.activate()
@@ -775,6 +778,9 @@ def main(argv=None):
         model = model.cuda()
     graph, si = rh.build_solver_info(model, args.bs, name, args.mode, shape, workdir=workdir,
                                      profile=profile, profiler="events" if args.costs == "events" else "reference")
+    if args.profile_only:
+        print(json.dumps({"cost_file": str(workdir / "data" / f"cost_{si.data_path}.pkl"), "costs": args.costs}))
+        return
     base = check_solution(si, hand_solution(si, "store_all"))
     sol = solve(si, args.budget, time_limit=args.time_limit, mip_rel_gap=args.gap, verbose=args.verbose)
     chk = check_solution(si, sol, args.budget)
