@@ -47,9 +47,6 @@ enum { MB_NCHW = 0, MB_NHWC = 1 };
 const char* mb_last_error(void);
 /* ABI version, bumped when a signature changes.                             */
 int mb_abi_version(void);
-/* Number of kernels this library has launched in this process (all threads).
- * bench.py reads it to report `gpu_launches`.                               */
-unsigned long long mb_launch_count(void);
 
 /* ---- ReLU (replaces lrrelu.cpp:11-20, lrrelu.cu:4-15; relu.py:9-118) ---- */
 
@@ -345,12 +342,6 @@ int mb_depthwise_dgrad(const float* dy, const float* w_tc, float* dx, const mb_c
                        void* stream);
 int mb_depthwise_wgrad(const float* x, const float* dy, float* dw_tc, float* dbias,
                        const mb_conv_desc* d, void* stream);
-/* Diagnostics.  When `device_buffer` (16 x int64, device memory) is non-NULL the
- * stride-1 multi-tap forward / backward-data kernel's first CTA records how many SM
- * cycles each of its roles spent waiting ([0] total, [1] input tile, [2] filter tile,
- * [3] accumulator free, [4]/[5] producer on free slots, [6] epilogue on results,
- * [7] epilogue busy, [8] work items).  NULL switches it off (the default).            */
-int mb_conv_debug_counters(long long* device_buffer);
 /* Few-channel convolutions (C <= 4, filter width <= 8, stride <= 2: the network's first
  * layer).  The input is copied once into a zero-padded 4-channel NHWC buffer
  * xp[N][Hp][Wp][4] (Hp, Wp from mb_conv_smallc_geometry; N*Hp*Wp*16 bytes, the caller's
@@ -380,6 +371,19 @@ int mb_conv2d_wgrad_smallc(const float* xp, const float* dy, float* dwp, float* 
  * the first pipeline wait that timed out (the kernel then gave up cleanly).
  * Synchronises the device.  reset != 0 clears it.                            */
 int mb_conv_device_status(int reset);
+
+/* ---- diagnostics (NOT part of the drop-in boundary: nothing in the operator library calls
+ * them; they exist for the bench harness and for kernel work and may change freely) -------- */
+
+/* Number of kernels this library has launched in this process (all threads).
+ * bench.py reads it to report `gpu_launches`.                               */
+unsigned long long mb_launch_count(void);
+/* When `device_buffer` (16 x int64, device memory) is non-NULL the stride-1 multi-tap
+ * forward / backward-data kernel's first CTA records how many SM cycles each of its roles
+ * spent waiting ([0] total, [1] input tile, [2] filter tile, [3] accumulator free, [4]/[5]
+ * producer on free slots, [6] epilogue on results, [7] epilogue busy, [8] work items).
+ * NULL switches it off (the default).                                                   */
+int mb_conv_debug_counters(long long* device_buffer);
 
 #ifdef __cplusplus
 }

@@ -213,3 +213,35 @@ def test_unet_with_transposed_convolution_through_the_runner_on_cpu():
         for (k, p), (_, q) in zip(m.named_parameters(), ref.named_parameters()):
             err = float((p.grad - q.grad).abs().max())
             assert err < 2e-3 * float(q.grad.abs().max()) + 1e-4 * top, (k, err)
+
+
+def test_rejected_geometries_say_why(built_lib):
+    """Geometries outside the kernels' range return MB_ERR_UNSUPPORTED with a message before
+    anything touches the device (no GPU needed: the descriptor is validated first)."""
+    import ctypes as C
+    from monet_b200 import _lib
+    api = _lib.lib()
+    one = C.c_void_p(16)          # a non-null, 16-byte aligned stand-in: never dereferenced
+
+    def conv(N, Cc, H, W, K, R, S, s, pad, groups=1):
+        P = (H + 2 * pad - (R - 1) - 1) // s + 1
+        Q = (W + 2 * pad - (S - 1) - 1) // s + 1
+        return _lib.ConvDesc(N, Cc, H, W, K, R, S, P, Q, s, s, pad, pad, 1, 1, groups)
+
+    cases = [
+        (conv(1, 32, 16, 16, 32, 3, 3, 3, 1), "stride"),            # stride above 2
+        (conv(1, 32, 16, 16, 32, 3, 3, 1, 1, groups=2), "group"),   # grouped, not depthwise
+        (conv(1, 32, 20, 20, 32, 9, 9, 1, 4), "taps"),              # more than 64 filter taps
+        (conv(1, 30, 16, 16, 32, 3, 3, 1, 1), "multiples of 4"),    # channel count not padded
+    ]
+    for d, word in cases:
+        rc = api.mb_conv2d_fprop(one, one, None, one, C.byref(d), 0, None, 0, None)
+        assert rc == 2, (word, rc, _lib.last_error())
+        assert word in _lib.last_error(), _lib.last_error()
+    d = conv(1, 32, 16, 16, 64, 3, 3, 1, 1, groups=32)              # depthwise with a channel multiplier
+    rc = api.mb_depthwise_fprop(one, one, None, one, C.byref(d), None)
+    assert rc == 2 and "groups" in _lib.last_error()
+    d = conv(1, 32, 16, 16, 32, 3, 3, 1, 1)
+    assert api.mb_conv2d_fprop(one, one, None, one, C.byref(d), 7, None, 0, None) == 2   # no such variant
+    pd = _lib.PoolDesc(1, 8, 16, 16, 4, 4, 5, 5, 3, 3, 0, 0, 1, 1, _lib.MB_NHWC)          # 25 taps > 4 bits
+    assert api.mb_maxpool2d_fwd(one, one, one, C.byref(pd), None) == 2 and "4-bit" in _lib.last_error()
