@@ -91,6 +91,7 @@ __global__ void __launch_bounds__(256) dw_dgrad(const float* __restrict__ dy, co
 // (4.5 instead of 9 loads per output at stride 1).  A warp still walks the channel groups
 // first, so every load instruction covers contiguous runs of 4*32 channels.
 constexpr int kTw = 4;
+constexpr int kPatchG = 4, kPatchRows = 4;   // channel groups (of 4) and output rows of a CTA's patch
 
 __device__ __forceinline__ void fma4(float4& acc, const float4& a, const float4& f) {
   acc.x = fmaf(a.x, f.x, acc.x); acc.y = fmaf(a.y, f.y, acc.y);
@@ -109,12 +110,23 @@ __global__ void __launch_bounds__(256) dw3x3_tiled(const float* __restrict__ x, 
   const int cg = p.C / 4;
   for (size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
        t += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const int g = static_cast<int>(t % cg);
-    size_t rest = t / cg;
+    // Work items are ordered so that the 256 threads of a CTA cover a patch -- 4 channel groups
+    // x a whole row of column tiles x 4 consecutive output rows -- instead of half a row of all
+    // channels: the three output rows that read an input row then sit in the same CTA and meet
+    // in L1 (before: 45 % L1 hits, 3.2x the input fetched from L2).
+    const int g_l = static_cast<int>(t % kPatchG);
+    size_t rest = t / kPatchG;
     const int qt = static_cast<int>(rest % qtiles);
     rest /= qtiles;
-    const int pp = static_cast<int>(rest % p.P);
-    const int n = static_cast<int>(rest / p.P);
+    const int r_l = static_cast<int>(rest % kPatchRows);
+    rest /= kPatchRows;
+    const int gchunks = (cg + kPatchG - 1) / kPatchG, pblocks = (p.P + kPatchRows - 1) / kPatchRows;
+    const int gc = static_cast<int>(rest % gchunks);
+    rest /= gchunks;
+    const int pb = static_cast<int>(rest % pblocks);
+    const int n = static_cast<int>(rest / pblocks);
+    const int g = gc * kPatchG + g_l, pp = pb * kPatchRows + r_l;
+    if (g >= cg || pp >= p.P) continue;
     const int q0 = qt * kTw;
     float4 f[9];
 #pragma unroll
@@ -320,6 +332,12 @@ __global__ void __launch_bounds__(256) dw3x3_wgrad(const float* __restrict__ x, 
   }
 }
 
+// work items of dw3x3_tiled: patches are padded to whole channel-group chunks and row blocks
+size_t tiled_items(const DwP& p, int qtiles) {
+  const size_t gchunks = (p.C / 4 + kPatchG - 1) / kPatchG, pblocks = (p.P + kPatchRows - 1) / kPatchRows;
+  return static_cast<size_t>(p.N) * pblocks * gchunks * kPatchRows * qtiles * kPatchG;
+}
+
 int check(const char* who, const mb_conv_desc* d, DwP* p) {
   if (!d) return fail(MB_ERR_INVALID_ARGUMENT, "%s: null descriptor", who);
   if (d->groups != d->C || d->K != d->C)
@@ -351,7 +369,7 @@ int mb_depthwise_fprop(const float* x, const float* w_tc, const float* bias, flo
     return fail(MB_ERR_INVALID_ARGUMENT, "mb_depthwise_fprop: null or misaligned pointer");
   if (p.R == 3 && p.S == 3 && p.dh == 1 && p.dw == 1 && p.sh == p.sw && (p.sh == 1 || p.sh == 2)) {
     const int qtiles = (p.Q + kTw - 1) / kTw;
-    const size_t total = static_cast<size_t>(p.N) * p.P * qtiles * (p.C / 4);
+    const size_t total = tiled_items(p, qtiles);
     const int grid = grid_for(total, 256, 8);
     if (p.sh == 1)
       dw3x3_tiled<1, false><<<grid, 256, 0, as_stream(stream)>>>(x, w_tc, bias, y, p, qtiles, total);
@@ -377,7 +395,7 @@ int mb_depthwise_dgrad(const float* dy, const float* w_tc, float* dx, const mb_c
     b.H = p.P; b.W = p.Q; b.P = p.H; b.Q = p.W;
     b.ph = 2 - p.ph; b.pw = 2 - p.pw;
     const int qtiles = (b.Q + kTw - 1) / kTw;
-    const size_t total = static_cast<size_t>(b.N) * b.P * qtiles * (b.C / 4);
+    const size_t total = tiled_items(b, qtiles);
     dw3x3_tiled<1, true><<<grid_for(total, 256, 8), 256, 0, as_stream(stream)>>>(dy, w_tc, nullptr, dx, b,
                                                                                  qtiles, total);
     return after_launch("depthwise_dgrad_3x3");

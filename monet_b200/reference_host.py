@@ -254,9 +254,14 @@ def build_solver_info(model, batch: int, model_name: str, mode: str, input_shape
     graph = ref.graph.Graph.create(cpu_model, input_shape)
     del cpu_model
     si = ref.solver_info.SolverInfo(batch, model_name, mode)
-    workdir = Path(workdir) if workdir is not None else ref.root
+    workdir = (Path(workdir) if workdir is not None else ref.root).resolve()
     with _in_dir(workdir):
-        if profile:
+        cached = (workdir / "data" / f"cost_{si.data_path}.pkl").is_file()
+        if profile and cached:
+            # get_workspace_cost() reads the tables of an earlier profiling run from
+            # ../data/cost_*.pkl (solver_info.py:347-360): no GPU needed
+            si.extract(graph)
+        elif profile:
             m = wrap_mobilenet(model)
             dev = next(m.parameters()).device
             if dev.type != "cuda":
