@@ -538,7 +538,10 @@ def torch_gpu_baseline(make_model, x, y, steps, warmup, pixelwise):
         torch.backends.cudnn.allow_tf32, torch.backends.cudnn.benchmark, torch.backends.cuda.matmul.allow_tf32 = old
 
 
-SOLVED_10GB = ROOT / "monet_b200" / "schedules" / "solution_resnet50_184_inplace_conv_multiway_newnode_10.00.pkl"
+_SCHEDULES = ROOT / "monet_b200" / "schedules"
+SOLVED_10GB = _SCHEDULES / "solution_resnet50_184_inplace_conv_multiway_newnode_10.00_measured.pkl"
+if not SOLVED_10GB.exists():        # solved on the bytes-and-flops cost model instead of measured kernel times
+    SOLVED_10GB = _SCHEDULES / "solution_resnet50_184_inplace_conv_multiway_newnode_10.00.pkl"
 
 
 def reference_executor_block(model, params, x, y, B, in_shape, args, timed):

@@ -91,7 +91,6 @@ __global__ void __launch_bounds__(256) dw_dgrad(const float* __restrict__ dy, co
 // (4.5 instead of 9 loads per output at stride 1).  A warp still walks the channel groups
 // first, so every load instruction covers contiguous runs of 4*32 channels.
 constexpr int kTw = 4;
-constexpr int kPatchG = 4, kPatchRows = 4;   // channel groups (of 4) and output rows of a CTA's patch
 
 __device__ __forceinline__ void fma4(float4& acc, const float4& a, const float4& f) {
   acc.x = fmaf(a.x, f.x, acc.x); acc.y = fmaf(a.y, f.y, acc.y);
@@ -108,25 +107,20 @@ __global__ void __launch_bounds__(256) dw3x3_tiled(const float* __restrict__ x, 
                                                    DwP p, int qtiles, size_t total) {
   constexpr int kCols = (kTw - 1) * STRIDE + 3;
   const int cg = p.C / 4;
-  for (size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
-       t += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    // Work items are ordered so that the 256 threads of a CTA cover a patch -- 4 channel groups
-    // x a whole row of column tiles x 4 consecutive output rows -- instead of half a row of all
-    // channels: the three output rows that read an input row then sit in the same CTA and meet
-    // in L1 (before: 45 % L1 hits, 3.2x the input fetched from L2).
-    const int g_l = static_cast<int>(t % kPatchG);
-    size_t rest = t / kPatchG;
-    const int qt = static_cast<int>(rest % qtiles);
-    rest /= qtiles;
-    const int r_l = static_cast<int>(rest % kPatchRows);
-    rest /= kPatchRows;
-    const int gchunks = (cg + kPatchG - 1) / kPatchG, pblocks = (p.P + kPatchRows - 1) / kPatchRows;
-    const int gc = static_cast<int>(rest % gchunks);
-    rest /= gchunks;
-    const int pb = static_cast<int>(rest % pblocks);
-    const int n = static_cast<int>(rest / pblocks);
-    const int g = gc * kPatchG + g_l, pp = pb * kPatchRows + r_l;
-    if (g >= cg || pp >= p.P) continue;
+  // 32-bit index arithmetic (the host sends larger problems to the generic kernel): the three
+  // 64-bit divisions per work item of the first version were a quarter of its instructions,
+  // and the kernel is bound by instruction issue, not by memory (ncu: ALU pipe 62 %, issue
+  // slots 67 % busy, DRAM 40 %)
+  const unsigned total32 = static_cast<unsigned>(total), ucg = static_cast<unsigned>(cg),
+                 uqt = static_cast<unsigned>(qtiles), uP = static_cast<unsigned>(p.P);
+  for (unsigned t = blockIdx.x * blockDim.x + threadIdx.x; t < total32; t += gridDim.x * blockDim.x) {
+    const unsigned r1 = t / ucg;
+    const int g = static_cast<int>(t - r1 * ucg);
+    const unsigned r2 = r1 / uqt;
+    const int qt = static_cast<int>(r1 - r2 * uqt);
+    const unsigned n_u = r2 / uP;
+    const int pp = static_cast<int>(r2 - n_u * uP);
+    const int n = static_cast<int>(n_u);
     const int q0 = qt * kTw;
     float4 f[9];
 #pragma unroll
@@ -138,9 +132,26 @@ __global__ void __launch_bounds__(256) dw3x3_tiled(const float* __restrict__ x, 
     for (int j = 0; j < kTw; ++j) acc[j] = b0;
     const float* xn = x + static_cast<size_t>(n) * p.H * p.W * p.C + g * 4;
     const int w0 = q0 * STRIDE - p.pw;
+    const int h0 = pp * STRIDE - p.ph;
+    if (h0 >= 0 && h0 + 2 < p.H && w0 >= 0 && w0 + kCols <= p.W) {
+      // the whole 3 x kCols window lies inside the map (most tiles): no bounds tests, no zero
+      // fill, one base pointer and two strides
+      const float4* xb = reinterpret_cast<const float4*>(xn + (static_cast<size_t>(h0) * p.W + w0) * p.C);
+      const size_t rstep = static_cast<size_t>(p.W) * cg;
+#pragma unroll
+      for (int r = 0; r < 3; ++r) {
+        float4 col[kCols];
+#pragma unroll
+        for (int c = 0; c < kCols; ++c) col[c] = __ldg(xb + r * rstep + static_cast<size_t>(c) * cg);
+#pragma unroll
+        for (int j = 0; j < kTw; ++j)
+#pragma unroll
+          for (int sidx = 0; sidx < 3; ++sidx) fma4(acc[j], col[j * STRIDE + sidx], f[r * 3 + sidx]);
+      }
+    } else
 #pragma unroll
     for (int r = 0; r < 3; ++r) {
-      const int h = pp * STRIDE - p.ph + r;
+      const int h = h0 + r;
       if (h < 0 || h >= p.H) continue;
       const float* xr = xn + static_cast<size_t>(h) * p.W * p.C;
       float4 col[kCols];
@@ -167,14 +178,16 @@ __global__ void __launch_bounds__(256) dw3x3_tiled(const float* __restrict__ x, 
 __global__ void __launch_bounds__(256) dw3x3s2_dgrad(const float* __restrict__ dy, const float* __restrict__ w,
                                                      float* __restrict__ dx, DwP p, size_t total) {
   const int cg = p.C / 4;
-  for (size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
-       t += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const int g = static_cast<int>(t % cg);
-    size_t pix = t / cg;
-    const int ww = static_cast<int>(pix % p.W);
-    pix /= p.W;
-    const int h = static_cast<int>(pix % p.H);
-    const int n = static_cast<int>(pix / p.H);
+  const unsigned total32 = static_cast<unsigned>(total), ucg = static_cast<unsigned>(cg),
+                 uW = static_cast<unsigned>(p.W), uH = static_cast<unsigned>(p.H);
+  for (unsigned t = blockIdx.x * blockDim.x + threadIdx.x; t < total32; t += gridDim.x * blockDim.x) {
+    const unsigned r1 = t / ucg;
+    const int g = static_cast<int>(t - r1 * ucg);
+    const unsigned r2 = r1 / uW;
+    const int ww = static_cast<int>(r1 - r2 * uW);
+    const unsigned n_u = r2 / uH;
+    const int h = static_cast<int>(r2 - n_u * uH);
+    const int n = static_cast<int>(n_u);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     const float* dn = dy + static_cast<size_t>(n) * p.P * p.Q * p.C + g * 4;
 #pragma unroll
@@ -278,10 +291,12 @@ __global__ void __launch_bounds__(256) dw3x3_wgrad(const float* __restrict__ x, 
     const size_t t0 = static_cast<size_t>(blockIdx.x) * per;
     const size_t t1 = (t0 + per) < tiles ? (t0 + per) : tiles;
     for (size_t tile = t0 + ty; tile < t1; tile += ty_n) {
-      const int qt = static_cast<int>(tile % qtiles);
-      size_t rest = tile / qtiles;
-      const int pp = static_cast<int>(rest % p.P);
-      const int n = static_cast<int>(rest / p.P);
+      const unsigned ut = static_cast<unsigned>(tile);        // the host checks tiles < 2^31
+      const unsigned r1 = ut / static_cast<unsigned>(qtiles);
+      const int qt = static_cast<int>(ut - r1 * static_cast<unsigned>(qtiles));
+      const unsigned n_u = r1 / static_cast<unsigned>(p.P);
+      const int pp = static_cast<int>(r1 - n_u * static_cast<unsigned>(p.P));
+      const int n = static_cast<int>(n_u);
       const int q0 = qt * kTw;
       float4 d[kTw];
       const float4* dr = reinterpret_cast<const float4*>(dy + ((static_cast<size_t>(n) * p.P + pp) * p.Q + q0) * p.C) + g;
@@ -332,12 +347,6 @@ __global__ void __launch_bounds__(256) dw3x3_wgrad(const float* __restrict__ x, 
   }
 }
 
-// work items of dw3x3_tiled: patches are padded to whole channel-group chunks and row blocks
-size_t tiled_items(const DwP& p, int qtiles) {
-  const size_t gchunks = (p.C / 4 + kPatchG - 1) / kPatchG, pblocks = (p.P + kPatchRows - 1) / kPatchRows;
-  return static_cast<size_t>(p.N) * pblocks * gchunks * kPatchRows * qtiles * kPatchG;
-}
-
 int check(const char* who, const mb_conv_desc* d, DwP* p) {
   if (!d) return fail(MB_ERR_INVALID_ARGUMENT, "%s: null descriptor", who);
   if (d->groups != d->C || d->K != d->C)
@@ -367,9 +376,10 @@ int mb_depthwise_fprop(const float* x, const float* w_tc, const float* bias, flo
   if (rc) return rc;
   if (!x || !w_tc || !y || !aligned(x, 16) || !aligned(w_tc, 16) || !aligned(y, 16) || !aligned(bias, 16))
     return fail(MB_ERR_INVALID_ARGUMENT, "mb_depthwise_fprop: null or misaligned pointer");
-  if (p.R == 3 && p.S == 3 && p.dh == 1 && p.dw == 1 && p.sh == p.sw && (p.sh == 1 || p.sh == 2)) {
+  if (p.R == 3 && p.S == 3 && p.dh == 1 && p.dw == 1 && p.sh == p.sw && (p.sh == 1 || p.sh == 2) &&
+      static_cast<size_t>(p.N) * p.P * ((p.Q + kTw - 1) / kTw) * (p.C / 4) < 0x7fffffffull) {
     const int qtiles = (p.Q + kTw - 1) / kTw;
-    const size_t total = tiled_items(p, qtiles);
+    const size_t total = static_cast<size_t>(p.N) * p.P * qtiles * (p.C / 4);
     const int grid = grid_for(total, 256, 8);
     if (p.sh == 1)
       dw3x3_tiled<1, false><<<grid, 256, 0, as_stream(stream)>>>(x, w_tc, bias, y, p, qtiles, total);
@@ -389,19 +399,20 @@ int mb_depthwise_dgrad(const float* dy, const float* w_tc, float* dx, const mb_c
   if (rc) return rc;
   if (!dy || !w_tc || !dx || !aligned(dy, 16) || !aligned(w_tc, 16) || !aligned(dx, 16))
     return fail(MB_ERR_INVALID_ARGUMENT, "mb_depthwise_dgrad: null or misaligned pointer");
-  if (p.R == 3 && p.S == 3 && p.dh == 1 && p.dw == 1 && p.sh == 1 && p.sw == 1 && p.ph <= 2 && p.pw <= 2) {
+  if (p.R == 3 && p.S == 3 && p.dh == 1 && p.dw == 1 && p.sh == 1 && p.sw == 1 && p.ph <= 2 && p.pw <= 2 &&
+      static_cast<size_t>(p.N) * p.H * ((p.W + kTw - 1) / kTw) * (p.C / 4) < 0x7fffffffull) {
     // stride 1: a forward pass over dy with the flipped filter and padding 2 - pad
     DwP b = p;
     b.H = p.P; b.W = p.Q; b.P = p.H; b.Q = p.W;
     b.ph = 2 - p.ph; b.pw = 2 - p.pw;
     const int qtiles = (b.Q + kTw - 1) / kTw;
-    const size_t total = tiled_items(b, qtiles);
+    const size_t total = static_cast<size_t>(b.N) * b.P * qtiles * (b.C / 4);
     dw3x3_tiled<1, true><<<grid_for(total, 256, 8), 256, 0, as_stream(stream)>>>(dy, w_tc, nullptr, dx, b,
                                                                                  qtiles, total);
     return after_launch("depthwise_dgrad_3x3");
   }
   const size_t total = static_cast<size_t>(p.N) * p.H * p.W * (p.C / 4);
-  if (p.R == 3 && p.S == 3 && p.dh == 1 && p.dw == 1 && p.sh == 2 && p.sw == 2) {
+  if (p.R == 3 && p.S == 3 && p.dh == 1 && p.dw == 1 && p.sh == 2 && p.sw == 2 && total < 0x7fffffffull) {
     dw3x3s2_dgrad<<<grid_for(total, 256, 8), 256, 0, as_stream(stream)>>>(dy, w_tc, dx, p, total);
     return after_launch("depthwise_dgrad_3x3s2");
   }
@@ -434,7 +445,8 @@ int mb_depthwise_wgrad(const float* x, const float* dy, float* dw_tc, float* dbi
   if (chunks > cap) chunks = cap;
   if (chunks < 1) chunks = 1;
   const size_t smem = 256 * sizeof(float4);
-  if (taps == 9 && p.dh == 1 && p.dw == 1 && p.sh == p.sw && (p.sh == 1 || p.sh == 2)) {
+  if (taps == 9 && p.dh == 1 && p.dw == 1 && p.sh == p.sw && (p.sh == 1 || p.sh == 2) &&
+      static_cast<size_t>(p.N) * p.P * ((p.Q + kTw - 1) / kTw) < 0x7fffffffull) {
     const int qtiles = (p.Q + kTw - 1) / kTw;
     const size_t tiles = static_cast<size_t>(p.N) * p.P * qtiles;
     int tchunks = static_cast<int>((tiles + ty * 2 - 1) / (static_cast<size_t>(ty) * 2));

@@ -147,12 +147,14 @@ def test_inplace_table_names_the_overwritten_input(host, tmp_path):
         assert si.nodes[si.inplace_list[v]].last_used == v
 
 
-def test_shipped_schedule_is_valid(host, tmp_path):
-    """The committed 10 GB ResNet-50 schedule still matches the graph this PyTorch traces, and
+@pytest.mark.parametrize("fname", ["solution_resnet50_184_inplace_conv_multiway_newnode_10.00.pkl",
+                                   "solution_resnet50_184_inplace_conv_multiway_newnode_10.00_measured.pkl"])
+def test_shipped_schedule_is_valid(host, tmp_path, fname):
+    """Each committed 10 GB ResNet-50 schedule still matches the graph this PyTorch traces, and
     satisfies every row of the reference's ILP literally (no budget row above 10 GB)."""
     from monet_b200 import solver
     rh, ref = host
-    path = Path(rh.__file__).resolve().parent / "schedules" / "solution_resnet50_184_inplace_conv_multiway_newnode_10.00.pkl"
+    path = Path(rh.__file__).resolve().parent / "schedules" / fname
     si, sol = ref.schedule.load_solution(str(path))
     chk = solver.check_solution(si, sol, 10.0)
     assert chk["violations"] == [] and chk["peak_gb"] <= 10.0
