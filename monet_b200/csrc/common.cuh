@@ -30,6 +30,24 @@ inline int grid_for(size_t work_items, size_t per_block, int ctas_per_sm) {
   return static_cast<int>(need < cap ? need : cap);
 }
 
+// Decompose a flat work-item index t = (rest * d1 + i1) * d0 + i0.  Indices below 2^32 take
+// 32-bit divisions: a 64-bit division costs several times as many instructions, and the
+// stencil kernels (pooling, depthwise) are bound by instruction issue rather than by memory.
+__device__ __forceinline__ void split3(size_t t, int d0, int d1, int& i0, int& i1, int& rest) {
+  if (t <= 0xffffffffull) {
+    const unsigned u = static_cast<unsigned>(t), ud0 = static_cast<unsigned>(d0), ud1 = static_cast<unsigned>(d1);
+    const unsigned r1 = u / ud0, r2 = r1 / ud1;
+    i0 = static_cast<int>(u - r1 * ud0);
+    i1 = static_cast<int>(r1 - r2 * ud1);
+    rest = static_cast<int>(r2);
+  } else {
+    const size_t r1 = t / d0, r2 = r1 / d1;
+    i0 = static_cast<int>(t - r1 * d0);
+    i1 = static_cast<int>(r1 - r2 * d1);
+    rest = static_cast<int>(r2);
+  }
+}
+
 // ---- 256-bit global accesses (8 floats per thread per instruction) --------
 struct f8 { float v[8]; };
 

@@ -34,12 +34,9 @@ __global__ void __launch_bounds__(256) maxpool_fwd_nhwc8(const float* __restrict
   const int dh = KH ? 1 : p.dh, dw = KW ? 1 : p.dw;
   for (size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
        t += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const int g = static_cast<int>(t % cg);
-    size_t pix = t / cg;
-    const int q = static_cast<int>(pix % p.Q);
-    pix /= p.Q;
-    const int pp = static_cast<int>(pix % p.P);
-    const int n = static_cast<int>(pix / p.P);
+    int g, q, rest;
+    split3(t, cg, p.Q, g, q, rest);
+    const int n = rest / p.P, pp = rest - n * p.P;
     const int h0 = pp * p.sh - p.ph, w0 = q * p.sw - p.pw;
     float best[8];
     uint32_t idx[8];
@@ -140,12 +137,9 @@ __global__ void __launch_bounds__(256) maxpool_bwd_nhwc8(const float* __restrict
   const int dh = KH ? 1 : p.dh, dw = KW ? 1 : p.dw;
   for (size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
        t += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const int g = static_cast<int>(t % cg);
-    size_t pix = t / cg;
-    const int w = static_cast<int>(pix % p.W);
-    pix /= p.W;
-    const int h = static_cast<int>(pix % p.H);
-    const int n = static_cast<int>(pix / p.H);
+    int g, w, rest;
+    split3(t, cg, p.W, g, w, rest);
+    const int n = rest / p.H, h = rest - n * p.H;
     float acc[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) acc[k] = 0.f;
@@ -199,12 +193,9 @@ __global__ void __launch_bounds__(256) maxpool_bwd_3x3s2p1_quad(const float* __r
   const int cg = p.C / 8, H2 = (p.H + 1) / 2, W2 = (p.W + 1) / 2;
   for (size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
        t += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const int g = static_cast<int>(t % cg);
-    size_t r = t / cg;
-    const int b = static_cast<int>(r % W2);
-    r /= W2;
-    const int a = static_cast<int>(r % H2);
-    const int n = static_cast<int>(r / H2);
+    int g, b, rest;
+    split3(t, cg, W2, g, b, rest);
+    const int n = rest / H2, a = rest - n * H2;
     float acc[2][2][8];
 #pragma unroll
     for (int u = 0; u < 2; ++u)
