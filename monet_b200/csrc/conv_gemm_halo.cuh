@@ -173,8 +173,8 @@ conv_gemm_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       int it = 0;
       long long w_af = 0, w_bf = 0, w_acc = 0;
       const long long t_start = prof ? clock64() : 0;
-      // 3x3 filters (every layer of the networks measured): the tap loop is unrolled with the tap
-      // offsets in registers, descriptors advance by their low word only and barriers are
+      // 3x3 filters (every layer of the networks measured) and the 7x7 stem: the tap loop is
+      // unrolled with the tap offsets in registers, descriptors advance by their low word only and barriers are
       // addressed by integer, so that few scalar instructions sit between two MMAs -- with
       // the generic loop below the issuing thread, not the tensor pipe, set the pace.
       auto issue_unrolled = [&](auto taps_c, auto mt_c) {
@@ -200,11 +200,19 @@ conv_gemm_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
           tc_fence_after();
           const uint32_t d_base = tmem_base + static_cast<uint32_t>(acc) * acc_cols;
           for (int kc = 0; ok && kc < p.kchunks; ++kc) {
-            if (!mbar_wait_u32(a_full_u + 8u * ra.stage, ra.phase, abort_flag)) { ok = false; break; }
+            {
+              const long long t0 = prof ? clock64() : 0;
+              if (!mbar_wait_u32(a_full_u + 8u * ra.stage, ra.phase, abort_flag)) { ok = false; break; }
+              if (prof) w_af += clock64() - t0;
+            }
             const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(ra.stage) * a_stage16;
 #pragma unroll
             for (int t = 0; t < TAPS; ++t) {
-              if (!mbar_wait_u32(b_full_u + 8u * rb.stage, rb.phase, abort_flag)) { ok = false; break; }
+              {
+                const long long t0 = prof ? clock64() : 0;
+                if (!mbar_wait_u32(b_full_u + 8u * rb.stage, rb.phase, abort_flag)) { ok = false; break; }
+                if (prof) w_bf += clock64() - t0;
+              }
               tc_fence_after();
               const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(rb.stage) * b_stage16;
 #pragma unroll
@@ -232,6 +240,10 @@ conv_gemm_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         issue_unrolled(std::integral_constant<int, 9>{}, std::integral_constant<int, 2>{});
       else if (p.num_taps == 9 && p.MT == 1)
         issue_unrolled(std::integral_constant<int, 9>{}, std::integral_constant<int, 1>{});
+      else if (p.num_taps == 4 && p.MT == 2)      // the 7x7 stride-2 stem: four row taps per phase pair
+        issue_unrolled(std::integral_constant<int, 4>{}, std::integral_constant<int, 2>{});
+      else if (p.num_taps == 4 && p.MT == 1)
+        issue_unrolled(std::integral_constant<int, 4>{}, std::integral_constant<int, 1>{});
       else
       for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++it) {
         const int acc = p.acc_bufs == 2 ? (it & 1) : 0;
