@@ -303,8 +303,9 @@ def family_costs(runner_obj, batch_shape):
     cost = {}
 
     def add(fam, b, f=0.0):
-        c = cost.setdefault(fam, [0.0, 0.0])
+        c = cost.setdefault(fam, [0.0, 0.0, []])
         c[0] += b; c[1] += f
+        c[2].append((b, f))          # per call, for the sum of per-layer floors
 
     shapes = runner_obj.shapes
     needed = getattr(runner_obj, "_need", {})     # node id -> backward step that reads its output
@@ -824,6 +825,34 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_dev, ms_e2e, ms_eager = float(t[0]), float(t[1]), float(t[2])
 
+    # ---- N > 1: the same replayed step without the gradient exchange, on every rank; the
+    # difference is the part of the all-reduce that backward does not hide
+    allreduce_exposed = None
+    if world > 1 and graph is not None:
+        kept, buckets = buckets, None          # `step` reads this variable when it runs
+        run.on_param_grad = None
+        g_local = None
+        try:
+            g_local = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_local, capture_error_mode="thread_local"):
+                step(x_st, y_st)
+        except Exception:
+            g_local = None
+            torch.cuda.synchronize()
+        ok = torch.tensor([1 if g_local is not None else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok[0]):
+            for _ in range(3):
+                g_local.replay()
+            ms_local, _ = timed(g_local.replay, args.steps)
+            t = torch.tensor([ms_local], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            allreduce_exposed = {"ms_per_step_without_exchange": float(t[0]),
+                                 "allreduce_ms_exposed": ms_dev - float(t[0])}
+        del g_local
+        buckets = kept
+        kept.install(run)
+
     # ---- comparators, rank 0 at N = 1 only (they are about one GPU): the reference's node set
     # (no fused nodes) through the same executor, and stock PyTorch on this GPU
     extras = {}
@@ -887,7 +916,7 @@ def run_ours(args):
             r["frac"] = r["achieved"] / r["peak"]
             return r
 
-        b, f = costs[dominant]
+        b, f = costs[dominant][:2]
         roof = roof_of(b, f, dom_ms)
         ratio = TRAFFIC_RATIO.get(dominant)
         roof.update({"traffic": (ratio * b / dom_calls / 1e9) if ratio else None, "traffic_unit": "GB per launch (ncu ratio x algorithmic bytes)",
@@ -899,13 +928,19 @@ def run_ours(args):
         for k, ms in sorted(survey.items(), key=lambda kv: -kv[1]):
             if k not in costs or ms <= 0:
                 continue
-            fb, ff = costs[k]
+            fb, ff, calls = costs[k]
             r = roof_of(fb, ff, ms)
+            # sum over the family's calls of each call's own floor (the slower of its bytes at the
+            # HBM rate and its flops at the TF32 rate): a family mixes HBM-bound and tensor-bound
+            # layers, so this, not the family totals, is what the kernels can be held against
+            floor_ms = sum(max(cb / (hbm * 1e9), cf / (tf32 * 1e12)) for cb, cf in calls) * 1e3
             families[k] = {"ms_per_step": round(ms, 3), "calls_per_step": survey_calls[k], "algorithmic_gb": round(fb / 1e9, 3),
                            "gflop": round(ff / 1e9, 1), "bound": r["bound"], "achieved": round(r["achieved"], 1),
-                           "unit": r["unit"], "frac": round(r["frac"], 3)}
+                           "unit": r["unit"], "frac": round(r["frac"], 3),
+                           "per_call_floor_ms": round(floor_ms, 3), "frac_of_per_call_floor": round(floor_ms / ms, 3)}
         conv_ms = sum(v["ms_per_step"] for k, v in families.items() if k.startswith("mb_conv2d"))
         conv_fl = sum(costs[k][1] for k in families if k.startswith("mb_conv2d"))
+        conv_floor = sum(v["per_call_floor_ms"] for k, v in families.items() if k.startswith("mb_conv2d"))
         line = {
             "metric": metric, "value": B * world / (ms_dev * 1e-3), "unit": "images/s",
             "n_gpus": world, "steps": args.steps, "warmup": W, "ms_per_step": ms_dev,
@@ -925,11 +960,15 @@ def run_ours(args):
             "tf32_peak_measured_tflops": tf32,
             "roofline_families": families,
             "conv_total": {"ms_per_step": round(conv_ms, 3), "tflops": round(conv_fl / (conv_ms * 1e-3) / 1e12, 1) if conv_ms else None,
-                           "frac_of_measured_tf32": round(conv_fl / (conv_ms * 1e-3) / 1e12 / tf32, 3) if conv_ms else None},
+                           "frac_of_measured_tf32": round(conv_fl / (conv_ms * 1e-3) / 1e12 / tf32, 3) if conv_ms else None,
+                           "per_call_floor_ms": round(conv_floor, 3),
+                           "frac_of_per_call_floor": round(conv_floor / conv_ms, 3) if conv_ms else None},
         }
         if buckets is not None:
             line["gradient_buckets"] = {"count": len(buckets.buckets), "mb": [round(fl.numel() * 4 / 2 ** 20, 1) for fl in buckets.flat],
                                         "overlap": "all-reduce (mean) per bucket on a communication stream during backward, inside the captured step"}
+        if allreduce_exposed is not None:
+            line.update(allreduce_exposed)
         line.update(extras)
         if graph_err:
             line["cuda_graph_error"] = graph_err
