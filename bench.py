@@ -60,6 +60,9 @@ def parse():
     ap.add_argument("--micro-batch", type=int, default=184)
     ap.add_argument("--cudnn", action="store_true",
                     help="with --micro on a convolution pass: also time cuDNN (TF32, benchmark mode) on the same tensors")
+    ap.add_argument("--conv-counters", action="store_true",
+                    help="with --micro on a stride-1 multi-tap fprop/dgrad: one extra launch with the kernel's own "
+                         "cycle counters (CTA 0) switched on, added to the line as `cta0_cycles`")
     return ap.parse_args()
 
 
@@ -207,6 +210,17 @@ def run_micro(args):
     ms = clock(fn)
     line = {"micro": args.micro, "batch": N, "ms": ms, "algorithmic_GBps": nbytes / ms / 1e6,
             "TFLOPps": flops / ms / 1e9, "conv_status": F.conv_device_status()}
+    if args.conv_counters and kind in ("fprop", "dgrad"):
+        import ctypes
+        from monet_b200 import _lib
+        buf = torch.zeros(16, dtype=torch.int64, device=dev)
+        _lib.lib().mb_conv_debug_counters(ctypes.c_void_p(buf.data_ptr()))
+        fn()
+        torch.cuda.synchronize()
+        _lib.lib().mb_conv_debug_counters(ctypes.c_void_p(0))
+        names = ["mma_thread_total", "mma_wait_input_tile", "mma_wait_filter_tile", "mma_wait_free_accumulator",
+                 "producer_wait_input_slot", "producer_wait_filter_slot", "epilogue_wait_result", "epilogue_busy", "work_items"]
+        line["cta0_cycles"] = dict(zip(names, buf.tolist()[:9]))
     if args.cudnn and kind in ("fprop", "dgrad", "wgrad"):
         # the library op this pass replaces, on the same tensors: cuDNN, TF32, benchmark mode
         torch.backends.cudnn.allow_tf32 = True
