@@ -509,8 +509,8 @@ int wgrad_run_halo(const char* who, wgh::Launches& hl, const float* x, const flo
     p.split_stride = split_stride;
     const int a = hl.phase_a[i], b = hl.phase_b[i];
     CUtensorMap mdy, mx;
-    rc = encode_act(who, &mdy, dy, d->K, d->Q, d->P, d->N, K4, K4 * d->Q, K4 * d->Q * d->P, p.Wh, p.bh,
-                    1, kWg);
+    rc = encode_act(who, &mdy, dy, d->K, d->Q, d->P, d->N, K4, K4 * d->Q, K4 * d->Q * d->P,
+                    p.row_loads ? p.bw : p.Wh, p.row_loads ? 1 : p.bh, 1, kWg);
     if (rc) return rc;
     const long long Wv = (d->W - b + d->stride_w - 1) / d->stride_w;
     const long long Hv = (d->H - a + d->stride_h - 1) / d->stride_h;

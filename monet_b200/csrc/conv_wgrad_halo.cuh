@@ -22,11 +22,19 @@
 // Compared with fetching one shifted x box per tap this cuts the x traffic
 // from R*S boxes to (bh + halo)/bh boxes per tile.
 //
+// Wide maps (a row with its halo does not fit a slot, or is wider than a TMA box): the map is
+// cut into column tiles of bw pixels.  The x box of a tile still carries its halo columns, but
+// the dy columns beyond bw belong to the next tile and must not be summed twice, so dy is
+// copied one image row at a time ({32 ch, bw, 1} boxes landing Wh rows apart) into a slot
+// that was zeroed once: the columns a tile does not own stay zero for the whole kernel.
+//
 // Work item: (128 output channels, one 32-channel chunk of x, a range of pixel
 // tiles); tensor memory holds the R*S accumulators of 128 x 32.  Rows that pad
 // a box up to a multiple of 8 (the MMA's K step) are zeroed once at kernel
 // start and never written again.
 #pragma once
+#include <cmath>
+
 #include "conv_wgrad.cuh"
 
 namespace mb {
@@ -44,6 +52,10 @@ struct WgHaloParams {
   unsigned char btap[16];   // filter tap (r*S + s) of each of this launch's taps
   int cchunks, k_tiles, splits;
   int Wh, bh;               // box width (pixels incl. halo) and output rows per tile
+  int tiles_w, bw;          // column tiles and the dy columns each owns (tiles_w == 1: bw == Q)
+  int row_loads;            // 1: dy arrives one image row per copy ({32 ch, bw, 1}), so that the
+                            //    Wh - bw columns a tile does not own stay zero (column tiles)
+  int a_boxes;              // dy boxes allocated per stage (2..4)
   int rowsA, rowsA_alloc;   // dy box rows (Wh*bh) and its allocation (multiple of 8)
   int rowsB, rowsB_alloc;   // x box rows (Wh*(bh+(R-1)*dil_h)) and its allocation
   int bhB;                  // x box height
@@ -81,11 +93,15 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
   const int t_end = (t_begin + per) < p.pix_tiles ? (t_begin + per) : p.pix_tiles;
   const int n_iter = t_end > t_begin ? t_end - t_begin : 0;
 
+  // Shared memory: the dy boxes of all stages first, then the x boxes.  An MMA always spans
+  // four dy boxes (M = 128); with fewer allocated (K <= 96) the rows of the missing ones are
+  // read from whatever follows -- the next stage's dy boxes or the x region, which the host
+  // sizes to cover them -- and land in accumulator rows that are never stored.
   const uint32_t a_box = static_cast<uint32_t>(p.rowsA_alloc) * 128u;
-  const uint32_t a_bytes = 4u * a_box;
+  const uint32_t a_bytes = static_cast<uint32_t>(p.a_boxes) * a_box;
   const uint32_t b_bytes = static_cast<uint32_t>(p.rowsB_alloc) * 128u;
-  const uint32_t stage_bytes = a_bytes + b_bytes;
-  const uint32_t tx_bytes = static_cast<uint32_t>(ka * p.rowsA + p.rowsB) * 128u;
+  const uint32_t b_region = static_cast<uint32_t>(p.stages) * a_bytes;
+  const uint32_t tx_bytes = static_cast<uint32_t>((p.row_loads ? ka * p.bh * p.bw : ka * p.rowsA) + p.rowsB) * 128u;
   uint32_t tmem_cols = 32;
   while (tmem_cols < 32u * p.ntaps) tmem_cols <<= 1;
 
@@ -98,17 +114,12 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
     *abort_flag = 0;
     fence_barrier_init();
   }
-  // zero the padding rows of every slot (TMA never touches them)
-  for (int s = 0; s < p.stages; ++s) {
-    uint8_t* slot = slots_ptr + static_cast<size_t>(s) * stage_bytes;
-    const int padA = (p.rowsA_alloc - p.rowsA) * 32;          // floats per box
-    for (int j = 0; j < 4; ++j) {
-      float* z = reinterpret_cast<float*>(slot + j * a_box + p.rowsA * 128);
-      for (int i = threadIdx.x; i < padA; i += blockDim.x) z[i] = 0.f;
-    }
-    float* zb = reinterpret_cast<float*>(slot + a_bytes + p.rowsB * 128);
-    const int padB = (p.rowsB_alloc - p.rowsB) * 32;
-    for (int i = threadIdx.x; i < padB; i += blockDim.x) zb[i] = 0.f;
+  // zero every slot once: the rows that pad a box up to a multiple of 8 and, with column tiles,
+  // the columns of a dy row that belong to the neighbouring tile are never written by TMA
+  {
+    float4* z = reinterpret_cast<float4*>(slots_ptr);
+    const uint32_t n16 = static_cast<uint32_t>(p.stages) * (a_bytes + b_bytes) / 16u;
+    for (uint32_t i = threadIdx.x; i < n16; i += blockDim.x) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // visible to the tensor core
   if (warp == 5) {
@@ -132,9 +143,9 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
       uint32_t armed[16];
       for (int s = 0; s < 16; ++s) armed[s] = 0;
       bool ok = true;
-      int ht = t_begin % p.tiles_h, n0 = t_begin / p.tiles_h;
+      int wt = t_begin % p.tiles_w, ht = (t_begin / p.tiles_w) % p.tiles_h, n0 = t_begin / (p.tiles_w * p.tiles_h);
       for (int t = t_begin; t < t_end; ++t) {
-        const int p0 = ht * p.bh;
+        const int p0 = ht * p.bh, w0 = wt * p.bw;
         if (lane == 0) {
           ok = mbar_wait(&empty[ring.stage], ring.phase ^ 1u, abort_flag);
           if (ok) {
@@ -144,13 +155,32 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
         }
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (!ok) break;
-        uint8_t* slot = slots_ptr + static_cast<size_t>(ring.stage) * stage_bytes;
-        if (lane < ka)
-          tma_load_4d(&mapDy, slot + lane * a_box, &full[ring.stage], k0 + 32 * lane, 0, p0, n0);
-        else if (lane == ka)
-          tma_load_4d(&mapX, slot + a_bytes, &full[ring.stage], cc * 32, p.org_w, p0 + p.org_h, n0);
+        uint8_t* slot_a = slots_ptr + static_cast<size_t>(ring.stage) * a_bytes;
+        uint8_t* slot_b = slots_ptr + b_region + static_cast<size_t>(ring.stage) * b_bytes;
+        if (!p.row_loads) {
+          if (lane < ka)
+            tma_load_4d(&mapDy, slot_a + lane * a_box, &full[ring.stage], k0 + 32 * lane, 0, p0, n0);
+          else if (lane == ka)
+            tma_load_4d(&mapX, slot_b, &full[ring.stage], cc * 32, p.org_w, p0 + p.org_h, n0);
+        } else {
+          // one copy per (dy box, image row): row h of a box starts h * Wh rows in, and Wh is a
+          // multiple of 8 rows, so every copy lands on a whole swizzle atom
+          const int nrow = ka * p.bh;
+          for (int l = lane; l <= nrow; l += 32) {
+            if (l < nrow) {
+              const int box = l / p.bh, h = l - box * p.bh;
+              tma_load_4d(&mapDy, slot_a + box * a_box + static_cast<size_t>(h) * p.Wh * 128, &full[ring.stage],
+                          k0 + 32 * box, w0, p0 + h, n0);
+            } else {
+              tma_load_4d(&mapX, slot_b, &full[ring.stage], cc * 32, w0 + p.org_w, p0 + p.org_h, n0);
+            }
+          }
+        }
         ring.advance();
-        if (++ht == p.tiles_h) { ht = 0; ++n0; }
+        if (++wt == p.tiles_w) {
+          wt = 0;
+          if (++ht == p.tiles_h) { ht = 0; ++n0; }
+        }
       }
       if (!ok && lane == 0) {
         *abort_flag = 1;
@@ -174,12 +204,13 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
           break;
         }
         tc_fence_after();
-        const uint32_t a_addr = slots0 + static_cast<uint32_t>(ring.stage) * stage_bytes;
+        const uint32_t a_addr = slots0 + static_cast<uint32_t>(ring.stage) * a_bytes;
+        const uint32_t b_addr = slots0 + b_region + static_cast<uint32_t>(ring.stage) * b_bytes;
         const uint64_t da = smem_desc(a_addr, a_box, 512, kSwizzle128BBase32B);
         for (int g = 0; g < p.ngroups; ++g) {
           // the taps of a group are tap_col_pitch rows apart, which is the descriptor's LBO
           const uint32_t idesc = idesc_tf32(kTileM, 32 * p.grp_n[g], 1, 1);
-          const uint64_t db = smem_desc(a_addr + a_bytes + static_cast<uint32_t>(p.grp_off[g]) * 128u,
+          const uint64_t db = smem_desc(b_addr + static_cast<uint32_t>(p.grp_off[g]) * 128u,
                                         static_cast<uint32_t>(p.tap_col_pitch) * 128u, 512,
                                         kSwizzle128BBase32B);
           const uint32_t d_tmem = tmem_base + 32u * p.grp_first[g];
@@ -267,9 +298,62 @@ inline bool plan_launch(int K, int C, int T, int N, int P, int Q, const Tap* tap
     if (taps[t].dw > max_dw) max_dw = taps[t].dw;
   }
   const int halo_h = max_dh - min_dh, halo_w = max_dw - min_dw;
-  p.Wh = Q + halo_w;
-  if (p.Wh > 256) return false;
   p.org_h = min_dh; p.org_w = min_dw;
+  p.cchunks = (C + 31) / 32;
+  p.k_tiles = (K + kTileM - 1) / kTileM;
+  // dy boxes per stage: all four of an M = 128 MMA unless the whole of K fits in fewer
+  p.a_boxes = (p.k_tiles > 1 || K > 96) ? 4 : (K > 64 ? 3 : 2);
+  auto sizes = [&](int Wh, int bh, int* ra, int* raa, int* rb, int* rba) {
+    *ra = Wh * bh;
+    *raa = (*ra + 7) / 8 * 8;
+    *rb = Wh * (bh + halo_h);
+    // the last tap of the last (padding) dy row reads up to raa + halo rows + halo columns
+    const int reach = *raa + halo_h * Wh + halo_w;
+    *rba = ((reach > *rb ? reach : *rb) + 7) / 8 * 8;
+  };
+  // largest tile height whose stage fits a slot of 108 KiB (two slots: larger tiles beat a
+  // third, smaller slot -- measured); 0 when not even one row fits
+  auto fit_bh = [&](int Wh, bool rows) {
+    for (int bh = P; bh >= 1; --bh) {
+      if (bh + halo_h > 256) continue;
+      if (rows && p.a_boxes * bh + 1 > 32) continue;        // one copy per lane of the producer warp
+      int ra, raa, rb, rba;
+      sizes(Wh, bh, &ra, &raa, &rb, &rba);
+      if (static_cast<size_t>(p.a_boxes * raa + rba) * 128 <= 108 * 1024) return bh;
+    }
+    return 0;
+  };
+  // Whole rows in a box when that fits (Wh = Q + halo).  Otherwise -- maps wider than a TMA box
+  // or than a slot -- the map is cut into column tiles of bw pixels: dy is copied row by row so
+  // that the Wh - bw columns a tile does not own stay zero and add nothing to the sums; Wh is
+  // rounded up to 8 rows so that every row copy starts on a swizzle atom.
+  p.tiles_w = 1; p.bw = Q; p.row_loads = 0;
+  p.Wh = Q + halo_w;
+  int best_bh = p.Wh <= 256 ? fit_bh(p.Wh, false) : 0;
+  if (!best_bh) {
+    if (C % 4 != 0 || K % 4 != 0) return false;           // row copies need 16-byte pixel strides
+    double best = 0.0;
+    for (int tw = 2; tw <= (Q + 7) / 8; ++tw) {
+      const int bw = (Q + tw - 1) / tw;
+      const int Wh = (bw + halo_w + 7) / 8 * 8;
+      if (Wh > 256) continue;
+      const int bh0 = fit_bh(Wh, true);
+      if (!bh0) continue;
+      const int th = (P + bh0 - 1) / bh0, bh = (P + th - 1) / th;
+      // MMA rows that are real pixels, times a penalty for refetching the halo rows of x
+      const double eff = static_cast<double>(Q) * P / (static_cast<double>(tw) * th * Wh * bh);
+      const double score = eff * std::sqrt(static_cast<double>(bh) / (bh + halo_h));
+      if (score > best + 1e-9) {
+        best = score; best_bh = bh0;
+        p.tiles_w = tw; p.bw = bw; p.Wh = Wh; p.row_loads = 1;
+      }
+    }
+    if (!best_bh) return false;
+  }
+  p.tiles_h = (P + best_bh - 1) / best_bh;
+  p.bh = (P + p.tiles_h - 1) / p.tiles_h;          // balanced tiles
+  p.bhB = p.bh + halo_h;
+  sizes(p.Wh, p.bh, &p.rowsA, &p.rowsA_alloc, &p.rowsB, &p.rowsB_alloc);
   // column pitch: smallest positive dw difference inside a row of taps
   int pitch = 0;
   for (int t = 1; t < ntaps; ++t)
@@ -293,39 +377,10 @@ inline bool plan_launch(int K, int C, int T, int N, int P, int Q, const Tap* tap
     }
   }
   p.ngroups = ng;
-  p.cchunks = (C + 31) / 32;
-  p.k_tiles = (K + kTileM - 1) / kTileM;
-  auto sizes = [&](int bh, int* ra, int* raa, int* rb, int* rba) {
-    *ra = p.Wh * bh;
-    *raa = (*ra + 7) / 8 * 8;
-    *rb = p.Wh * (bh + halo_h);
-    // the last tap of the last (padding) dy row reads up to raa + halo rows + halo columns
-    const int reach = *raa + halo_h * p.Wh + halo_w;
-    *rba = ((reach > *rb ? reach : *rb) + 7) / 8 * 8;
-  };
-  int best_bh = 0;
-  for (int bh = P; bh >= 1; --bh) {
-    int ra, raa, rb, rba;
-    sizes(bh, &ra, &raa, &rb, &rba);
-    if (bh + halo_h > 256) continue;
-    const size_t stage = static_cast<size_t>(4 * raa + rba) * 128;
-    // two slots of up to 108 KiB: larger tiles beat a third, smaller slot (measured)
-    if (stage <= 108 * 1024) { best_bh = bh; break; }
-  }
-  if (!best_bh) {
-    int ra, raa, rb, rba;
-    sizes(1, &ra, &raa, &rb, &rba);
-    if (static_cast<size_t>(4 * raa + rba) * 128 > 107 * 1024) return false;
-    best_bh = 1;
-  }
-  p.tiles_h = (P + best_bh - 1) / best_bh;
-  p.bh = (P + p.tiles_h - 1) / p.tiles_h;          // balanced tiles
-  p.bhB = p.bh + halo_h;
-  sizes(p.bh, &p.rowsA, &p.rowsA_alloc, &p.rowsB, &p.rowsB_alloc);
-  const long long tiles = static_cast<long long>(p.tiles_h) * N;
+  const long long tiles = static_cast<long long>(p.tiles_w) * p.tiles_h * N;
   if (tiles > 0x7fffffffLL) return false;
   p.pix_tiles = static_cast<int>(tiles);
-  const size_t stage = static_cast<size_t>(4 * p.rowsA_alloc + p.rowsB_alloc) * 128;
+  const size_t stage = static_cast<size_t>(p.a_boxes * p.rowsA_alloc + p.rowsB_alloc) * 128;
   int st = static_cast<int>((216 * 1024) / stage);
   if (st > 8) st = 8;
   if (st < 2) return false;

@@ -32,6 +32,9 @@ CASES = [
     (1, 32, 7, 300, 64, 3, 1, 1, 1),     # map wider than a TMA box: column-tiled halo kernel
     (2, 64, 5, 610, 32, 3, 1, 1, 1),     # UNet's 608-wide maps, ragged last column tile
     (1, 32, 9, 257, 40, 5, 1, 2, 1),     # 5x5 on a wide map, odd width
+    (2, 64, 9, 224, 64, 3, 1, 1, 1),     # VGG's 224-wide 64-channel layer: a row with halo exceeds a backward-filter slot
+    (1, 32, 6, 300, 96, 3, 1, 1, 1),     # wide map, three boxes of output channels
+    (1, 32, 50, 520, 32, 3, 2, 1, 1),    # stride 2 on a wide map: column tiles per stride phase
 ]
 
 
