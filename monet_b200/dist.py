@@ -24,13 +24,29 @@ import torch
 import torch.distributed as dist
 
 
-def plan_buckets(sizes: Sequence[int], n_buckets: int) -> List[List[int]]:
+def plan_buckets(sizes: Sequence[int], n_buckets: int, tail_fraction: float = 0.0) -> List[List[int]]:
     """Splits indices 0..len(sizes)-1, taken in REVERSE order, into at most ``n_buckets``
-    consecutive groups of roughly equal total size.  Returns lists of indices, first bucket =
-    the parameters whose gradients are ready first."""
+    consecutive groups.  Returns lists of indices, first bucket = the parameters whose
+    gradients are ready first.
+
+    With ``tail_fraction`` = 0 the groups have roughly equal total size.  The last group is the
+    one nothing can hide: its gradients are complete only when the backward ends, so its
+    all-reduce runs while the compute stream waits.  With ``tail_fraction`` > 0 that group is
+    cut down to the last parameters holding at most that fraction of all elements (always at
+    least one parameter) and the other groups share the rest equally: in a convolutional
+    network the first layers have few weights, so the exposed exchange shrinks to a
+    latency-bound one."""
     order = list(range(len(sizes) - 1, -1, -1))
     total = float(sum(sizes))
     n_buckets = max(1, min(n_buckets, len(order)))
+    tail: List[int] = []
+    if tail_fraction > 0.0 and n_buckets >= 2:
+        acc = 0.0
+        while len(order) > n_buckets - 1 and (not tail or acc + sizes[order[-1]] <= tail_fraction * total):
+            acc += sizes[order[-1]]
+            tail.insert(0, order.pop())
+        n_buckets -= 1
+        total -= acc
     target = total / n_buckets
     out: List[List[int]] = [[]]
     acc = 0.0
@@ -39,18 +55,20 @@ def plan_buckets(sizes: Sequence[int], n_buckets: int) -> List[List[int]]:
             out.append([])
         out[-1].append(i)
         acc += sizes[i]
+    if tail:
+        out.append(tail)
     return out
 
 
 class GradientBuckets:
     def __init__(self, named_params: Sequence[Tuple[str, torch.Tensor]], n_buckets: int = 4,
-                 group=None, overlap: bool = True):
+                 group=None, overlap: bool = True, tail_fraction: float = 0.02):
         self.params = [(n, p) for n, p in named_params if p.requires_grad]
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.backend = dist.get_backend(group) if dist.is_initialized() else None
         sizes = [p.numel() for _, p in self.params]
-        self.buckets = plan_buckets(sizes, n_buckets)
+        self.buckets = plan_buckets(sizes, n_buckets, tail_fraction)
         self.flat: List[torch.Tensor] = []
         self.views: Dict[str, torch.Tensor] = {}
         self.bucket_of: Dict[str, int] = {}

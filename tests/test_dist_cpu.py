@@ -84,6 +84,9 @@ def test_gradient_buckets_two_ranks():
     from monet_b200.dist import plan_buckets
     assert plan_buckets([10, 10, 10, 10], 2) == [[3, 2], [1, 0]]
     assert plan_buckets([1, 1], 8) == [[1], [0]]
+    # the last bucket (nothing left to hide its all-reduce behind) shrinks to the tail fraction
+    assert plan_buckets([1, 1, 2, 50, 50, 50, 50], 4, 0.02) == [[6], [5, 4], [3], [2, 1, 0]]
+    assert plan_buckets([5, 5], 2, 0.02) == [[1], [0]] and plan_buckets([5], 3, 0.02) == [[0]]
     world, port = 2, _free_port()
     with mp.Manager() as m:
         out = m.dict()
