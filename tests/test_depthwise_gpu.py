@@ -9,7 +9,9 @@ pytestmark = pytest.mark.gpu
 
 # N, C, H, W, R, stride, pad
 CASES = [(2, 32, 14, 14, 3, 1, 1), (3, 96, 15, 13, 3, 2, 1), (2, 144, 7, 7, 3, 1, 1), (1, 8, 9, 9, 5, 1, 2),
-         (4, 24, 28, 28, 3, 2, 1), (2, 16, 6, 6, 1, 1, 0)]
+         (4, 24, 28, 28, 3, 2, 1), (2, 16, 6, 6, 1, 1, 0),
+         (2, 16, 11, 11, 3, 2, 0),      # stride 2 without padding: the per-pixel backward-data kernel
+         (1, 40, 30, 34, 3, 1, 1)]      # interior tiles of the row-tiled kernels
 
 
 @pytest.mark.parametrize("case", CASES)
