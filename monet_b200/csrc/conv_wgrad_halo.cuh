@@ -63,6 +63,12 @@ struct WgHaloParams {
   int org_h, org_w;         // x box origin relative to the dy box origin (in x-view pixels)
   int stages;
   int use_atomics;
+  // Filter-row mode (frows > 0; layers with 128 or more input channels, stride 1, dilation 1): a
+  // CTA owns ONE filter row and `gch` 32-channel chunks of x.  Its x boxes start at that filter
+  // row (no halo rows), the chunks sit back to back, and one MMA per tap s spans all chunks
+  // (N = 32 * chunks, leading-dimension stride = one x box) at the operand offset of s rows.
+  int frows, S;             // filter rows R (0: mode off) and taps per row
+  int gch, cgroups;         // chunks per CTA and ceil(cchunks / gch)
 };
 
 __global__ void __launch_bounds__(192, 1)
@@ -80,11 +86,21 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+  const bool rowmode = p.frows > 0;
   int wi = blockIdx.x;
   const int split = wi % p.splits;
   wi /= p.splits;
-  const int cc = wi % p.cchunks;
-  const int kt = wi / p.cchunks;
+  int cc, kt, frow = 0, nch = 1;          // first chunk, k tile, filter row, chunks of this CTA
+  if (rowmode) {
+    cc = (wi % p.cgroups) * p.gch;
+    wi /= p.cgroups;
+    frow = wi % p.frows;
+    kt = wi / p.frows;
+    nch = (p.cchunks - cc) < p.gch ? (p.cchunks - cc) : p.gch;
+  } else {
+    cc = wi % p.cchunks;
+    kt = wi / p.cchunks;
+  }
   const int k0 = kt * kTileM;
   int ka = (p.K - k0 + 31) / 32;
   if (ka > 4) ka = 4;
@@ -99,11 +115,13 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
   // sizes to cover them -- and land in accumulator rows that are never stored.
   const uint32_t a_box = static_cast<uint32_t>(p.rowsA_alloc) * 128u;
   const uint32_t a_bytes = static_cast<uint32_t>(p.a_boxes) * a_box;
-  const uint32_t b_bytes = static_cast<uint32_t>(p.rowsB_alloc) * 128u;
+  const uint32_t b_box = static_cast<uint32_t>(p.rowsB_alloc) * 128u;
+  const uint32_t b_bytes = b_box * static_cast<uint32_t>(rowmode ? p.gch : 1);
   const uint32_t b_region = static_cast<uint32_t>(p.stages) * a_bytes;
-  const uint32_t tx_bytes = static_cast<uint32_t>((p.row_loads ? ka * p.bh * p.bw : ka * p.rowsA) + p.rowsB) * 128u;
+  const uint32_t tx_bytes =
+      static_cast<uint32_t>((p.row_loads ? ka * p.bh * p.bw : ka * p.rowsA) + nch * p.rowsB) * 128u;
   uint32_t tmem_cols = 32;
-  while (tmem_cols < 32u * p.ntaps) tmem_cols <<= 1;
+  while (tmem_cols < 32u * (rowmode ? p.S * p.gch : p.ntaps)) tmem_cols <<= 1;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
@@ -160,19 +178,21 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
         if (!p.row_loads) {
           if (lane < ka)
             tma_load_4d(&mapDy, slot_a + lane * a_box, &full[ring.stage], k0 + 32 * lane, 0, p0, n0);
-          else if (lane == ka)
-            tma_load_4d(&mapX, slot_b, &full[ring.stage], cc * 32, p.org_w, p0 + p.org_h, n0);
+          else if (lane < ka + nch)
+            tma_load_4d(&mapX, slot_b + (lane - ka) * b_box, &full[ring.stage], (cc + lane - ka) * 32, p.org_w,
+                        p0 + p.org_h + frow, n0);
         } else {
           // one copy per (dy box, image row): row h of a box starts h * Wh rows in, and Wh is a
           // multiple of 8 rows, so every copy lands on a whole swizzle atom
           const int nrow = ka * p.bh;
-          for (int l = lane; l <= nrow; l += 32) {
+          for (int l = lane; l < nrow + nch; l += 32) {
             if (l < nrow) {
               const int box = l / p.bh, h = l - box * p.bh;
               tma_load_4d(&mapDy, slot_a + box * a_box + static_cast<size_t>(h) * p.Wh * 128, &full[ring.stage],
                           k0 + 32 * box, w0, p0 + h, n0);
             } else {
-              tma_load_4d(&mapX, slot_b, &full[ring.stage], cc * 32, w0 + p.org_w, p0 + p.org_h, n0);
+              tma_load_4d(&mapX, slot_b + (l - nrow) * b_box, &full[ring.stage], (cc + l - nrow) * 32,
+                          w0 + p.org_w, p0 + p.org_h + frow, n0);
             }
           }
         }
@@ -207,6 +227,17 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
         const uint32_t a_addr = slots0 + static_cast<uint32_t>(ring.stage) * a_bytes;
         const uint32_t b_addr = slots0 + b_region + static_cast<uint32_t>(ring.stage) * b_bytes;
         const uint64_t da = smem_desc(a_addr, a_box, 512, kSwizzle128BBase32B);
+        if (rowmode) {
+          // one MMA per tap of the filter row, N = all chunks of this CTA (LBO = one x box)
+          const uint32_t idesc = idesc_tf32(kTileM, 32 * nch, 1, 1);
+          for (int sx = 0; sx < p.S; ++sx) {
+            const uint64_t db = smem_desc(b_addr + static_cast<uint32_t>(sx * p.tap_col_pitch) * 128u, b_box, 512,
+                                          kSwizzle128BBase32B);
+            const uint32_t d_tmem = tmem_base + 32u * static_cast<uint32_t>(sx * p.gch);
+            for (int k = 0; k < ksteps; ++k)
+              mma_tf32(d_tmem, da + 64u * k, db + 64u * k, idesc, (it | k) != 0 ? 1u : 0u);
+          }
+        } else
         for (int g = 0; g < p.ngroups; ++g) {
           // the taps of a group are tap_col_pitch rows apart, which is the descriptor's LBO
           const uint32_t idesc = idesc_tf32(kTileM, 32 * p.grp_n[g], 1, 1);
@@ -234,7 +265,13 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
       tc_fence_after();
       float* base = p.out + static_cast<long long>(split) * p.split_stride;
       const int k = k0 + warp * 32 + lane;
-      for (int t = 0; t < p.ntaps; ++t) {
+      const int n_units = rowmode ? p.S * nch : p.ntaps;
+      for (int u = 0; u < n_units; ++u) {
+        // unit -> accumulator column block, filter tap and 32-channel chunk
+        const int sx = rowmode ? u / nch : 0, cj = rowmode ? u - sx * nch : 0;
+        const int t = rowmode ? sx * p.gch + cj : u;
+        const int tap = rowmode ? p.btap[frow * p.S + sx] : p.btap[u];
+        const int cu = cc + cj;
         float v[32];
         if (n_iter > 0) {
           tmem_ld32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + 32u * t, v);
@@ -244,8 +281,8 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
           for (int j = 0; j < 32; ++j) v[j] = 0.f;
         }
         if (k < p.K) {
-          float* dst = base + (static_cast<long long>(k) * p.T + p.btap[t]) * p.C + cc * 32;
-          const int left = p.C - cc * 32;
+          float* dst = base + (static_cast<long long>(k) * p.T + tap) * p.C + cu * 32;
+          const int left = p.C - cu * 32;
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             if (4 * j < left) {
@@ -278,14 +315,17 @@ struct Plan {
   WgHaloParams p;
   size_t smem;
   int grid;
+  int items;      // work items before the pixel split: grid = items * splits
 };
 
 struct Tap { int dh, dw, btap; };   // x pixel = dy pixel + (dh, dw) in the x view; filter tap index
 
 // One launch: dy grid P x Q (x N images), an x view, and the taps that read that view.
 // `taps` must be sorted by (dh, dw).  Returns false when the geometry does not fit.
+// `frows` > 0 asks for the filter-row mode (the taps must then be the full frows x S grid at
+// dilation 1): a CTA takes one filter row and up to 16 / S chunks of x.
 inline bool plan_launch(int K, int C, int T, int N, int P, int Q, const Tap* taps, int ntaps,
-                        int variant, Plan* pl) {
+                        int variant, Plan* pl, int frows = 0, int S = 0) {
   if (ntaps < 1 || ntaps > 16) return false;
   WgHaloParams& p = pl->p;
   memset(&p, 0, sizeof(p));
@@ -297,10 +337,19 @@ inline bool plan_launch(int K, int C, int T, int N, int P, int Q, const Tap* tap
     if (taps[t].dw < min_dw) min_dw = taps[t].dw;
     if (taps[t].dw > max_dw) max_dw = taps[t].dw;
   }
-  const int halo_h = max_dh - min_dh, halo_w = max_dw - min_dw;
+  // in filter-row mode the x boxes of a CTA start at its filter row: no halo rows
+  const int halo_h = frows > 0 ? 0 : max_dh - min_dh, halo_w = max_dw - min_dw;
   p.org_h = min_dh; p.org_w = min_dw;
   p.cchunks = (C + 31) / 32;
   p.k_tiles = (K + kTileM - 1) / kTileM;
+  p.frows = frows; p.S = S; p.gch = 1; p.cgroups = p.cchunks;
+  if (frows > 0) {
+    if (S < 1 || S > 16 || frows * S != ntaps) return false;
+    const int gmax = 16 / S;                       // 512 accumulator columns / (32 * S)
+    p.cgroups = (p.cchunks + gmax - 1) / gmax;
+    p.gch = (p.cchunks + p.cgroups - 1) / p.cgroups;
+  }
+  const int xb = p.gch;                            // x boxes per stage
   // dy boxes per stage: all four of an M = 128 MMA unless the whole of K fits in fewer
   p.a_boxes = (p.k_tiles > 1 || K > 96) ? 4 : (K > 64 ? 3 : 2);
   auto sizes = [&](int Wh, int bh, int* ra, int* raa, int* rb, int* rba) {
@@ -316,10 +365,10 @@ inline bool plan_launch(int K, int C, int T, int N, int P, int Q, const Tap* tap
   auto fit_bh = [&](int Wh, bool rows) {
     for (int bh = P; bh >= 1; --bh) {
       if (bh + halo_h > 256) continue;
-      if (rows && p.a_boxes * bh + 1 > 32) continue;        // one copy per lane of the producer warp
+      if (rows && p.a_boxes * bh + xb > 32) continue;       // one copy per lane of the producer warp
       int ra, raa, rb, rba;
       sizes(Wh, bh, &ra, &raa, &rb, &rba);
-      if (static_cast<size_t>(p.a_boxes * raa + rba) * 128 <= 108 * 1024) return bh;
+      if (static_cast<size_t>(p.a_boxes * raa + xb * rba) * 128 <= 108 * 1024) return bh;
     }
     return 0;
   };
@@ -380,13 +429,13 @@ inline bool plan_launch(int K, int C, int T, int N, int P, int Q, const Tap* tap
   const long long tiles = static_cast<long long>(p.tiles_w) * p.tiles_h * N;
   if (tiles > 0x7fffffffLL) return false;
   p.pix_tiles = static_cast<int>(tiles);
-  const size_t stage = static_cast<size_t>(p.a_boxes * p.rowsA_alloc + p.rowsB_alloc) * 128;
+  const size_t stage = static_cast<size_t>(p.a_boxes * p.rowsA_alloc + xb * p.rowsB_alloc) * 128;
   int st = static_cast<int>((216 * 1024) / stage);
   if (st > 8) st = 8;
   if (st < 2) return false;
   p.stages = st;
   pl->smem = 512 + 1024 + stage * st;
-  const int items = p.k_tiles * p.cchunks;
+  const int items = frows > 0 ? p.k_tiles * frows * p.cgroups : p.k_tiles * p.cchunks;
   // one wave of CTAs: the kernel is bound by MMA issue, a second wave would only repeat the
   // set-up and double the number of partial results to combine
   int splits = num_sms() / items;
@@ -396,6 +445,7 @@ inline bool plan_launch(int K, int C, int T, int N, int P, int Q, const Tap* tap
   if (variant == 1 && splits > 64) splits = 64;
   p.splits = splits;
   p.use_atomics = variant == 0;
+  pl->items = items;
   pl->grid = items * splits;
   return true;
 }
@@ -422,7 +472,35 @@ inline bool eligible(const mb_conv_desc* d) {
   return d->stride_h <= 2 && d->stride_w <= 2 && d->Q >= 24 && d->P >= 24;
 }
 
+// Filter-row mode: stride 1, dilation 1, whole 32-channel chunks, at least 128 input channels.
+// Where it is used is a matter of measurement against the per-tap kernel of conv_wgrad.cuh
+// (batch 176 VGG-16 and batch 11 UNet layers, all 3x3): that kernel's 256 x 256 tile needs 2 KB
+// of operands per pixel from L2 and is starved by it on most layers, this mode needs 1 KB for
+// three quarters of the work but issues 128-column MMAs and pads every row to Wh.  It wins for
+// 128 input channels on every map (1.43 -> 1.18 ms on 112x112, 0.46 -> 0.35 on 208x304) and for
+// 256 / 512 input channels unless K = 256 -- where the per-tap kernel has one M = 256 tile, its
+// best case (0.93 against 1.39 ms) -- or the map is small or the work items leave SMs idle.
+inline bool row_mode_ok(const mb_conv_desc* d) {
+  if (!(d->groups == 1 && d->R * d->S > 1 && d->R * d->S <= 16 && d->stride_h == 1 && d->stride_w == 1 &&
+        d->dil_h == 1 && d->dil_w == 1 && d->C % 32 == 0 && d->K % 4 == 0 && d->C >= 128))
+    return false;
+  if (d->C == 128) return true;
+  return d->C <= 512 && d->K != 256 && static_cast<long long>(d->P) * d->Q >= 700;
+}
+
 inline bool make_plans(const mb_conv_desc* d, int variant, Launches* L) {
+  if (row_mode_ok(d)) {
+    Tap taps[16];
+    int nt = 0;
+    for (int r = 0; r < d->R; ++r)
+      for (int s = 0; s < d->S; ++s) taps[nt++] = Tap{r - d->pad_h, s - d->pad_w, r * d->S + s};
+    L->n = 1;
+    L->phase_a[0] = L->phase_b[0] = 0;
+    // only when its work items fill the SMs: k tiles x filter rows x chunk groups x pixel splits
+    if (plan_launch(d->K, d->C, d->R * d->S, d->N, d->P, d->Q, taps, nt, variant, &L->plan[0], d->R, d->S) &&
+        L->plan[0].grid * 100 >= num_sms() * 85)
+      return true;
+  }
   if (!eligible(d)) return false;
   L->n = 0;
   for (int a = 0; a < d->stride_h; ++a)
@@ -455,7 +533,7 @@ inline bool make_plans(const mb_conv_desc* d, int variant, Launches* L) {
         const int s0 = L->plan[0].p.splits < L->plan[i].p.splits ? L->plan[0].p.splits : L->plan[i].p.splits;
         for (int j = 0; j < L->n; ++j) {
           L->plan[j].p.splits = s0;
-          L->plan[j].grid = L->plan[j].p.k_tiles * L->plan[j].p.cchunks * s0;
+          L->plan[j].grid = L->plan[j].items * s0;
         }
       }
   }

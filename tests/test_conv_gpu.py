@@ -35,6 +35,10 @@ CASES = [
     (2, 64, 9, 224, 64, 3, 1, 1, 1),     # VGG's 224-wide 64-channel layer: a row with halo exceeds a backward-filter slot
     (1, 32, 6, 300, 96, 3, 1, 1, 1),     # wide map, three boxes of output channels
     (1, 32, 50, 520, 32, 3, 2, 1, 1),    # stride 2 on a wide map: column tiles per stride phase
+    (2, 256, 10, 12, 96, 3, 1, 1, 1),    # backward-filter by filter row: 8 chunks in two groups, three dy boxes
+    (1, 160, 9, 40, 64, 3, 1, 1, 1),     # 5 chunks in one group
+    (1, 192, 6, 300, 32, 3, 1, 1, 1),    # filter-row mode with column tiles
+    (2, 128, 9, 9, 136, 5, 1, 2, 1),     # 5x5: three chunks at most per CTA, two tiles of output channels
 ]
 
 
