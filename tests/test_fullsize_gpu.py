@@ -155,6 +155,40 @@ def test_resnet50_convolutions_at_batch_184_against_the_oracle(cuda, geom):
     assert F.conv_device_status() == 0
 
 
+# 3x3 layers of VGG-16 (224-wide input) and of the UNet configuration (416 x 608 input) at their
+# real spatial extents, with a batch the CPU oracle finishes in seconds: (N, C, H, W, K).  They
+# select the column-tiled many-tap kernels, the backward-filter halo kernel with column tiles
+# and row-wise dy copies, and the backward-filter-by-filter-row mode (with and without tiles).
+WIDE_LAYERS = [(2, 64, 224, 224, 64), (1, 64, 416, 608, 64), (1, 128, 416, 608, 64), (1, 128, 208, 304, 128),
+               (2, 128, 112, 112, 128), (2, 512, 28, 28, 512), (1, 256, 52, 76, 512), (1, 64, 208, 304, 128)]
+
+
+@pytest.mark.parametrize("layer", WIDE_LAYERS, ids=lambda g: "n%d_c%d_%dx%d_k%d" % g)
+def test_vgg_and_unet_layers_at_their_real_extents(cuda, layer):
+    from monet_b200 import functional as F
+    from oracle import lm_ops_oracle as oracle
+    N, C, H, W, K = layer
+    g = torch.Generator().manual_seed(C + W)
+    x = torch.randn(N, C, H, W, generator=g)
+    w = torch.randn(K, C, 3, 3, generator=g) * (2.0 / (C * 9)) ** 0.5
+    ref_y = oracle.conv_forward(x, w, None, 1, 1, 1)
+    dy = torch.randn(ref_y.shape, generator=g)
+    ref_dx, ref_dw, _ = oracle.conv_backward(dy, x, w, 1, 1, 1)
+
+    def err(a, ref):
+        return float((a.cpu() - ref).abs().max() / ref.abs().max().clamp_min(1e-6))
+
+    xc = x.to(cuda).contiguous(memory_format=torch.channels_last)
+    dyc = dy.to(cuda).contiguous(memory_format=torch.channels_last)
+    wc = w.to(cuda)
+    assert err(F.conv2d_fprop(xc, wc, None, 1, 1, 1), ref_y) < 2e-2
+    assert err(F.conv2d_dgrad(dyc, wc, x.shape, 1, 1, 1), ref_dx) < 2e-2
+    for variant in (0, 1):
+        dw, _ = F.conv2d_wgrad(xc, dyc, w.shape, 1, 1, 1, variant=variant)
+        assert err(dw, ref_dw) < 2e-2, ("wgrad", variant, err(dw, ref_dw))
+    assert F.conv_device_status() == 0
+
+
 def test_stem_configuration_verbatim(cuda):
     """The CPU-runnable configuration at its stated size: N = 4, 3 x 224 x 224, conv 7x7/2 ->
     BN(train) -> ReLU (1-bit mask) -> max-pool 3x3/2 (4-bit indices), forward and backward through
