@@ -69,6 +69,13 @@ struct WgHaloParams {
   // (N = 32 * chunks, leading-dimension stride = one x box) at the operand offset of s rows.
   int frows, S;             // filter rows R (0: mode off) and taps per row
   int gch, cgroups;         // chunks per CTA and ceil(cchunks / gch)
+  // Stacked mode (3x3, stride 1, K <= 64): the lower half of the M = 128 operand, which 64 output
+  // channels leave empty, holds the same dy channels one image row further down.  An MMA at
+  // the x offset of filter row r then yields filter row r in accumulator rows 0-63 and filter
+  // row r - 1 in rows 64-127, so offsets r = 1 and r = 3 cover the three filter rows with two
+  // MMAs per K step instead of three (rows 0-63 of the second are not used).  Tiles start one
+  // row above the map so that both halves see every dy row once.
+  int stack;
 };
 
 __global__ void __launch_bounds__(192, 1)
@@ -118,8 +125,9 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
   const uint32_t b_box = static_cast<uint32_t>(p.rowsB_alloc) * 128u;
   const uint32_t b_bytes = b_box * static_cast<uint32_t>(rowmode ? p.gch : 1);
   const uint32_t b_region = static_cast<uint32_t>(p.stages) * a_bytes;
+  const int ndy = p.stack ? 2 * ka : ka;   // dy boxes copied per stage
   const uint32_t tx_bytes =
-      static_cast<uint32_t>((p.row_loads ? ka * p.bh * p.bw : ka * p.rowsA) + nch * p.rowsB) * 128u;
+      static_cast<uint32_t>((p.row_loads ? ndy * p.bh * p.bw : ndy * p.rowsA) + nch * p.rowsB) * 128u;
   uint32_t tmem_cols = 32;
   while (tmem_cols < 32u * (rowmode ? p.S * p.gch : p.ntaps)) tmem_cols <<= 1;
 
@@ -163,7 +171,7 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
       bool ok = true;
       int wt = t_begin % p.tiles_w, ht = (t_begin / p.tiles_w) % p.tiles_h, n0 = t_begin / (p.tiles_w * p.tiles_h);
       for (int t = t_begin; t < t_end; ++t) {
-        const int p0 = ht * p.bh, w0 = wt * p.bw;
+        const int p0 = ht * p.bh - (p.stack ? 1 : 0), w0 = wt * p.bw;
         if (lane == 0) {
           ok = mbar_wait(&empty[ring.stage], ring.phase ^ 1u, abort_flag);
           if (ok) {
@@ -176,20 +184,24 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
         uint8_t* slot_a = slots_ptr + static_cast<size_t>(ring.stage) * a_bytes;
         uint8_t* slot_b = slots_ptr + b_region + static_cast<size_t>(ring.stage) * b_bytes;
         if (!p.row_loads) {
-          if (lane < ka)
-            tma_load_4d(&mapDy, slot_a + lane * a_box, &full[ring.stage], k0 + 32 * lane, 0, p0, n0);
-          else if (lane < ka + nch)
-            tma_load_4d(&mapX, slot_b + (lane - ka) * b_box, &full[ring.stage], (cc + lane - ka) * 32, p.org_w,
+          if (lane < ndy) {
+            // stacked: copies ka.. go to boxes 2.. and start one image row further down
+            const int half = lane / ka, j = lane - half * ka;
+            tma_load_4d(&mapDy, slot_a + (2 * half + j) * a_box, &full[ring.stage], k0 + 32 * j, 0, p0 + half, n0);
+          } else if (lane < ndy + nch) {
+            tma_load_4d(&mapX, slot_b + (lane - ndy) * b_box, &full[ring.stage], (cc + lane - ndy) * 32, p.org_w,
                         p0 + p.org_h + frow, n0);
+          }
         } else {
           // one copy per (dy box, image row): row h of a box starts h * Wh rows in, and Wh is a
           // multiple of 8 rows, so every copy lands on a whole swizzle atom
-          const int nrow = ka * p.bh;
+          const int nrow = ndy * p.bh;
           for (int l = lane; l < nrow + nch; l += 32) {
             if (l < nrow) {
-              const int box = l / p.bh, h = l - box * p.bh;
-              tma_load_4d(&mapDy, slot_a + box * a_box + static_cast<size_t>(h) * p.Wh * 128, &full[ring.stage],
-                          k0 + 32 * box, w0, p0 + h, n0);
+              const int d = l / p.bh, h = l - d * p.bh;
+              const int half = d / ka, j = d - half * ka;
+              tma_load_4d(&mapDy, slot_a + (2 * half + j) * a_box + static_cast<size_t>(h) * p.Wh * 128,
+                          &full[ring.stage], k0 + 32 * j, w0, p0 + half + h, n0);
             } else {
               tma_load_4d(&mapX, slot_b + (l - nrow) * b_box, &full[ring.stage], (cc + l - nrow) * 32,
                           w0 + p.org_w, p0 + p.org_h + frow, n0);
@@ -264,13 +276,22 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
     if (got) {
       tc_fence_after();
       float* base = p.out + static_cast<long long>(split) * p.split_stride;
-      const int k = k0 + warp * 32 + lane;
-      const int n_units = rowmode ? p.S * nch : p.ntaps;
+      // stacked: accumulator rows 64-127 (warps 2, 3) are output channels 0-63 again
+      const int k = k0 + (p.stack ? (warp & 1) : warp) * 32 + lane;
+      const int n_units = rowmode ? p.S * nch : (p.stack ? 2 * p.S : p.ntaps);
       for (int u = 0; u < n_units; ++u) {
         // unit -> accumulator column block, filter tap and 32-channel chunk
         const int sx = rowmode ? u / nch : 0, cj = rowmode ? u - sx * nch : 0;
         const int t = rowmode ? sx * p.gch + cj : u;
-        const int tap = rowmode ? p.btap[frow * p.S + sx] : p.btap[u];
+        int tap = rowmode ? p.btap[frow * p.S + sx] : p.btap[p.stack ? 0 : u];
+        if (p.stack) {
+          // block 0 (x offset of filter row 1): rows 0-63 -> filter row 1, rows 64-127 -> row 0;
+          // block 1 (offset of "row 3"): rows 64-127 -> filter row 2, rows 0-63 unused
+          const int blk = u / p.S, sc = u - blk * p.S;
+          const int frow_of = warp < 2 ? (blk == 0 ? 1 : -1) : (blk == 0 ? 0 : 2);
+          if (frow_of < 0) continue;
+          tap = p.btap[frow_of * p.S + sc];
+        }
         const int cu = cc + cj;
         float v[32];
         if (n_iter > 0) {
@@ -337,8 +358,14 @@ inline bool plan_launch(int K, int C, int T, int N, int P, int Q, const Tap* tap
     if (taps[t].dw < min_dw) min_dw = taps[t].dw;
     if (taps[t].dw > max_dw) max_dw = taps[t].dw;
   }
-  // in filter-row mode the x boxes of a CTA start at its filter row: no halo rows
-  const int halo_h = frows > 0 ? 0 : max_dh - min_dh, halo_w = max_dw - min_dw;
+  // stacked mode: a full 3x3 grid of taps at dilation 1 and at most 64 output channels
+  bool stack = frows == 0 && K <= 64 && ntaps == 9;
+  for (int t = 0; stack && t < 9; ++t)
+    stack = taps[t].dh == min_dh + t / 3 && taps[t].dw == min_dw + t % 3;
+  p.stack = stack ? 1 : 0;
+  // in filter-row mode the x boxes of a CTA start at its filter row: no halo rows; in stacked
+  // mode the second MMA reads at the offset of a fourth filter row
+  const int halo_h = frows > 0 ? 0 : (stack ? 3 : max_dh - min_dh), halo_w = max_dw - min_dw;
   p.org_h = min_dh; p.org_w = min_dw;
   p.cchunks = (C + 31) / 32;
   p.k_tiles = (K + kTileM - 1) / kTileM;
@@ -351,7 +378,7 @@ inline bool plan_launch(int K, int C, int T, int N, int P, int Q, const Tap* tap
   }
   const int xb = p.gch;                            // x boxes per stage
   // dy boxes per stage: all four of an M = 128 MMA unless the whole of K fits in fewer
-  p.a_boxes = (p.k_tiles > 1 || K > 96) ? 4 : (K > 64 ? 3 : 2);
+  p.a_boxes = (p.k_tiles > 1 || K > 96 || stack) ? 4 : (K > 64 ? 3 : 2);
   auto sizes = [&](int Wh, int bh, int* ra, int* raa, int* rb, int* rba) {
     *ra = Wh * bh;
     *raa = (*ra + 7) / 8 * 8;
@@ -399,8 +426,9 @@ inline bool plan_launch(int K, int C, int T, int N, int P, int Q, const Tap* tap
     }
     if (!best_bh) return false;
   }
-  p.tiles_h = (P + best_bh - 1) / best_bh;
-  p.bh = (P + p.tiles_h - 1) / p.tiles_h;          // balanced tiles
+  const int Pt = P + (stack ? 1 : 0);              // stacked tiles start one row above the map
+  p.tiles_h = (Pt + best_bh - 1) / best_bh;
+  p.bh = (Pt + p.tiles_h - 1) / p.tiles_h;         // balanced tiles
   p.bhB = p.bh + halo_h;
   sizes(p.Wh, p.bh, &p.rowsA, &p.rowsA_alloc, &p.rowsB, &p.rowsB_alloc);
   // column pitch: smallest positive dw difference inside a row of taps
@@ -426,6 +454,16 @@ inline bool plan_launch(int K, int C, int T, int N, int P, int Q, const Tap* tap
     }
   }
   p.ngroups = ng;
+  if (stack) {
+    // two MMAs per K step: at the x offsets of filter rows 1 and "3", three taps wide each
+    p.S = 3;
+    p.ngroups = 2;
+    for (int g = 0; g < 2; ++g) {
+      p.grp_off[g] = static_cast<short>((1 + 2 * g) * p.Wh);
+      p.grp_n[g] = 3;
+      p.grp_first[g] = static_cast<unsigned char>(3 * g);
+    }
+  }
   const long long tiles = static_cast<long long>(p.tiles_w) * p.tiles_h * N;
   if (tiles > 0x7fffffffLL) return false;
   p.pix_tiles = static_cast<int>(tiles);
