@@ -92,6 +92,9 @@ MICRO = {
     # fused softmax + cross-entropy on 65 536 rows of 1000 classes (ResNet's own 184 rows are 0.7 MB)
     "dw3x3_fprop": ("dw_fprop", 144, 56, 144, 3, 1, 1), "dw3x3_dgrad": ("dw_dgrad", 144, 56, 144, 3, 1, 1),
     "dw3x3_wgrad": ("dw_wgrad", 144, 56, 144, 3, 1, 1),
+    "dw3x3s2_fprop": ("dw_fprop", 96, 112, 96, 3, 2, 1), "dw3x3s2_dgrad": ("dw_dgrad", 96, 112, 96, 3, 2, 1),
+    # VGG-16's 512-channel 28x28 layer (--micro-batch 176): backward-filter by filter row
+    "wgrad3x3_c512_28": ("wgrad", 512, 28, 512, 3, 1, 1),
     "cat_bwd": ("cat_bwd", 128, 208, 0, 0, 0, 0), "cat_fwd": ("cat_fwd", 128, 208, 0, 0, 0, 0),
     "fc_fwd": ("fc_fwd", 25088, 1, 4096, 1, 1, 0), "fc_dgrad": ("fc_dgrad", 25088, 1, 4096, 1, 1, 0),
     "fc_wgrad": ("fc_wgrad", 25088, 1, 4096, 1, 1, 0),
