@@ -240,6 +240,10 @@ conv_gemm_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         issue_unrolled(std::integral_constant<int, 9>{}, std::integral_constant<int, 2>{});
       else if (p.num_taps == 9 && p.MT == 1)
         issue_unrolled(std::integral_constant<int, 9>{}, std::integral_constant<int, 1>{});
+      else if (p.num_taps == 3 && p.MT == 2)      // 3x3 on a few-channel input: one tap per filter row
+        issue_unrolled(std::integral_constant<int, 3>{}, std::integral_constant<int, 2>{});
+      else if (p.num_taps == 3 && p.MT == 1)
+        issue_unrolled(std::integral_constant<int, 3>{}, std::integral_constant<int, 1>{});
       else if (p.num_taps == 4 && p.MT == 2)      // the 7x7 stride-2 stem: four row taps per phase pair
         issue_unrolled(std::integral_constant<int, 4>{}, std::integral_constant<int, 2>{});
       else if (p.num_taps == 4 && p.MT == 1)

@@ -160,7 +160,8 @@ def test_resnet50_convolutions_at_batch_184_against_the_oracle(cuda, geom):
 # select the column-tiled many-tap kernels, the backward-filter halo kernel with column tiles
 # and row-wise dy copies, and the backward-filter-by-filter-row mode (with and without tiles).
 WIDE_LAYERS = [(2, 64, 224, 224, 64), (1, 64, 416, 608, 64), (1, 128, 416, 608, 64), (1, 128, 208, 304, 128),
-               (2, 128, 112, 112, 128), (2, 512, 28, 28, 512), (1, 256, 52, 76, 512), (1, 64, 208, 304, 128)]
+               (2, 128, 112, 112, 128), (2, 512, 28, 28, 512), (1, 256, 52, 76, 512), (1, 64, 208, 304, 128),
+               (2, 3, 224, 224, 64), (1, 3, 416, 608, 64)]        # the two networks' first layers (few-channel path)
 
 
 @pytest.mark.parametrize("layer", WIDE_LAYERS, ids=lambda g: "n%d_c%d_%dx%d_k%d" % g)
@@ -178,7 +179,7 @@ def test_vgg_and_unet_layers_at_their_real_extents(cuda, layer):
     def err(a, ref):
         return float((a.cpu() - ref).abs().max() / ref.abs().max().clamp_min(1e-6))
 
-    xc = x.to(cuda).contiguous(memory_format=torch.channels_last)
+    xc = x.to(cuda).contiguous(memory_format=torch.channels_last) if C % 4 == 0 else x.to(cuda)
     dyc = dy.to(cuda).contiguous(memory_format=torch.channels_last)
     wc = w.to(cuda)
     assert err(F.conv2d_fprop(xc, wc, None, 1, 1, 1), ref_y) < 2e-2
