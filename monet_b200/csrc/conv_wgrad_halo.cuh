@@ -108,6 +108,7 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
     cc = wi % p.cchunks;
     kt = wi / p.cchunks;
   }
+  const int xrow = (rowmode && p.stack) ? 1 + 2 * frow : frow;   // x box row offset of this CTA
   const int k0 = kt * kTileM;
   int ka = (p.K - k0 + 31) / 32;
   if (ka > 4) ka = 4;
@@ -190,7 +191,7 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
             tma_load_4d(&mapDy, slot_a + (2 * half + j) * a_box, &full[ring.stage], k0 + 32 * j, 0, p0 + half, n0);
           } else if (lane < ndy + nch) {
             tma_load_4d(&mapX, slot_b + (lane - ndy) * b_box, &full[ring.stage], (cc + lane - ndy) * 32, p.org_w,
-                        p0 + p.org_h + frow, n0);
+                        p0 + p.org_h + xrow, n0);
           }
         } else {
           // one copy per (dy box, image row): row h of a box starts h * Wh rows in, and Wh is a
@@ -204,7 +205,7 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
                           &full[ring.stage], k0 + 32 * j, w0, p0 + half + h, n0);
             } else {
               tma_load_4d(&mapX, slot_b + (l - nrow) * b_box, &full[ring.stage], (cc + l - nrow) * 32,
-                          w0 + p.org_w, p0 + p.org_h + frow, n0);
+                          w0 + p.org_w, p0 + p.org_h + xrow, n0);
             }
           }
         }
@@ -283,8 +284,14 @@ conv_wgrad_halo_tcgen05(const __grid_constant__ CUtensorMap mapDy, const __grid_
         // unit -> accumulator column block, filter tap and 32-channel chunk
         const int sx = rowmode ? u / nch : 0, cj = rowmode ? u - sx * nch : 0;
         const int t = rowmode ? sx * p.gch + cj : u;
-        int tap = rowmode ? p.btap[frow * p.S + sx] : p.btap[p.stack ? 0 : u];
-        if (p.stack) {
+        int tap = rowmode ? p.btap[(p.stack ? 0 : frow) * p.S + sx] : p.btap[p.stack ? 0 : u];
+        if (rowmode && p.stack) {
+          // x offset of filter row 1 (frow 0): rows 0-63 -> filter row 1, rows 64-127 -> row 0;
+          // offset of "row 3" (frow 1): rows 64-127 -> filter row 2, rows 0-63 unused
+          const int frow_of = warp < 2 ? (frow == 0 ? 1 : -1) : (frow == 0 ? 0 : 2);
+          if (frow_of < 0) continue;
+          tap = p.btap[frow_of * p.S + sx];
+        } else if (p.stack) {
           // block 0 (x offset of filter row 1): rows 0-63 -> filter row 1, rows 64-127 -> row 0;
           // block 1 (offset of "row 3"): rows 64-127 -> filter row 2, rows 0-63 unused
           const int blk = u / p.S, sc = u - blk * p.S;
@@ -359,7 +366,7 @@ inline bool plan_launch(int K, int C, int T, int N, int P, int Q, const Tap* tap
     if (taps[t].dw > max_dw) max_dw = taps[t].dw;
   }
   // stacked mode: a full 3x3 grid of taps at dilation 1 and at most 64 output channels
-  bool stack = frows == 0 && K <= 64 && ntaps == 9;
+  bool stack = (frows == 0 || (frows == 3 && S == 3)) && K <= 64 && ntaps == 9;
   for (int t = 0; stack && t < 9; ++t)
     stack = taps[t].dh == min_dh + t / 3 && taps[t].dw == min_dw + t % 3;
   p.stack = stack ? 1 : 0;
@@ -369,7 +376,8 @@ inline bool plan_launch(int K, int C, int T, int N, int P, int Q, const Tap* tap
   p.org_h = min_dh; p.org_w = min_dw;
   p.cchunks = (C + 31) / 32;
   p.k_tiles = (K + kTileM - 1) / kTileM;
-  p.frows = frows; p.S = S; p.gch = 1; p.cgroups = p.cchunks;
+  // filter-row mode stacked: the two x offsets (filter rows 1 and "3") are the work items
+  p.frows = (frows > 0 && stack) ? 2 : frows; p.S = S; p.gch = 1; p.cgroups = p.cchunks;
   if (frows > 0) {
     if (S < 1 || S > 16 || frows * S != ntaps) return false;
     const int gmax = 16 / S;                       // 512 accumulator columns / (32 * S)
@@ -454,7 +462,7 @@ inline bool plan_launch(int K, int C, int T, int N, int P, int Q, const Tap* tap
     }
   }
   p.ngroups = ng;
-  if (stack) {
+  if (stack && frows == 0) {
     // two MMAs per K step: at the x offsets of filter rows 1 and "3", three taps wide each
     p.S = 3;
     p.ngroups = 2;
@@ -473,7 +481,7 @@ inline bool plan_launch(int K, int C, int T, int N, int P, int Q, const Tap* tap
   if (st < 2) return false;
   p.stages = st;
   pl->smem = 512 + 1024 + stage * st;
-  const int items = frows > 0 ? p.k_tiles * frows * p.cgroups : p.k_tiles * p.cchunks;
+  const int items = frows > 0 ? p.k_tiles * p.frows * p.cgroups : p.k_tiles * p.cchunks;
   // one wave of CTAs: the kernel is bound by MMA issue, a second wave would only repeat the
   // set-up and double the number of partial results to combine
   int splits = num_sms() / items;

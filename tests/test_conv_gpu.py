@@ -39,6 +39,8 @@ CASES = [
     (1, 160, 9, 40, 64, 3, 1, 1, 1),     # 5 chunks in one group
     (1, 192, 6, 300, 32, 3, 1, 1, 1),    # filter-row mode with column tiles
     (2, 128, 9, 9, 136, 5, 1, 2, 1),     # 5x5: three chunks at most per CTA, two tiles of output channels
+    (3, 128, 12, 20, 64, 3, 1, 1, 1),    # filter-row mode with the stacked dy operand (K <= 64)
+    (2, 160, 7, 9, 24, 3, 1, 1, 1),      # the same with one box of output channels and 5 chunks
 ]
 
 
