@@ -13,6 +13,7 @@
 //   wgrad  dw = x (*) dy, db = sum dy   see conv_wgrad.cuh
 #include "conv_gemm.cuh"
 #include "conv_gemm_halo.cuh"
+#include "conv_gemm_pair.cuh"
 #include "conv_wgrad.cuh"
 #include "conv_wgrad_halo.cuh"
 
@@ -238,6 +239,78 @@ int run_halo(const char* who, const float* in, int Cin, int Win, int Hin, const 
     if (taps[t].dw > max_dw) max_dw = taps[t].dw;
   }
   const int halo_h = max_dh - min_dh, halo_w = max_dw - min_dw;
+  // 64 output columns, a full 3x3 grid of taps one row above to one row below, rows that fit an
+  // M = 128 tile with their halo: two output rows per GEMM row (conv_gemm_pair.cuh)
+  if (!in_strides && ntaps == 9 && Kout == 64 && halo_h == 2 && halo_w == 2 && min_dh == -1 && Hin >= 2 && Po >= 2) {
+    PairParams q;
+    std::memset(&q, 0, sizeof(q));
+    bool grid3 = true;
+    for (int t = 0; t < 9 && grid3; ++t) {
+      const int r = taps[t].dh - min_dh, c = taps[t].dw - min_dw;
+      grid3 = r >= 0 && r < 3 && c >= 0 && c < 3 && q.btap[r][c] == 0;
+      if (grid3) q.btap[r][c] = static_cast<short>(taps[t].btap + 1);      // +1: 0 marks "not seen yet"
+    }
+    for (int r = 0; r < 3; ++r)
+      for (int c = 0; c < 3; ++c) q.btap[r][c] = static_cast<short>(q.btap[r][c] - 1);
+    if (grid3) {
+      const int pairs = (Po + 1) / 2;
+      q.bias = bias; q.Kout = Kout; q.kchunks = (Cin + kChunkK - 1) / kChunkK;
+      // whole rows in a tile when they fit; else the column tiling with the most useful MMA rows
+      q.tiles_w = 1; q.bw = Qo;
+      if (Qo + 2 > kTileM) {
+        double best = 0.0;
+        for (int bw = 14; bw <= kTileM - 2; ++bw) {
+          const int tw = (Qo + bw - 1) / bw, j = kTileM / (bw + 2);
+          const double eff = static_cast<double>(j) * Qo / (static_cast<double>(kTileM) * tw);
+          if (eff > best + 1e-9) { best = eff; q.tiles_w = tw; q.bw = bw; }
+        }
+        q.bw = (Qo + q.tiles_w - 1) / q.tiles_w;          // balanced
+      }
+      q.Wh = q.bw + 2;
+      const int jmax = kTileM / q.Wh;
+      q.MT = pairs > jmax ? 2 : 1;                       // two M tiles share every filter tile
+      q.tiles_h = (pairs + jmax * q.MT - 1) / (jmax * q.MT);
+      q.J = (pairs + q.tiles_h * q.MT - 1) / (q.tiles_h * q.MT);
+      q.Hb = q.MT * q.J + 1;
+      q.box_rows = q.Wh * q.Hb;
+      q.a_half = (q.box_rows * 128 + 1023) / 1024 * 1024;
+      q.out_rows = q.Wh * q.J;
+      q.org_w = min_dw;
+      q.rows_even = (Po + 1) / 2; q.rows_odd = Po / 2;
+      q.b_mn = filter_mn ? 1 : 0;
+      q.prof = g_conv_prof;
+      q.a_stages = 2;
+      const size_t budget = 222 * 1024 - 2048;
+      const size_t staging = (static_cast<size_t>(q.out_rows) * 128 + 1023) / 1024 * 1024;
+      const size_t fixed = 2 * 2 * static_cast<size_t>(q.a_half) + staging;
+      const long long items = static_cast<long long>(q.tiles_h) * q.tiles_w * N;
+      if (fixed + 5 * 8192 <= budget && items <= 0x7fffffffLL) {
+        q.b_stages = 3;                                    // the three filter slots of a filter column
+        q.num_items = static_cast<int>(items);
+        const size_t smem = 512 + 1024 + fixed + 5 * 8192;
+        const long long C4 = static_cast<long long>(Cin) * 4, K4 = static_cast<long long>(Kout) * 4;
+        CUtensorMap me, mo_in, mb2, moe, moo;
+        int rc = encode_act(who, &me, in, Cin, Win, (Hin + 1) / 2, N, C4, 2 * C4 * Win, C4 * Win * Hin, q.Wh, q.Hb, 1);
+        if (rc) return rc;
+        rc = encode_act(who, &mo_in, in + static_cast<long long>(Win) * Cin, Cin, Win, Hin / 2, N, C4, 2 * C4 * Win,
+                        C4 * Win * Hin, q.Wh, q.Hb, 1);
+        if (rc) return rc;
+        rc = filter_mn ? encode_filter_mn(who, &mb2, filt, Cin, T, Kout, 64) : encode_filter(who, &mb2, filt, Cin, T, Kout, 64);
+        if (rc) return rc;
+        const int sbw = q.tiles_w == 1 ? q.Wh : q.bw, sbh = q.tiles_w == 1 ? q.J : 1;   // store box
+        rc = encode_act(who, &moe, out, Kout, Qo, (Po + 1) / 2, N, K4, 2 * K4 * Qo, K4 * Qo * Po, sbw, sbh, 1);
+        if (rc) return rc;
+        rc = encode_act(who, &moo, out + static_cast<long long>(Qo) * Kout, Kout, Qo, Po / 2, N, K4, 2 * K4 * Qo,
+                        K4 * Qo * Po, sbw, sbh, 1);
+        if (rc) return rc;
+        static std::atomic<unsigned long long> pair_smem_done{0};
+        if (int rc2 = raise_smem_limit(who, conv_gemm_pair, pair_smem_done)) return rc2;
+        const int grid = q.num_items < num_sms() ? q.num_items : num_sms();
+        conv_gemm_pair<<<grid, 192, smem, st>>>(me, mo_in, mb2, moe, moo, q);
+        return after_launch("conv_gemm_pair");
+      }
+    }
+  }
   // Geometry of one candidate: the map cut into `tw` column tiles.  Returns the fraction of MMA
   // rows that are real output pixels, or 0 when the candidate does not fit (TMA box limits, two
   // accumulators, shared memory).

@@ -41,6 +41,13 @@ CASES = [
     (2, 128, 9, 9, 136, 5, 1, 2, 1),     # 5x5: three chunks at most per CTA, two tiles of output channels
     (3, 128, 12, 20, 64, 3, 1, 1, 1),    # filter-row mode with the stacked dy operand (K <= 64)
     (2, 160, 7, 9, 24, 3, 1, 1, 1),      # the same with one box of output channels and 5 chunks
+    (3, 64, 13, 17, 64, 3, 1, 1, 1),     # 64 output channels: two output rows per GEMM row, odd extents
+    (2, 96, 9, 30, 64, 3, 1, 1, 1),      # the same with three channel chunks
+    (1, 64, 2, 5, 64, 3, 1, 1, 1),       # a single row pair
+    (2, 64, 11, 20, 96, 3, 1, 1, 1),     # backward-data has 64 columns here (C = 64), forward 96
+    (1, 32, 40, 126, 64, 3, 1, 1, 1),    # the widest row that fits one tile (126 + 2 = 128)
+    (1, 64, 9, 300, 64, 3, 1, 1, 1),     # row pairs with column tiles, odd height, ragged last tile
+    (2, 32, 6, 127, 64, 3, 1, 1, 1),     # one column too wide for a single tile
 ]
 
 
