@@ -1,7 +1,8 @@
 #!/usr/bin/env python
 """Installs the HOST side of a MONeT checkout under ``baseline/_ref/`` (git-ignored).
 
-    python baseline/install_ref.py [path/to/MONeT]        # default: $MONET_ROOT or /root/reference
+    python baseline/install_ref.py [path/to/MONeT]        # default: $MONET_ROOT, else a checkout named
+                                                          # `reference` beside this repository
 
 MONeT is not an installable distribution: its ``setup.py`` names packages that have no
 ``__init__.py`` (``pip install --target`` produces an empty wheel) and its README runs everything
@@ -37,7 +38,7 @@ HOST_FILES = [
 
 
 def install(source: str | os.PathLike | None = None, target: Path = TARGET) -> Path:
-    src = Path(source or os.environ.get("MONET_ROOT", "/root/reference"))
+    src = Path(source or os.environ.get("MONET_ROOT") or HERE.parent.parent / "reference")
     if not (src / "monet" / "schedule.py").exists():
         raise FileNotFoundError(f"{src} is not a MONeT checkout (monet/schedule.py missing)")
     for rel in HOST_FILES:
